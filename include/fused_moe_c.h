@@ -1,0 +1,148 @@
+/*
+ * C-ABI of the B200 fused-MoE library (libfmoe_b200.so).
+ *
+ * This is the boundary a foreign-function binding attaches to: plain C structs with
+ * fixed-width integers, device pointers as void*, the CUDA stream as void*.  No C++
+ * or torch types appear in any signature.
+ *
+ * What it replaces: Composable Kernel's ck_tile fused-MoE host entry points
+ * (fused_moe_traits / fused_moe_args / fused_moe(traits, args, stream) and the separately
+ * callable moe_sorting).  TheRock builds that library from the rocm-libraries submodule
+ * (math-libs/CMakeLists.txt:582-608, source dir projects/composablekernel; submodule
+ * declared at .gitmodules:19-22) and ships only include/ck/** for it
+ * (math-libs/artifact-composable-kernel.toml:5-8).  The submodule is empty in the
+ * reference checkout, so no file:line inside the ck_tile headers can be cited; the C++
+ * mirror of the host surface is include/fused_moe.hpp.
+ *
+ * Ownership: the caller owns every device buffer, including the workspace whose size is
+ * queried with fmoe_get_workspace_size.  The library allocates no device memory.
+ * Errors: every entry point returns 0 on success or a negative fmoe_status; the text of
+ * the last error on the calling thread is available from fmoe_last_error().  Nothing
+ * throws across this boundary and no device code traps.
+ */
+#ifndef FMOE_B200_FUSED_MOE_C_H_
+#define FMOE_B200_FUSED_MOE_C_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FMOE_API __attribute__((visibility("default")))
+#else
+#define FMOE_API
+#endif
+
+enum fmoe_status {
+  FMOE_OK = 0,
+  FMOE_ERR_INVALID_ARG = -1,    /* null pointer, bad dimension, unsupported combination */
+  FMOE_ERR_UNSUPPORTED = -2,    /* shape / dtype / block size outside what the kernels tile */
+  FMOE_ERR_WORKSPACE = -3,      /* workspace pointer missing or too small */
+  FMOE_ERR_CUDA = -4,           /* a CUDA runtime / driver call failed */
+  FMOE_ERR_DEVICE_TIMEOUT = -5  /* a bounded device-side wait ran out (status word set) */
+};
+
+enum fmoe_dtype { FMOE_BF16 = 0, FMOE_FP8_E4M3 = 1 };
+
+enum fmoe_quant {
+  FMOE_QUANT_NONE = 0,          /* bf16 activations and weights */
+  FMOE_QUANT_TOKEN_CHANNEL = 1, /* fp8: dynamic per-token activation scale, per-output-channel weight scale */
+  FMOE_QUANT_BLOCK128 = 2       /* fp8: 1x128 activation groups, 128x128 weight blocks */
+};
+
+enum fmoe_activation { FMOE_ACT_SILU = 0 };
+
+/* Compile-time-like selection of the operator variant (ck_tile's fused_moe_traits role). */
+typedef struct fmoe_traits_c {
+  int32_t quant;        /* fmoe_quant */
+  int32_t weight_dtype; /* fmoe_dtype; must agree with quant */
+  int32_t activation;   /* fmoe_activation */
+  int32_t gate_only;    /* 0: W1 holds gate rows then up rows (2I); 1 is rejected (unsupported) */
+  int32_t block_m;      /* rows per sorted block; 128 */
+  int32_t reserved[3];
+} fmoe_traits_c;
+
+/* Run-time arguments (ck_tile's fused_moe_args role).  All pointers are device pointers. */
+typedef struct fmoe_args_c {
+  const void* x;            /* [T, H] bf16 activations */
+  const void* w1;           /* [E, 2I, H] gate rows then up rows; bf16 or e4m3 */
+  const void* w2;           /* [E, H, I]; bf16 or e4m3 */
+  const float* w1_scale;    /* quant 1: [E, 2I]; quant 2: [E, 2I/128, H/128]; else NULL */
+  const float* w2_scale;    /* quant 1: [E, H];  quant 2: [E, H/128, I/128]; else NULL */
+  const int32_t* topk_ids;  /* [T, K]; ids outside [0, E) are skipped */
+  const float* topk_weight; /* [T, K] */
+  void* out;                /* [T, H] bf16 */
+  void* workspace;          /* >= fmoe_get_workspace_size bytes, 256-byte aligned */
+  uint64_t workspace_bytes;
+  int32_t T, H, I, E, K;
+  int32_t reserved[3];
+} fmoe_args_c;
+
+/* Library version: major*10000 + minor*100 + patch. */
+FMOE_API int fmoe_version(void);
+
+/* Text of the most recent error on the calling thread ("" if none). */
+FMOE_API const char* fmoe_last_error(void);
+
+/* Capacity (in slots) of the sorted arrays for T tokens, K experts per token, E experts:
+ * T*K + E*(block_m-1) rounded up to block_m. */
+FMOE_API int64_t fmoe_sort_capacity(int32_t T, int32_t K, int32_t E, int32_t block_m);
+
+/* moe_sorting: stable bucket of the T*K (token, k) pairs by expert id, each bucket padded
+ * to a multiple of block_m.  Outputs (device): sorted_token_ids[cap] (pad = T),
+ * sorted_weights[cap] (pad = 0), sorted_expert_ids[cap/block_m] (unused blocks = -1),
+ * num_tokens_post_pad[1].  Enqueues on `stream` and returns.
+ * Replaces ck_tile's moe_sorting host call (source absent from the reference checkout). */
+FMOE_API int fmoe_sort(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                       int32_t E, int32_t block_m, int32_t* sorted_token_ids,
+                       float* sorted_weights, int32_t* sorted_expert_ids,
+                       int32_t* num_tokens_post_pad, void* stream);
+
+/* Byte offsets of the regions fmoe_run keeps in the workspace.  After a run has completed
+ * the regions hold that run's intermediates, which lets a caller (or a test) inspect every
+ * stage: meta[0] = num_tokens_post_pad, meta[1] = device status word. */
+typedef struct fmoe_ws_layout_c {
+  int64_t capacity;           /* slots in the sorted arrays */
+  uint64_t total_bytes;
+  uint64_t meta;              /* int32[64] */
+  uint64_t sorted_token_ids;  /* int32[capacity] */
+  uint64_t sorted_weights;    /* float[capacity] */
+  uint64_t sorted_rows;       /* int32[capacity]: flat token*K+k per slot, -1 = pad */
+  uint64_t sorted_expert_ids; /* int32[capacity/block_m] */
+  uint64_t mblk_cum;          /* int32[E+1]: cumulative blocks per expert */
+  uint64_t a_sorted;          /* [capacity, H] activations in sorted order (bf16 or e4m3) */
+  uint64_t a_scale;           /* float[capacity] (fp8 variants) */
+  uint64_t y;                 /* bf16 [capacity, I]: SiLU(gate)*up */
+  uint64_t y_quant;           /* e4m3 [capacity, I] (fp8 variants) */
+  uint64_t y_scale;           /* float[capacity] (fp8 variants) */
+  uint64_t slots;             /* float [T*K, H]: weighted expert outputs before the combine */
+} fmoe_ws_layout_c;
+
+FMOE_API int fmoe_get_workspace_layout(const fmoe_traits_c* traits, const fmoe_args_c* args,
+                                       fmoe_ws_layout_c* layout);
+
+/* Bytes of workspace fmoe_run needs for these traits / dimensions. */
+FMOE_API int fmoe_get_workspace_size(const fmoe_traits_c* traits, const fmoe_args_c* args,
+                                     uint64_t* bytes);
+
+/* The fused operator: moe_sorting -> gather(+quant) -> gemm1 + SiLU*up -> (quant) ->
+ * gemm2 * topk_weight -> ordered combine into out.  Asynchronous on `stream` when ms_out
+ * is NULL; when ms_out is given the call synchronises and stores the elapsed milliseconds.
+ * Replaces ck_tile's fused_moe(traits, args, stream). */
+FMOE_API int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream,
+                      float* ms_out);
+
+/* Reads the device status word of a workspace after the stream has been synchronised:
+ * 0 = clean, otherwise the code a kernel stored when a bounded wait ran out. */
+FMOE_API int fmoe_check_status(const void* workspace, void* stream, int32_t* status_out);
+
+/* Number of kernels one fmoe_run launches for these traits (for launch accounting). */
+FMOE_API int fmoe_launches_per_run(const fmoe_traits_c* traits);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* FMOE_B200_FUSED_MOE_C_H_ */

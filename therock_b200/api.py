@@ -1,0 +1,215 @@
+"""ctypes binding of the C-ABI plus the Python mirror of the ck_tile host surface:
+FusedMoeTraits / FusedMoeArgs / fused_moe(traits, args, stream) and moe_sorting."""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfmoe_b200.so")
+
+QUANT = {"none": 0, "token_channel": 1, "block128": 2}
+
+
+class FmoeError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"fmoe error {code}: {msg}")
+        self.code = code
+
+
+class _Traits(ctypes.Structure):
+    _fields_ = [("quant", ctypes.c_int32), ("weight_dtype", ctypes.c_int32),
+                ("activation", ctypes.c_int32), ("gate_only", ctypes.c_int32),
+                ("block_m", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+
+
+class _Args(ctypes.Structure):
+    _fields_ = [("x", ctypes.c_void_p), ("w1", ctypes.c_void_p), ("w2", ctypes.c_void_p),
+                ("w1_scale", ctypes.c_void_p), ("w2_scale", ctypes.c_void_p),
+                ("topk_ids", ctypes.c_void_p), ("topk_weight", ctypes.c_void_p),
+                ("out", ctypes.c_void_p), ("workspace", ctypes.c_void_p),
+                ("workspace_bytes", ctypes.c_uint64),
+                ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("I", ctypes.c_int32),
+                ("E", ctypes.c_int32), ("K", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+
+
+class _Layout(ctypes.Structure):
+    _fields_ = [("capacity", ctypes.c_int64)] + [(n, ctypes.c_uint64) for n in (
+        "total_bytes", "meta", "sorted_token_ids", "sorted_weights", "sorted_rows",
+        "sorted_expert_ids", "mblk_cum", "a_sorted", "a_scale", "y", "y_quant", "y_scale", "slots")]
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libfmoe_b200.so; raises if it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FmoeError(-100, f"{LIB_PATH} is missing: build it with "
+                                  "`python -m therock_b200.build` (nvcc, sm_100a)")
+        l = ctypes.CDLL(LIB_PATH)
+        l.fmoe_version.restype = ctypes.c_int
+        l.fmoe_last_error.restype = ctypes.c_char_p
+        l.fmoe_sort_capacity.restype = ctypes.c_int64
+        l.fmoe_sort_capacity.argtypes = [ctypes.c_int32] * 4
+        l.fmoe_sort.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
+                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        l.fmoe_get_workspace_layout.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args),
+                                                ctypes.POINTER(_Layout)]
+        l.fmoe_get_workspace_size.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args),
+                                              ctypes.POINTER(ctypes.c_uint64)]
+        l.fmoe_run.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.c_void_p,
+                               ctypes.POINTER(ctypes.c_float)]
+        l.fmoe_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
+        l.fmoe_launches_per_run.argtypes = [ctypes.POINTER(_Traits)]
+        _lib = l
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise FmoeError(rc, lib().fmoe_last_error().decode())
+
+
+@dataclass
+class FusedMoeTraits:
+    """Variant selection (role of ck_tile's fused_moe_traits)."""
+    prec_i: str = "bf16"
+    prec_w: str = "bf16"          # "bf16" | "fp8"
+    prec_o: str = "bf16"
+    quant: str = "none"           # "none" | "token_channel" | "block128"
+    activation: str = "silu"
+    gate_only: int = 0
+    block_m: int = 128
+
+    def to_c(self) -> _Traits:
+        if self.prec_i != "bf16" or self.prec_o != "bf16":
+            raise FmoeError(-2, "activations and output are bf16")
+        if self.quant not in QUANT:
+            raise FmoeError(-1, f"unknown quant mode {self.quant!r}")
+        if self.prec_w not in ("bf16", "fp8"):
+            raise FmoeError(-1, f"unknown weight precision {self.prec_w!r}")
+        if self.activation != "silu":
+            raise FmoeError(-2, "only SiLU activation is built")
+        t = _Traits()
+        t.quant = QUANT[self.quant]
+        t.weight_dtype = 0 if self.prec_w == "bf16" else 1
+        t.activation = 0
+        t.gate_only = self.gate_only
+        t.block_m = self.block_m
+        return t
+
+
+@dataclass
+class FusedMoeArgs:
+    """One call's tensors (role of ck_tile's fused_moe_args).  All CUDA tensors, contiguous."""
+    a: torch.Tensor                       # [T, H] bf16
+    g: torch.Tensor                       # [E, 2I, H] bf16 or float8_e4m3fn / uint8
+    d: torch.Tensor                       # [E, H, I]
+    topk_ids: torch.Tensor                # [T, K] int32
+    topk_weight: torch.Tensor             # [T, K] float32
+    o: Optional[torch.Tensor] = None      # [T, H] bf16 (allocated if None)
+    g_scale: Optional[torch.Tensor] = None
+    d_scale: Optional[torch.Tensor] = None
+    workspace: Optional[torch.Tensor] = None   # uint8, >= fused_moe_workspace_size bytes
+
+    def to_c(self) -> _Args:
+        for name in ("a", "g", "d", "topk_ids", "topk_weight"):
+            t = getattr(self, name)
+            if not (t.is_cuda and t.is_contiguous()):
+                raise FmoeError(-1, f"{name} must be a contiguous CUDA tensor")
+        if self.a.dtype != torch.bfloat16:
+            raise FmoeError(-1, "a must be bf16")
+        if self.topk_ids.dtype != torch.int32 or self.topk_weight.dtype != torch.float32:
+            raise FmoeError(-1, "topk_ids must be int32 and topk_weight float32")
+        T, H = self.a.shape
+        E, I2, H2 = self.g.shape
+        if H2 != H or tuple(self.d.shape) != (E, H, I2 // 2) or I2 % 2:
+            raise FmoeError(-1, "weight shapes do not match [E,2I,H] / [E,H,I]")
+        if self.topk_ids.shape[0] != T or self.topk_weight.shape != self.topk_ids.shape:
+            raise FmoeError(-1, "topk tensors must be [T, K]")
+        c = _Args()
+        c.x, c.w1, c.w2 = self.a.data_ptr(), self.g.data_ptr(), self.d.data_ptr()
+        c.w1_scale = self.g_scale.data_ptr() if self.g_scale is not None else None
+        c.w2_scale = self.d_scale.data_ptr() if self.d_scale is not None else None
+        c.topk_ids, c.topk_weight = self.topk_ids.data_ptr(), self.topk_weight.data_ptr()
+        c.out = self.o.data_ptr() if self.o is not None else None
+        if self.workspace is not None:
+            c.workspace = self.workspace.data_ptr()
+            c.workspace_bytes = self.workspace.numel() * self.workspace.element_size()
+        c.T, c.H, c.I, c.E, c.K = T, H, I2 // 2, E, self.topk_ids.shape[1]
+        return c
+
+
+def sort_capacity(T: int, K: int, E: int, block_m: int = 128) -> int:
+    return int(lib().fmoe_sort_capacity(T, K, E, block_m))
+
+
+def launches_per_run(traits: FusedMoeTraits) -> int:
+    t = traits.to_c()
+    return int(lib().fmoe_launches_per_run(ctypes.byref(t)))
+
+
+def workspace_layout(traits: FusedMoeTraits, args: FusedMoeArgs) -> dict:
+    t, a, l = traits.to_c(), args.to_c(), _Layout()
+    _check(lib().fmoe_get_workspace_layout(ctypes.byref(t), ctypes.byref(a), ctypes.byref(l)))
+    return {n: int(getattr(l, n)) for n, _ in _Layout._fields_}
+
+
+def fused_moe_workspace_size(traits: FusedMoeTraits, args: FusedMoeArgs) -> int:
+    t, a, n = traits.to_c(), args.to_c(), ctypes.c_uint64(0)
+    _check(lib().fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)))
+    return int(n.value)
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(stream.cuda_stream) if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def fused_moe(traits: FusedMoeTraits, args: FusedMoeArgs, stream=None, time_kernel: bool = False):
+    """Enqueues the fused operator on `stream` (torch current stream by default).
+    Returns the output tensor, or (output, elapsed_ms) when time_kernel is set.  Missing
+    output / workspace tensors are allocated here with torch (callers on a hot loop pass
+    their own)."""
+    if args.o is None:
+        args.o = torch.empty_like(args.a)
+    if args.workspace is None:
+        args.workspace = torch.empty(fused_moe_workspace_size(traits, args), dtype=torch.uint8,
+                                     device=args.a.device)
+    t, a = traits.to_c(), args.to_c()
+    ms = ctypes.c_float(0.0)
+    _check(lib().fmoe_run(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream),
+                          ctypes.byref(ms) if time_kernel else None))
+    return (args.o, float(ms.value)) if time_kernel else args.o
+
+
+def check_status(workspace: torch.Tensor, stream=None) -> int:
+    st = ctypes.c_int32(0)
+    _check(lib().fmoe_check_status(workspace.data_ptr(), _stream_ptr(stream), ctypes.byref(st)))
+    return int(st.value)
+
+
+def moe_sorting(topk_ids: torch.Tensor, topk_weight: torch.Tensor, num_experts: int,
+                block_m: int = 128, stream=None):
+    """Returns (sorted_token_ids, sorted_weights, sorted_expert_ids, num_tokens_post_pad)."""
+    if not (topk_ids.is_cuda and topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()):
+        raise FmoeError(-1, "topk_ids must be a contiguous CUDA int32 tensor")
+    T, K = topk_ids.shape
+    cap = sort_capacity(T, K, num_experts, block_m)
+    dev = topk_ids.device
+    ids = torch.empty(cap, dtype=torch.int32, device=dev)
+    w = torch.empty(cap, dtype=torch.float32, device=dev)
+    eids = torch.empty(cap // block_m, dtype=torch.int32, device=dev)
+    npp = torch.empty(1, dtype=torch.int32, device=dev)
+    _check(lib().fmoe_sort(topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, num_experts, block_m,
+                           ids.data_ptr(), w.data_ptr(), eids.data_ptr(), npp.data_ptr(),
+                           _stream_ptr(stream)))
+    return ids, w, eids, npp

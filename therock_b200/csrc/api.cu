@@ -1,0 +1,277 @@
+// C-ABI of libfmoe_b200.so: argument validation, workspace planning and the launch
+// sequence of the fused-MoE operator.  No device memory is allocated here; every buffer
+// belongs to the caller.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/fused_moe_c.h"
+#include "gemm.cuh"
+#include "internal.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+inline uint64_t align256(uint64_t v) { return (v + 255) & ~static_cast<uint64_t>(255); }
+
+struct Plan {
+  int64_t cap = 0;
+  fmoe_ws_layout_c l{};
+};
+
+int validate_traits(const fmoe_traits_c* t) {
+  if (!t) return fail(FMOE_ERR_INVALID_ARG, "traits is null");
+  if (t->quant < FMOE_QUANT_NONE || t->quant > FMOE_QUANT_BLOCK128)
+    return fail(FMOE_ERR_INVALID_ARG, "unknown quant mode %d", t->quant);
+  const int want = t->quant == FMOE_QUANT_NONE ? FMOE_BF16 : FMOE_FP8_E4M3;
+  if (t->weight_dtype != want)
+    return fail(FMOE_ERR_INVALID_ARG, "weight_dtype %d does not match quant mode %d", t->weight_dtype, t->quant);
+  if (t->activation != FMOE_ACT_SILU) return fail(FMOE_ERR_UNSUPPORTED, "only SiLU activation is built");
+  if (t->gate_only != 0) return fail(FMOE_ERR_UNSUPPORTED, "gate_only variant is not built");
+  if (t->block_m != fmoe::kBlockM) return fail(FMOE_ERR_UNSUPPORTED, "block_m must be %d", fmoe::kBlockM);
+  if (t->quant == FMOE_QUANT_BLOCK128)
+    return fail(FMOE_ERR_UNSUPPORTED, "block128 quantisation is not built yet");
+  return FMOE_OK;
+}
+
+int validate_dims(const fmoe_traits_c* t, const fmoe_args_c* a) {
+  if (!a) return fail(FMOE_ERR_INVALID_ARG, "args is null");
+  if (a->T < 0 || a->H <= 0 || a->I <= 0 || a->E <= 0 || a->K <= 0)
+    return fail(FMOE_ERR_INVALID_ARG, "dimensions must be positive (T=%d H=%d I=%d E=%d K=%d)", a->T, a->H, a->I, a->E, a->K);
+  if (a->K > a->E) return fail(FMOE_ERR_INVALID_ARG, "topk %d exceeds experts %d", a->K, a->E);
+  if (a->E > 1024) return fail(FMOE_ERR_UNSUPPORTED, "at most 1024 experts");
+  if (a->I % fmoe::kSlabRows) return fail(FMOE_ERR_UNSUPPORTED, "intermediate size must be a multiple of %d", fmoe::kSlabRows);
+  if (a->H % fmoe::kTileN) return fail(FMOE_ERR_UNSUPPORTED, "hidden size must be a multiple of %d", fmoe::kTileN);
+  if (static_cast<int64_t>(a->T) * a->K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
+  (void)t;
+  return FMOE_OK;
+}
+
+int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
+  const int64_t cap = fmoe_sort_capacity(a->T, a->K, a->E, t->block_m);
+  const bool fp8 = t->quant != FMOE_QUANT_NONE;
+  p->cap = cap;
+  uint64_t off = 0;
+  auto take = [&off](uint64_t bytes) { uint64_t o = off; off = align256(off + bytes); return o; };
+  fmoe_ws_layout_c& l = p->l;
+  l.capacity = cap;
+  l.meta = take(64 * sizeof(int32_t));
+  l.sorted_token_ids = take(cap * 4);
+  l.sorted_weights = take(cap * 4);
+  l.sorted_rows = take(cap * 4);
+  l.sorted_expert_ids = take(cap / t->block_m * 4);
+  l.mblk_cum = take((a->E + 1) * 4);
+  l.a_sorted = take(static_cast<uint64_t>(cap) * a->H * (fp8 ? 1 : 2));
+  l.a_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 : 0);
+  l.y = take(static_cast<uint64_t>(cap) * a->I * 2);
+  l.y_quant = take(fp8 ? static_cast<uint64_t>(cap) * a->I : 0);
+  l.y_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 : 0);
+  l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * 4);
+  l.total_bytes = off;
+  return FMOE_OK;
+}
+
+int set_device_for(const void* ptr) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+    cudaGetLastError();
+    return FMOE_OK;   // not fatal: keep the calling thread's device
+  }
+  if (attr.type == cudaMemoryTypeDevice) {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != attr.device && cudaSetDevice(attr.device) != cudaSuccess)
+      return fail(FMOE_ERR_CUDA, "cudaSetDevice(%d) failed", attr.device);
+  }
+  return FMOE_OK;
+}
+
+#define FMOE_CUDA(expr)                                                                    \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess)                                                                \
+      return fail(FMOE_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));         \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int fmoe_version(void) { return 100; }
+
+const char* fmoe_last_error(void) { return g_err; }
+
+int64_t fmoe_sort_capacity(int32_t T, int32_t K, int32_t E, int32_t block_m) {
+  if (block_m <= 0) return 0;
+  const int64_t c = static_cast<int64_t>(T) * K + static_cast<int64_t>(E) * (block_m - 1);
+  return (c + block_m - 1) / block_m * block_m;
+}
+
+int fmoe_sort(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E,
+              int32_t block_m, int32_t* sorted_token_ids, float* sorted_weights,
+              int32_t* sorted_expert_ids, int32_t* num_tokens_post_pad, void* stream) {
+  if (!topk_ids || !sorted_token_ids) return fail(FMOE_ERR_INVALID_ARG, "topk_ids and sorted_token_ids are required");
+  if (sorted_weights && !topk_weight) return fail(FMOE_ERR_INVALID_ARG, "sorted_weights requested without topk_weight");
+  if (T < 0 || K <= 0 || E <= 0 || block_m <= 0) return fail(FMOE_ERR_INVALID_ARG, "bad dimensions");
+  if (E > 1024) return fail(FMOE_ERR_UNSUPPORTED, "at most 1024 experts");
+  if (static_cast<int64_t>(T) * K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
+  int rc = set_device_for(topk_ids);
+  if (rc != FMOE_OK) return rc;
+  FMOE_CUDA(fmoe::launch_moe_sorting(topk_ids, topk_weight, T, K, E, block_m,
+                                     fmoe_sort_capacity(T, K, E, block_m), sorted_token_ids,
+                                     sorted_weights, nullptr, sorted_expert_ids, num_tokens_post_pad,
+                                     nullptr, nullptr, static_cast<cudaStream_t>(stream)));
+  return FMOE_OK;
+}
+
+int fmoe_get_workspace_layout(const fmoe_traits_c* traits, const fmoe_args_c* args,
+                              fmoe_ws_layout_c* layout) {
+  int rc = validate_traits(traits);
+  if (rc == FMOE_OK) rc = validate_dims(traits, args);
+  if (rc != FMOE_OK) return rc;
+  if (!layout) return fail(FMOE_ERR_INVALID_ARG, "layout is null");
+  Plan p;
+  make_plan(traits, args, &p);
+  *layout = p.l;
+  return FMOE_OK;
+}
+
+int fmoe_get_workspace_size(const fmoe_traits_c* traits, const fmoe_args_c* args, uint64_t* bytes) {
+  if (!bytes) return fail(FMOE_ERR_INVALID_ARG, "bytes is null");
+  fmoe_ws_layout_c l;
+  int rc = fmoe_get_workspace_layout(traits, args, &l);
+  if (rc != FMOE_OK) return rc;
+  *bytes = l.total_bytes;
+  return FMOE_OK;
+}
+
+int fmoe_launches_per_run(const fmoe_traits_c* traits) {
+  if (validate_traits(traits) != FMOE_OK) return FMOE_ERR_INVALID_ARG;
+  // sort, gather(+quant), gemm1, [quant of the intermediate], gemm2, combine
+  return traits->quant == FMOE_QUANT_NONE ? 5 : 6;
+}
+
+int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_v, float* ms_out) {
+  int rc = validate_traits(traits);
+  if (rc == FMOE_OK) rc = validate_dims(traits, args);
+  if (rc != FMOE_OK) return rc;
+  const fmoe_args_c& a = *args;
+  if (!a.x || !a.w1 || !a.w2 || !a.topk_ids || !a.topk_weight || !a.out)
+    return fail(FMOE_ERR_INVALID_ARG, "x, w1, w2, topk_ids, topk_weight and out are required");
+  const bool fp8 = traits->quant != FMOE_QUANT_NONE;
+  if (fp8 && (!a.w1_scale || !a.w2_scale)) return fail(FMOE_ERR_INVALID_ARG, "fp8 variants need w1_scale and w2_scale");
+  Plan plan;
+  make_plan(traits, args, &plan);
+  if (!a.workspace) return fail(FMOE_ERR_WORKSPACE, "workspace is null (%llu bytes needed)", (unsigned long long)plan.l.total_bytes);
+  if (a.workspace_bytes < plan.l.total_bytes)
+    return fail(FMOE_ERR_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)a.workspace_bytes,
+                (unsigned long long)plan.l.total_bytes);
+  if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return fail(FMOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  if (a.T == 0) return FMOE_OK;
+  rc = set_device_for(a.x);
+  if (rc != FMOE_OK) return rc;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  const fmoe_ws_layout_c& l = plan.l;
+  int32_t* meta = reinterpret_cast<int32_t*>(ws + l.meta);
+  int32_t* num_post_pad = meta + 0;
+  int32_t* status = meta + 1;
+  int32_t* sorted_ids = reinterpret_cast<int32_t*>(ws + l.sorted_token_ids);
+  float* sorted_w = reinterpret_cast<float*>(ws + l.sorted_weights);
+  int32_t* sorted_rows = reinterpret_cast<int32_t*>(ws + l.sorted_rows);
+  int32_t* expert_ids = reinterpret_cast<int32_t*>(ws + l.sorted_expert_ids);
+  int32_t* mblk_cum = reinterpret_cast<int32_t*>(ws + l.mblk_cum);
+  void* a_sorted = ws + l.a_sorted;
+  float* a_scale = fp8 ? reinterpret_cast<float*>(ws + l.a_scale) : nullptr;
+  void* y = ws + l.y;
+  void* yq = ws + l.y_quant;
+  float* y_scale = fp8 ? reinterpret_cast<float*>(ws + l.y_scale) : nullptr;
+  float* slots = reinterpret_cast<float*>(ws + l.slots);
+
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  if (ms_out) {
+    FMOE_CUDA(cudaEventCreate(&ev0));
+    FMOE_CUDA(cudaEventCreate(&ev1));
+    FMOE_CUDA(cudaEventRecord(ev0, stream));
+  }
+
+  FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
+                                     sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
+                                     mblk_cum, status, stream));
+  FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, fp8 ? 1 : 0,
+                                     a_sorted, a_scale, stream));
+
+  fmoe::GemmLaunch g{};
+  int drv = 0;
+  g.fp8 = fp8;
+  g.num_experts = a.E;
+  g.mblk_cum = mblk_cum;
+  g.sorted_rows = sorted_rows;
+  g.sorted_weights = sorted_w;
+  g.status = status;
+  g.max_m_blocks = static_cast<int>(plan.cap / fmoe::kBlockM);
+  // gemm1: [cap, H] x W1[E, 2I, H]^T -> SiLU(gate) * up -> y [cap, I]
+  g.epilogue = fmoe::kEpiSiluMul;
+  g.a = a_sorted; g.a_rows = plan.cap; g.b = a.w1; g.k_elems = a.H;
+  g.b_rows_per_expert = 2 * a.I;
+  g.n_blocks = a.I / fmoe::kSlabRows; g.n_stride = fmoe::kSlabRows; g.second_slab_offset = a.I;
+  g.a_scale = a_scale; g.b_scale = fp8 ? a.w1_scale : nullptr;
+  g.out = y; g.ld_out = a.I;
+  if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
+    return fail(FMOE_ERR_CUDA, "gemm1 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+
+  const void* a2 = y;
+  if (fp8) {
+    FMOE_CUDA(fmoe::launch_gather_rows(y, static_cast<int>(plan.cap), a.I, nullptr, num_post_pad, plan.cap, 1,
+                                       yq, y_scale, stream));
+    a2 = yq;
+  }
+  // gemm2: [cap, I] x W2[E, H, I]^T * topk_weight -> slots [T*K, H]
+  g.epilogue = fmoe::kEpiScaledSlots;
+  g.a = a2; g.b = a.w2; g.k_elems = a.I;
+  g.b_rows_per_expert = a.H;
+  g.n_blocks = a.H / fmoe::kTileN; g.n_stride = fmoe::kTileN; g.second_slab_offset = fmoe::kSlabRows;
+  g.a_scale = y_scale; g.b_scale = fp8 ? a.w2_scale : nullptr;
+  g.out = slots; g.ld_out = a.H;
+  if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
+    return fail(FMOE_ERR_CUDA, "gemm2 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+
+  FMOE_CUDA(fmoe::launch_combine(slots, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream));
+
+  if (ms_out) {
+    FMOE_CUDA(cudaEventRecord(ev1, stream));
+    FMOE_CUDA(cudaEventSynchronize(ev1));
+    FMOE_CUDA(cudaEventElapsedTime(ms_out, ev0, ev1));
+    cudaEventDestroy(ev0);
+    cudaEventDestroy(ev1);
+    int32_t st = 0;
+    FMOE_CUDA(cudaMemcpy(&st, status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st != 0) return fail(FMOE_ERR_DEVICE_TIMEOUT, "device status word 0x%x: a bounded wait ran out", st);
+  }
+  return FMOE_OK;
+}
+
+int fmoe_check_status(const void* workspace, void* stream, int32_t* status_out) {
+  if (!workspace || !status_out) return fail(FMOE_ERR_INVALID_ARG, "workspace and status_out are required");
+  // the meta block is the first region of every workspace layout; word 1 is the status
+  const int32_t* status = reinterpret_cast<const int32_t*>(workspace) + 1;
+  FMOE_CUDA(cudaMemcpyAsync(status_out, status, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                            static_cast<cudaStream_t>(stream)));
+  FMOE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (*status_out != 0) return fail(FMOE_ERR_DEVICE_TIMEOUT, "device status word 0x%x", *status_out);
+  return FMOE_OK;
+}
+
+}  // extern "C"

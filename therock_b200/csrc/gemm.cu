@@ -1,0 +1,120 @@
+// Host side of the grouped GEMM: TMA descriptors and the persistent launch.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "gemm.cuh"
+#include "internal.h"
+
+namespace fmoe {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime so the library does not link
+// libcuda directly.
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Row-major [rows, k_elems] matrix, box = 128 bytes of K x 128 rows, 128-byte swizzle.
+CUresult make_map(CUtensorMap* tm, const void* base, bool fp8, int64_t rows, int k_elems) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return CUDA_ERROR_NOT_FOUND;
+  const int esize = fp8 ? 1 : 2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_elems), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(k_elems) * esize};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kStageKBytes / esize), static_cast<cuuint32_t>(kSlabRows)};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(tm, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
+
+int sm_count() {
+  static int n[kMaxDevices] = {0};
+  const int dev = current_device();
+  if (n[dev] == 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n[dev] = v > 0 ? v : 148;
+  }
+  return n[dev];
+}
+
+template <bool kFp8, int kEpi>
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                           int grid, cudaStream_t stream) {
+  static bool configured[kMaxDevices] = {false};   // per instantiation and device
+  const int dev = current_device();
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_kernel<kFp8, kEpi>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  fmoe_grouped_gemm_kernel<kFp8, kEpi><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
+  CUtensorMap ta, tb;
+  CUresult r = make_map(&ta, g.a, g.fp8, g.a_rows, g.k_elems);
+  if (r == CUDA_SUCCESS)
+    r = make_map(&tb, g.b, g.fp8, static_cast<int64_t>(g.num_experts) * g.b_rows_per_expert, g.k_elems);
+  if (r != CUDA_SUCCESS) {
+    if (drv_err) *drv_err = static_cast<int>(r);
+    return cudaErrorInvalidValue;
+  }
+  GemmParams p;
+  p.mblk_cum = g.mblk_cum;
+  p.num_experts = g.num_experts;
+  p.n_blocks = g.n_blocks;
+  const int k_bytes = g.k_elems * (g.fp8 ? 1 : 2);
+  p.k_iters = (k_bytes + kStageKBytes - 1) / kStageKBytes;
+  p.b_rows_per_expert = g.b_rows_per_expert;
+  p.n_stride = g.n_stride;
+  p.second_slab_offset = g.second_slab_offset;
+  p.sorted_rows = g.sorted_rows;
+  p.sorted_weights = g.sorted_weights;
+  p.a_scale = g.a_scale;
+  p.b_scale = g.b_scale;
+  p.out = g.out;
+  p.ld_out = g.ld_out;
+  p.status = g.status;
+  p.desc_template = g.desc_template_override ? g.desc_template_override : ptx::sw128_kmajor_desc_template();
+  p.idesc = g.idesc_override ? g.idesc_override : ptx::make_idesc(g.fp8 ? 0u : 1u, kBlockM, kTileN);
+  const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
+  const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
+  if (g.fp8) {
+    return g.epilogue == kEpiSiluMul ? launch_variant<true, kEpiSiluMul>(ta, tb, p, grid, stream)
+                                     : launch_variant<true, kEpiScaledSlots>(ta, tb, p, grid, stream);
+  }
+  return g.epilogue == kEpiSiluMul ? launch_variant<false, kEpiSiluMul>(ta, tb, p, grid, stream)
+                                   : launch_variant<false, kEpiScaledSlots>(ta, tb, p, grid, stream);
+}
+
+}  // namespace fmoe

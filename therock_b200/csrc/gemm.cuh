@@ -1,0 +1,300 @@
+// Expert-grouped GEMM for the fused-MoE operator on sm_100a.
+//
+// One persistent CTA per SM walks a list of (expert, n-block, m-block) tiles.  Every tile
+// is D[128 x 256] = A[128 x K] * B[256 x K]^T with
+//   A  = 128 consecutive sorted rows (one moe_sorting block, all of one expert),
+//   B  = two 128-row slabs of that expert's weight matrix (gate rows + up rows for the
+//        first GEMM, two consecutive row slabs for the second).
+// Operands arrive through TMA into a 4-stage shared-memory ring (128-byte swizzle),
+// tcgen05.mma accumulates in tensor memory (two 256-column accumulators so the epilogue of
+// tile i overlaps the main loop of tile i+1), and four epilogue warps read the accumulator
+// back with tcgen05.ld and apply the fused epilogue.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (warp w may touch TMEM lanes 32*(w%4) .. +31).
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+
+namespace fmoe {
+
+constexpr int kBlockM = 128;        // rows per tile == moe_sorting block
+constexpr int kTileN = 256;         // accumulator columns per tile
+constexpr int kSlabRows = 128;      // rows per B slab (two slabs per tile)
+constexpr int kStageKBytes = 128;   // bytes of K per pipeline stage (one swizzle row)
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kStageKBytes;            // 16 KiB
+constexpr int kBBytes = kTileN * kStageKBytes;             // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;             // 48 KiB
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kSmemMisc = 4096;
+constexpr int kGemmSmemBytes = kStages * kStageBytes + kSmemMisc + 1024;  // +1024 alignment slack
+
+enum : int { kEpiSiluMul = 1, kEpiScaledSlots = 2 };
+
+// Device status codes written to the workspace status word.
+enum : int { kStatusOk = 0, kStatusGemmTimeout = 0x100 };
+
+struct GemmParams {
+  const int* mblk_cum;          // [E+1] cumulative 128-row blocks per expert (from moe_sorting)
+  int num_experts;
+  int n_blocks;                 // tiles along N per expert
+  int k_iters;                  // ceil(K_bytes / 128)
+  int b_rows_per_expert;        // rows of the B matrix per expert
+  int n_stride;                 // first-slab row step per n-block
+  int second_slab_offset;       // row distance from the first slab to the second
+  const int* sorted_rows;       // [cap] flat (token*K + k) per sorted slot, -1 = pad
+  const float* sorted_weights;  // [cap]
+  const float* a_scale;         // [cap] per-sorted-row activation scale, or nullptr
+  const float* b_scale;         // [E * b_rows_per_expert] per-output-channel scale, or nullptr
+  void* out;                    // kEpiSiluMul: bf16 [cap, ld_out]; kEpiScaledSlots: f32 [T*K, ld_out]
+  int ld_out;                   // elements per output row
+  int* status;                  // device status word
+  uint64_t desc_template;       // shared-memory matrix descriptor without the address
+  uint32_t idesc;               // tcgen05 instruction descriptor
+};
+
+struct TileCoord {
+  int expert, m_blk, n_blk;
+};
+
+// tile -> (expert, n-block, m-block): experts in order, then n-blocks, then that expert's
+// m-blocks fastest, so CTAs running side by side share the same weight slabs through L2.
+__device__ __forceinline__ TileCoord decode_tile(int tile, const int* __restrict__ cum, int E,
+                                                 int n_blocks) {
+  int lo = 1, hi = E;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (cum[mid] * n_blocks > tile) hi = mid; else lo = mid + 1;
+  }
+  TileCoord t;
+  t.expert = lo - 1;
+  int base = cum[t.expert];
+  int cnt = cum[t.expert + 1] - base;
+  int local = tile - base * n_blocks;
+  t.n_blk = local / cnt;
+  t.m_blk = base + local % cnt;
+  return t;
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+template <bool kFp8, int kEpi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
+                         const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* misc = smem + kStages * kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);            // [kStages]
+  uint64_t* empty_bar = full_bar + kStages;                          // [kStages]
+  uint64_t* acc_full_bar = empty_bar + kStages;                      // [2]
+  uint64_t* acc_empty_bar = acc_full_bar + 2;                        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements per stage
+  constexpr int kUmmaKBytes = 32;                   // one MMA consumes 32 bytes of K per row
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&acc_full_bar[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&acc_empty_bar[b]), 128);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.mblk_cum[p.num_experts] * p.n_blocks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tm_a);
+      ptx::prefetch_tensormap(&tm_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord tc = decode_tile(tile, p.mblk_cum, p.num_experts, p.n_blocks);
+        const int a_row = tc.m_blk * kBlockM;
+        const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
+        const int b_row1 = b_row0 + p.second_slab_offset;
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&full_bar[stage]);
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+          ptx::mbar_arrive_expect_tx(full, kStageBytes);
+          const int kx = k * kElemsPerStage;
+          ptx::tma_load_2d(sa, &tm_a, full, kx, a_row);
+          ptx::tma_load_2d(sb, &tm_b, full, kx, b_row0);
+          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, kx, b_row1);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 1);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kTileN);
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint64_t da = ptx::make_smem_desc(p.desc_template, sa);
+          const uint64_t db = ptx::make_smem_desc(p.desc_template, sa + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
+            // advancing K inside the swizzle row = advancing the start address
+            const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
+            const uint32_t accum = (k | kk) ? 1u : 0u;
+            if (kFp8) ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, accum);
+            else      ptx::umma_f16(d_tmem, da + adv, db + adv, p.idesc, accum);
+          }
+          ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));   // frees the stage when MMAs finish
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit(ptx::smem_u32(&acc_full_bar[acc]));    // accumulator ready
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 2);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int epi_tid = threadIdx.x - 64;            // 0..127
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const TileCoord tc = decode_tile(tile, p.mblk_cum, p.num_experts, p.n_blocks);
+      const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
+      // Per-output-channel scales of this tile's two slabs (same addresses for the whole
+      // warp, so these are broadcast loads served by L1).
+      const float* bs0 = p.b_scale ? p.b_scale + b_row0 : nullptr;
+      const float* bs1 = p.b_scale ? bs0 + p.second_slab_offset : nullptr;
+      const int slot = tc.m_blk * kBlockM + quad * 32 + lane;   // sorted slot of this thread's row
+      const float a_s = p.a_scale ? p.a_scale[slot] : 1.0f;
+      if (!ptx::mbar_wait(ptx::smem_u32(&acc_full_bar[acc]), acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(acc * kTileN);
+      if (kEpi == kEpiSiluMul) {
+        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) +
+                              static_cast<size_t>(slot) * p.ld_out + tc.n_blk * kSlabRows;
+#pragma unroll 1
+        for (int c = 0; c < kSlabRows / 32; ++c) {
+          uint32_t g[32], u[32];
+          ptx::tmem_ld_32x32(t_row + c * 32, g);
+          ptx::tmem_ld_32x32(t_row + kSlabRows + c * 32, u);
+          ptx::tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float g0 = __uint_as_float(g[j]), g1 = __uint_as_float(g[j + 1]);
+            float u0 = __uint_as_float(u[j]), u1 = __uint_as_float(u[j + 1]);
+            if (p.b_scale != nullptr) {
+              const float2 sg = __ldg(reinterpret_cast<const float2*>(bs0 + c * 32 + j));
+              const float2 su = __ldg(reinterpret_cast<const float2*>(bs1 + c * 32 + j));
+              g0 = (g0 * a_s) * sg.x;
+              g1 = (g1 * a_s) * sg.y;
+              u0 = (u0 * a_s) * su.x;
+              u1 = (u1 * a_s) * su.y;
+            }
+            __nv_bfloat162 v = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
+            packed[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      } else {
+        const int row = p.sorted_rows[slot];
+        const float w = p.sorted_weights[slot];
+        float* orow = reinterpret_cast<float*>(p.out) +
+                      static_cast<size_t>(row < 0 ? 0 : row) * p.ld_out + tc.n_blk * kTileN;
+#pragma unroll 1
+        for (int c = 0; c < kTileN / 32; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(t_row + c * 32, v);
+          ptx::tmem_ld_wait();
+          if (row >= 0) {
+            float4* dst = reinterpret_cast<float4*>(orow + c * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float f[4];
+              float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+              // second GEMM: the tile's 256 columns are 256 consecutive output channels
+              if (p.b_scale != nullptr) sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+              const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float x = __uint_as_float(v[4 * q + j]);
+                if (p.b_scale != nullptr) x = (x * a_s) * scv[j];
+                f[j] = w * x;
+              }
+              dst[q] = make_float4(f[0], f[1], f[2], f[3]);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(ptx::smem_u32(&acc_empty_bar[acc]));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!ok && epi_tid == 0) atomicExch(p.status, kStatusGemmTimeout | 3);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fmoe

@@ -1,0 +1,56 @@
+// Launchers shared between the translation units of libfmoe_b200.so (not part of the ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fmoe {
+
+// moe_sorting.  All outputs are device pointers; sorted_rows, mblk_cum and status_to_clear
+// (a status word the kernel resets to 0) may be null.
+cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight, int T, int K,
+                               int E, int block_m, int64_t cap, int32_t* sorted_token_ids,
+                               float* sorted_weights, int32_t* sorted_rows,
+                               int32_t* sorted_expert_ids, int32_t* num_post_pad,
+                               int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream);
+
+// Gather rows of a bf16 matrix into sorted order, optionally quantising each row to e4m3.
+//   src [n_src, cols] bf16; row_ids [cap] (entry >= n_src means pad -> zero row) or null
+//   for identity; only slots < *num_post_pad are touched.
+//   quant 0: dst bf16 [cap, cols].  quant 1: dst e4m3 [cap, cols] + scales[cap] (one per
+//   row).  quant 2: dst e4m3 + scales [cap, cols/128] (one per 128 columns).
+cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
+                               const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
+                               float* scales, cudaStream_t stream);
+
+// out[t, :] = bf16( sum_k slots[t*K + k, :] ) over the k whose expert id lies in [0, E).
+cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
+                           int H, void* out, cudaStream_t stream);
+
+struct GemmLaunch {
+  bool fp8;
+  int epilogue;                 // kEpiSiluMul / kEpiScaledSlots
+  const void* a;                // [a_rows, k_elems] row-major
+  int64_t a_rows;
+  const void* b;                // [E * b_rows_per_expert, k_elems] row-major
+  int k_elems;
+  int num_experts;
+  int b_rows_per_expert;
+  int n_blocks, n_stride, second_slab_offset;
+  const int32_t* mblk_cum;
+  const int32_t* sorted_rows;
+  const float* sorted_weights;
+  const float* a_scale;
+  const float* b_scale;
+  void* out;
+  int ld_out;
+  int32_t* status;
+  int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
+  uint64_t desc_template_override;  // 0 = the library's descriptor encoding (diagnostics only)
+  uint32_t idesc_override;          // 0 = the library's instruction descriptor
+};
+// Returns cudaSuccess or the failing CUDA error; *drv_err receives a CUresult when the
+// tensor-map encode fails.
+cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err);
+
+}  // namespace fmoe

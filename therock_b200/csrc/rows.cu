@@ -1,0 +1,162 @@
+// Row-wise helper kernels of the fused-MoE operator (all HBM-bound, 16-byte vector access):
+//   gather_rows  : activations -> sorted order (the A operand of the grouped GEMMs), with
+//                  optional dynamic e4m3 quantisation per row or per 128-column group;
+//                  the same kernel with identity indices quantises the intermediate.
+//   combine      : out[t] = bf16( sum over k, ascending, of the weighted expert outputs ).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "internal.h"
+
+namespace fmoe {
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = bf16_bits_to_f32(w[i] & 0xffffu);
+    f[2 * i + 1] = bf16_bits_to_f32(w[i] >> 16);
+  }
+}
+
+__device__ __forceinline__ uint32_t e4m3_byte(float x) {
+  return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+
+// quantise 8 floats with one scale into 8 bytes
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float scale) {
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    lo |= e4m3_byte(f[i] / scale) << (8 * i);
+    hi |= e4m3_byte(f[4 + i] / scale) << (8 * i);
+  }
+  return make_uint2(lo, hi);
+}
+
+// One CTA per sorted slot.
+template <int kQuant>
+__global__ void __launch_bounds__(kRowThreads)
+gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
+                   const int32_t* __restrict__ row_ids, const int32_t* __restrict__ num_post_pad,
+                   void* __restrict__ dst, float* __restrict__ scales) {
+  const int slot = blockIdx.x;
+  if (slot >= *num_post_pad) return;
+  const int row = row_ids ? row_ids[slot] : slot;
+  const int nvec = cols >> 3;                       // 8 bf16 per 16-byte vector
+  const bool pad = row < 0 || row >= n_src;
+  const uint4* s = src + static_cast<size_t>(pad ? 0 : row) * nvec;
+
+  if (kQuant == 0) {
+    uint4* d = reinterpret_cast<uint4*>(dst) + static_cast<size_t>(slot) * nvec;
+    for (int i = threadIdx.x; i < nvec; i += kRowThreads)
+      d[i] = pad ? make_uint4(0, 0, 0, 0) : s[i];
+    return;
+  }
+
+  uint2* d = reinterpret_cast<uint2*>(dst) + static_cast<size_t>(slot) * nvec;
+  if (kQuant == 1) {
+    // per-row scale: block-wide absmax, then a second pass (the row is L1/L2 resident)
+    __shared__ float warp_max[kRowThreads / 32];
+    __shared__ float row_scale;
+    float amax = 0.0f;
+    if (!pad) {
+      for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+        float f[8];
+        unpack8(s[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kRowThreads / 32; ++w) m = fmaxf(m, warp_max[w]);
+      const float sc = m > 0.0f ? m / 448.0f : 1.0f;
+      row_scale = sc;
+      scales[slot] = sc;
+    }
+    __syncthreads();
+    const float sc = row_scale;
+    for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+      if (pad) { d[i] = make_uint2(0, 0); continue; }
+      float f[8];
+      unpack8(s[i], f);
+      d[i] = quant8(f, sc);
+    }
+  } else {
+    // one scale per 128 columns = 16 vectors = a 16-lane group
+    const int ngroups = cols >> 7;
+    for (int base = 0; base < nvec; base += kRowThreads) {    // warp-uniform trip count
+      const int i = base + threadIdx.x;
+      const bool live = i < nvec;                             // nvec is a multiple of 16
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (live && !pad) unpack8(s[i], f);
+      float amax = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+      const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
+      if (!live) continue;
+      if ((i & 15) == 0) scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
+      d[i] = quant8(f, sc);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRowThreads)
+combine_kernel(const float4* __restrict__ slots, const int32_t* __restrict__ topk_ids, int K, int E,
+               int H, uint2* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int nvec = H >> 2;
+  for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < K; ++k) {
+      const int e = topk_ids[t * K + k];
+      if (e < 0 || e >= E) continue;
+      const float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+    out[static_cast<size_t>(t) * nvec + i] =
+        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
+                               const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
+                               float* scales, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>(cap));
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  if (quant == 0)
+    gather_rows_kernel<0><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales);
+  else if (quant == 1)
+    gather_rows_kernel<1><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales);
+  else
+    gather_rows_kernel<2><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
+                           int H, void* out, cudaStream_t stream) {
+  combine_kernel<<<T, kRowThreads, 0, stream>>>(reinterpret_cast<const float4*>(slots), topk_ids, K,
+                                                E, H, reinterpret_cast<uint2*>(out));
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

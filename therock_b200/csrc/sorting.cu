@@ -1,0 +1,136 @@
+// moe_sorting for sm_100a: stable bucketing of the T*K routed (token, k) pairs by expert,
+// every bucket padded to a multiple of block_m.
+//
+// One CTA of 32 warps.  The flat pair range is cut into 32 contiguous chunks, one per
+// warp, so the stable order inside an expert is (chunk, position in chunk).  Pass 1 counts
+// per (warp, expert) with __match_any_sync groups; a warp-shuffle prefix sum over the
+// experts turns the counts into padded bucket offsets; pass 2 re-walks the chunks and
+// places every pair at  offset[e] + (pairs of e in earlier chunks) + (rank inside the
+// 32-wide group, from the match mask).  All arithmetic is integer: the result is
+// bit-exact by construction.
+#include "internal.h"
+
+namespace fmoe {
+namespace {
+
+constexpr int kSortThreads = 1024;
+constexpr int kSortWarps = kSortThreads / 32;
+
+__global__ void __launch_bounds__(kSortThreads, 1)
+moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_weight,
+                   int T, int K, int E, int block_m, int cap,
+                   int32_t* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights,
+                   int32_t* __restrict__ sorted_rows, int32_t* __restrict__ sorted_expert_ids,
+                   int32_t* __restrict__ num_post_pad, int32_t* __restrict__ mblk_cum,
+                   int32_t* __restrict__ status_to_clear) {
+  extern __shared__ int32_t sm[];
+  int32_t* cnt = sm;                      // [kSortWarps][E] counts, later running offsets
+  int32_t* blk_cum = sm + kSortWarps * E; // [E + 1] cumulative padded blocks
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int R = T * K;
+  // chunk length: multiple of 32 so every warp iterates over whole 32-wide groups
+  const int chunk = ((R + kSortWarps - 1) / kSortWarps + 31) & ~31;
+  const int r_begin = warp * chunk;
+  const int r_end = min(R, r_begin + chunk);
+
+  for (int i = tid; i < kSortWarps * E; i += kSortThreads) cnt[i] = 0;
+  for (int i = tid; i < cap; i += kSortThreads) {
+    sorted_token_ids[i] = T;
+    if (sorted_weights) sorted_weights[i] = 0.0f;
+    if (sorted_rows) sorted_rows[i] = -1;
+  }
+  if (sorted_expert_ids)
+    for (int i = tid; i < cap / block_m; i += kSortThreads) sorted_expert_ids[i] = -1;
+  __syncthreads();
+
+  // pass 1: per-(warp, expert) histogram
+  int32_t* my_cnt = cnt + warp * E;
+  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+    const int r = r0 + lane;
+    int e = (r < r_end) ? topk_ids[r] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned mask = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
+    __syncwarp();
+  }
+  __syncthreads();
+
+  // per expert: total, and counts -> exclusive prefix over warps
+  for (int e = tid; e < E; e += kSortThreads) {
+    int run = 0;
+    for (int w = 0; w < kSortWarps; ++w) {
+      const int c = cnt[w * E + e];
+      cnt[w * E + e] = run;
+      run += c;
+    }
+    blk_cum[e + 1] = (run + block_m - 1) / block_m;   // padded blocks of expert e
+  }
+  if (tid == 0) blk_cum[0] = 0;
+  __syncthreads();
+
+  // inclusive prefix sum of the block counts over experts: warp 0, 32 experts per step
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 1; base <= E; base += 32) {
+      const int idx = base + lane;
+      int v = (idx <= E) ? blk_cum[idx] : 0;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, off);
+        if (lane >= off) v += n;
+      }
+      v += carry;
+      if (idx <= E) blk_cum[idx] = v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+
+  for (int e = tid; e <= E; e += kSortThreads) {
+    if (mblk_cum) mblk_cum[e] = blk_cum[e];
+    if (e < E && sorted_expert_ids)
+      for (int b = blk_cum[e]; b < blk_cum[e + 1]; ++b) sorted_expert_ids[b] = e;
+  }
+  if (tid == 0 && num_post_pad) num_post_pad[0] = blk_cum[E] * block_m;
+  if (tid == 0 && status_to_clear) status_to_clear[0] = 0;
+
+  // pass 2: placement
+  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+    const int r = r0 + lane;
+    int e = (r < r_end) ? topk_ids[r] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned mask = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int rank = __popc(mask & ((1u << lane) - 1u));
+      const int pos = blk_cum[e] * block_m + my_cnt[e] + rank;
+      sorted_token_ids[pos] = r / K;
+      if (sorted_weights) sorted_weights[pos] = topk_weight[r];
+      if (sorted_rows) sorted_rows[pos] = r;
+    }
+    __syncwarp();
+    if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
+    __syncwarp();
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight, int T, int K,
+                               int E, int block_m, int64_t cap, int32_t* sorted_token_ids,
+                               float* sorted_weights, int32_t* sorted_rows,
+                               int32_t* sorted_expert_ids, int32_t* num_post_pad,
+                               int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream) {
+  const size_t smem = (static_cast<size_t>(kSortWarps) * E + E + 1) * sizeof(int32_t);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_sorting_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  moe_sorting_kernel<<<1, kSortThreads, smem, stream>>>(
+      topk_ids, topk_weight, T, K, E, block_m, static_cast<int>(cap), sorted_token_ids,
+      sorted_weights, sorted_rows, sorted_expert_ids, num_post_pad, mblk_cum, status_to_clear);
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe
