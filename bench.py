@@ -1,0 +1,436 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-MoE hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--config C1] [--impl reference]
+
+A "step" is one pass of the fused operator (moe_sorting -> gemm1+SiLU*up -> gemm2 -> combine)
+over one batch of synthetic tokens.  At N=1 the workload is the Mixtral-8x7B-shape bf16
+prefill configuration (tokens=4096, hidden=4096, intermediate=14336, experts=8, topk=2).
+For N>1 the same global batch is split expert-parallel: tokens data-parallel, experts
+sharded, NCCL all-to-all dispatch and return around the local operator ("strong" scaling).
+
+One JSON line is printed by rank 0.  `value` is TFLOP/s with inputs resident in HBM, `e2e`
+the same metric with host buffers (pinned H2D of activations and routing, D2H of the
+output, every step), `roofline` the dominant kernel (gate+up GEMM) against the measured
+dense bf16 peak, `cpu_baseline` the CPU oracle timed on a bounded token sample.
+
+`--impl reference` times the CPU implementation of the same path (the repository's CPU
+restatement: the reference project ships no source for this operator) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: (T, H, I, E, K, quant)
+    "C0": dict(T=128, H=512, I=1024, E=8, K=2, quant=0, label="cpu-ref-shape-bf16"),
+    "C1": dict(T=4096, H=4096, I=14336, E=8, K=2, quant=0, label="mixtral-8x7b-prefill-bf16"),
+    "C2": dict(T=8192, H=4096, I=14336, E=8, K=2, quant=1, label="mixtral-8x7b-prefill-fp8"),
+    "C3": dict(T=16, H=4096, I=14336, E=8, K=2, quant=1, label="mixtral-8x7b-decode-fp8"),
+}
+QUANT_NAME = {0: "none", 1: "token_channel"}
+
+# DRAM bytes (read + write) of one gate+up GEMM launch on the benchmark workload, from the
+# ncu capture summarised under profiles/ (null until a capture has been taken).
+GEMM1_DRAM_TRAFFIC_BYTES = {"C1": None, "C2": None, "C3": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_burst=d["bf16_tflops"],
+                    bf16_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.t = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [r for r in self.rows if t0 <= r[0] <= t1] or self.rows
+        for _, line in rows:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def flops_per_step(c) -> float:
+    return 6.0 * c["T"] * c["K"] * c["H"] * c["I"]
+
+
+# ------------------------------------------------------------------------------ CPU arm
+
+def make_host_inputs(c, seed=0):
+    """Synthetic inputs on the host: activations N(0,1), weights N(0,0.02), softmax top-K."""
+    import torch
+    from oracle import oracle as O
+    T, H, I, E, K, quant = c["T"], c["H"], c["I"], c["E"], c["K"], c["quant"]
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=dev).cpu().numpy()
+    ids, w = O.route(logits, K, "softmax")
+
+    def weights(rows, cols):
+        out_q, out_s = [], []
+        for _ in range(E):
+            wf = torch.randn(rows, cols, generator=g, device=dev) * 0.02
+            if quant == 0:
+                out_q.append(wf.to(torch.bfloat16).view(torch.int16).cpu())
+            else:
+                s = wf.abs().amax(dim=1) / 448.0
+                out_q.append((wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).cpu())
+                out_s.append(s.cpu())
+        q = torch.stack(out_q).numpy()
+        return (q.view(np.uint16) if quant == 0 else q), (torch.stack(out_s).numpy() if out_s else None)
+
+    w1, s1 = weights(2 * I, H)
+    w2, s2 = weights(H, I)
+    return dict(x=x.view(torch.int16).cpu().numpy().view(np.uint16), w1=w1, w2=w2, w1_scale=s1, w2_scale=s2,
+                topk_ids=ids, topk_w=w, quant=quant)
+
+
+def cpu_time_tokens(d, sel, threads=0):
+    from oracle import oracle as O
+    t0 = time.perf_counter()
+    O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], d["quant"], d["w1_scale"], d["w2_scale"],
+                sel=sel, n_threads=threads)
+    return time.perf_counter() - t0
+
+
+def cpu_sample_size(d, c, budget_s: float, n_calls: int) -> int:
+    """Tokens per timed call so that n_calls calls take about budget_s."""
+    from oracle import oracle as O
+    probe = np.arange(min(O.max_threads(), c["T"]), dtype=np.int32)
+    t = max(cpu_time_tokens(d, probe), 1e-4)
+    per_token = t / len(probe)
+    n = int(budget_s / max(n_calls, 1) / per_token)
+    n = max(len(probe), min(c["T"], n))
+    return n
+
+
+def run_reference(a, c):
+    """CPU implementation of the path on the host cores, a bounded token sample per step."""
+    from oracle import oracle as O
+    O.build()
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    d = make_host_inputs(c)
+    cores = O.max_threads()
+    n = cpu_sample_size(d, c, budget_s=90.0, n_calls=a.steps + a.warmup)
+    rng = np.random.default_rng(0)
+    for _ in range(a.warmup):
+        cpu_time_tokens(d, rng.choice(c["T"], n, replace=False).astype(np.int32))
+    t = 0.0
+    for _ in range(a.steps):
+        t += cpu_time_tokens(d, rng.choice(c["T"], n, replace=False).astype(np.int32))
+    fl = 6.0 * n * c["K"] * c["H"] * c["I"] * a.steps
+    val = fl / t / 1e12
+    sample = f"{n} of {c['T']} tokens per step (full weights, all {c['E']} experts), {a.steps} steps"
+    line = {"impl": "reference", "metric": "fused_moe_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": a.gpus,
+            "steps": a.steps, "warmup": a.warmup, "ms_per_step": t / a.steps * 1e3 * (c["T"] / n),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype_name(c),
+            "data": "synthetic", "config": workload_config(c, a.gpus),
+            "tokens_per_s": n * a.steps / t,
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of the operator (the reference project ships no source for it); "
+                    "ms_per_step is the sample time scaled to the full batch"}
+    print(json.dumps(line), flush=True)
+
+
+def dtype_name(c):
+    return "bf16" if c["quant"] == 0 else "fp8_e4m3"
+
+
+def workload_config(c, gpus):
+    return {"workload": c["label"], "tokens": c["T"], "hidden": c["H"], "intermediate": c["I"],
+            "experts": c["E"], "topk": c["K"], "quant": QUANT_NAME[c["quant"]],
+            "parallelism": "single" if gpus == 1 else f"ep{gpus}",
+            "l2_policy": "weights (GBs) stream from HBM every step: inputs larger than L2, no flush"}
+
+
+# ------------------------------------------------------------------------------ GPU arm
+
+def device_inputs(c, dev, rank=0, world=1, seed=0):
+    """Synthetic inputs generated on the device.  Weights are drawn per expert from a
+    generator seeded by (seed, expert), so every rank of an expert-parallel run holds exactly
+    the experts a single-GPU run would."""
+    import torch
+    T, H, I, E, K, quant = c["T"], c["H"], c["I"], c["E"], c["K"], c["quant"]
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=dev)
+    p = torch.softmax(logits, dim=-1)
+    w, ids = torch.topk(p, K, dim=-1)
+    w = (w / w.sum(dim=-1, keepdim=True)).float().contiguous()
+    ids = ids.to(torch.int32).contiguous()
+    e_local = E // world
+    w1s, w2s, s1s, s2s = [], [], [], []
+    for e in range(rank * e_local, (rank + 1) * e_local):
+        ge = torch.Generator(device=dev)
+        ge.manual_seed(seed * 1000003 + 17 + e)
+        for rows, cols, wl, sl in ((2 * I, H, w1s, s1s), (H, I, w2s, s2s)):
+            wf = torch.randn(rows, cols, generator=ge, device=dev) * 0.02
+            if quant == 0:
+                wl.append(wf.to(torch.bfloat16))
+            else:
+                s = wf.abs().amax(dim=1) / 448.0
+                wl.append((wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8))
+                sl.append(s)
+            del wf
+    w1, w2 = torch.stack(w1s), torch.stack(w2s)
+    s1 = torch.stack(s1s).contiguous() if s1s else None
+    s2 = torch.stack(s2s).contiguous() if s2s else None
+    t_local = T // world
+    sl = slice(rank * t_local, (rank + 1) * t_local)
+    return dict(x=x[sl].contiguous(), ids=ids[sl].contiguous(), w=w[sl].contiguous(), w1=w1, w2=w2, s1=s1, s2=s2,
+                x_full=x, ids_full=ids, w_full=w)
+
+
+def run_gpu(a, c):
+    import torch
+    import torch.distributed as dist
+    import therock_b200 as M
+    from therock_b200 import api, ep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != a.gpus:
+        if world == 1 and a.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if c["E"] % world or c["T"] % world:
+        raise SystemExit("experts and tokens must divide over the ranks")
+
+    M.lib()  # fails loudly when the CUDA library has not been built
+    traits = M.FusedMoeTraits(prec_w="bf16" if c["quant"] == 0 else "fp8", quant=QUANT_NAME[c["quant"]])
+    d = device_inputs(c, dev, rank, world)
+    T_local, H = d["x"].shape
+
+    if world == 1:
+        args = M.FusedMoeArgs(a=d["x"], g=d["w1"], d=d["w2"], topk_ids=d["ids"], topk_weight=d["w"],
+                              g_scale=d["s1"], d_scale=d["s2"])
+        args.o = torch.empty_like(d["x"])
+        args.workspace = torch.empty(M.fused_moe_workspace_size(traits, args), dtype=torch.uint8, device=dev)
+
+        def step():
+            return M.fused_moe(traits, args)
+        launches_per_step = M.launches_per_run(traits)
+    else:
+        local = ep.make_local_moe(traits, d["w1"], d["w2"], d["s1"], d["s2"])
+        moe = ep.ExpertParallelMoE(c["E"], world, rank, local)
+
+        def step():
+            return moe.forward(d["x"], d["ids"], d["w"])
+        launches_per_step = M.launches_per_run(traits) + 2     # + pack and combine kernels
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        t1 = time.time()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), t0, t1
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for _ in range(max(a.warmup, 3)):
+        step()
+    ms_total, t0, t1 = timed(step, a.steps)
+    clocks = sampler.summary(t0, t1) if sampler else None
+
+    # per-kernel durations over the same number of steps (single GPU: events between kernels)
+    stage = None
+    if world == 1:
+        prof = api.StageProfile(a.steps)
+        barrier()
+        for _ in range(a.steps):
+            prof.run(traits, args)
+        stage = prof.read()
+        prof.close()
+        assert api.check_status(args.workspace) == 0
+
+    # end to end: host buffers in, host buffer out, every step
+    x_h = d["x"].cpu().pin_memory()
+    ids_h = d["ids"].cpu().pin_memory()
+    w_h = d["w"].cpu().pin_memory()
+    out_h = torch.empty(T_local, H, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        d["x"].copy_(x_h, non_blocking=True)
+        d["ids"].copy_(ids_h, non_blocking=True)
+        d["w"].copy_(w_h, non_blocking=True)
+        out = step()
+        out_h.copy_(out, non_blocking=True)
+    n_e2e = max(3, min(a.steps, 100))
+    for _ in range(3):
+        e2e_step()
+    ms_e2e, _, _ = timed(e2e_step, n_e2e)
+    if sampler:
+        sampler.stop()
+
+    fl = flops_per_step(c)
+    ms_step = ms_total / a.steps
+    value = fl / ms_step / 1e9
+    e2e_val = fl / (ms_e2e / n_e2e) / 1e9
+    h2d = (x_h.numel() * 2 + ids_h.numel() * 4 + w_h.numel() * 4) * world
+    d2h = out_h.numel() * 2 * world
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    line = {"metric": "fused_moe_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": a.gpus, "steps": a.steps,
+            "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": dtype_name(c), "data": "synthetic", "config": workload_config(c, a.gpus),
+            "tokens_per_s": c["T"] / (ms_step * 1e-3),
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / n_e2e, "steps": n_e2e},
+            "gpu_launches": launches_per_step * a.steps, "clocks": clocks}
+    if stage is not None:
+        runs = max(stage["runs"], 1)
+        per = {k: stage[k] / runs for k in api.STAGES}
+        g1_ms = per["gemm1"]
+        if c["T"] <= 64:
+            # decode: weight streaming bounds the step; report the gate+up GEMM against HBM
+            wbytes = c["E"] * 2 * c["I"] * c["H"] * (2 if c["quant"] == 0 else 1)
+            achieved = wbytes / (g1_ms * 1e-3) / 1e9
+            peak, unit, bound = peaks["hbm_gbs"], "GB/s", "hbm"
+            peak_kind = peaks["source"] + " copy bandwidth"
+        else:
+            achieved = 4.0 * c["T"] * c["K"] * c["H"] * c["I"] / (g1_ms * 1e-3) / 1e12
+            long_loop = ms_total > 1000.0
+            peak = peaks["bf16_sustained"] if long_loop else peaks["bf16_burst"]
+            peak_kind = f"{peaks['source']} cuBLAS bf16, {'sustained' if long_loop else 'burst'}"
+            if c["quant"] != 0:
+                peak *= 2.0
+                peak_kind += " x2 (no fp8 peak was measured)"
+            unit, bound = "TFLOP/s", "tensor"
+        line["roofline"] = {"bound": bound, "kernel": "fmoe_grouped_gemm_kernel (gate+up, SiLU*up epilogue)",
+                            "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                            "traffic": GEMM1_DRAM_TRAFFIC_BYTES.get(a.config), "peak_kind": peak_kind,
+                            "ms_per_launch": g1_ms}
+        line["stage_ms"] = per
+
+    if world == 1:
+        # CPU baseline: the oracle on a bounded token sample of the same workload
+        from oracle import oracle as O
+        O.build()
+        hd = dict(x=d["x_full"].view(torch.int16).cpu().numpy().view(np.uint16),
+                  w1=(d["w1"].view(torch.int16) if c["quant"] == 0 else d["w1"]).cpu().numpy(),
+                  w2=(d["w2"].view(torch.int16) if c["quant"] == 0 else d["w2"]).cpu().numpy(),
+                  w1_scale=None if d["s1"] is None else d["s1"].cpu().numpy(),
+                  w2_scale=None if d["s2"] is None else d["s2"].cpu().numpy(),
+                  topk_ids=d["ids_full"].cpu().numpy(), topk_w=d["w_full"].cpu().numpy(), quant=c["quant"])
+        if c["quant"] == 0:
+            hd["w1"], hd["w2"] = hd["w1"].view(np.uint16), hd["w2"].view(np.uint16)
+        n = cpu_sample_size(hd, c, budget_s=15.0, n_calls=1)
+        sel = np.random.default_rng(0).choice(c["T"], n, replace=False).astype(np.int32)
+        t = cpu_time_tokens(hd, sel)
+        line["cpu_baseline"] = {"value": 6.0 * n * c["K"] * c["H"] * c["I"] / t / 1e12, "unit": "TFLOP/s",
+                                "cores": O.max_threads(), "kind": "port",
+                                "sample": f"{n} of {c['T']} tokens, full weights, one pass ({t:.1f} s)"}
+        # parity spot check of the benchmarked run against the same oracle call
+        ref = O.fused_moe(hd["x"], hd["w1"], hd["w2"], hd["topk_ids"], hd["topk_w"], c["quant"], hd["w1_scale"],
+                          hd["w2_scale"], sel=sel[:8])
+        got = step().view(torch.int16).cpu().numpy().view(np.uint16)[sel[:8]]
+        gf, rf = O.bf16_to_f32(got), O.bf16_to_f32(ref)
+        line["parity_rel_l2"] = float(np.linalg.norm(gf - rf) / max(np.linalg.norm(rf), 1e-30))
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="C1", choices=sorted(CONFIGS))
+    a = ap.parse_args()
+    c = CONFIGS[a.config]
+    if a.impl == "reference":
+        run_reference(a, c)
+    else:
+        run_gpu(a, c)
+
+
+if __name__ == "__main__":
+    main()

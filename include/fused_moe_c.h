@@ -139,6 +139,32 @@ FMOE_API int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void
  * 0 = clean, otherwise the code a kernel stored when a bounded wait ran out. */
 FMOE_API int fmoe_check_status(const void* workspace, void* stream, int32_t* status_out);
 
+/* Per-stage timing without synchronising inside the timed loop.  fmoe_profile_create
+ * makes a handle holding events for up to max_runs runs; fmoe_run_profiled is fmoe_run
+ * plus one event record between consecutive kernels; fmoe_profile_read waits for the
+ * recorded runs, adds up the milliseconds of each of the six stages (sort, gather(+quant),
+ * gemm1, quant of the intermediate, gemm2, combine) into stage_ms[6], stores the number of
+ * runs and empties the handle.  No counterpart in ck_tile (its host API times the whole
+ * call only). */
+FMOE_API int fmoe_profile_create(int32_t max_runs, void** handle);
+FMOE_API int fmoe_run_profiled(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream,
+                               void* handle);
+FMOE_API int fmoe_profile_read(void* handle, float* stage_ms, int32_t* runs);
+FMOE_API int fmoe_profile_destroy(void* handle);
+
+/* Expert-parallel pack: dst[i, :] = src[row_ids[i], :] for i < *n_rows_dev (a device
+ * int32, <= n_rows); bf16 rows of `cols` elements; ids outside [0, n_src) give zero rows.
+ * Used to lay token rows out per destination rank before the all-to-all dispatch.  The
+ * reference operator is single-GPU (no counterpart); expert parallelism is added here. */
+FMOE_API int fmoe_gather_rows(const void* src, int32_t n_src, int32_t cols, const int32_t* row_ids,
+                              int32_t n_rows, const int32_t* n_rows_dev, void* dst, void* stream);
+
+/* Expert-parallel combine: out[t, :] = bf16( sum over k ascending of rows[index[t*K+k], :] )
+ * with f32 accumulation; index < 0 skips the term.  rows are the bf16 partial results that
+ * came back through the all-to-all.  No counterpart in the single-GPU reference. */
+FMOE_API int fmoe_combine_rows(const void* rows, const int32_t* index, int32_t T, int32_t K,
+                               int32_t H, void* out, void* stream);
+
 /* Number of kernels one fmoe_run launches for these traits (for launch accounting). */
 FMOE_API int fmoe_launches_per_run(const fmoe_traits_c* traits);
 

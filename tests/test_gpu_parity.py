@@ -1,0 +1,229 @@
+"""GPU parity tests: the CUDA path, called through the C-ABI, against the CPU oracle.
+
+Tolerances (from the task statement): moe_sorting bit-exact; bf16 rtol = atol = 1e-2;
+fp8 relative L2 <= 4e-2."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+import therock_b200 as M
+from therock_b200 import api
+from tests.util import (args_for, bf16_dev, out_bits, rel_l2, run_gpu, run_oracle, to_dev, traits_for)
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+BF16_TOL = dict(rtol=1e-2, atol=1e-2)
+FP8_REL_L2 = 4e-2
+
+
+def check(d, got, ref):
+    g, r = O.bf16_to_f32(got), O.bf16_to_f32(ref)
+    assert not np.isnan(g).any()
+    if d["quant"] == 0:
+        np.testing.assert_allclose(g, r, **BF16_TOL)
+    assert rel_l2(got, ref) <= (2e-3 if d["quant"] == 0 else FP8_REL_L2)
+
+
+# ------------------------------------------------------------------------------ moe_sorting
+
+SORT_CASES = [(128, 2, 8, "softmax"), (4096, 2, 8, "softmax"), (8192, 2, 8, "softmax"), (16, 2, 8, "softmax"),
+              (8192, 8, 256, "sigmoid"), (1, 1, 1, "softmax"), (3, 5, 5, "softmax"), (777, 3, 17, "softmax"),
+              (33, 1, 300, "sigmoid")]
+
+
+@pytest.mark.parametrize("T,K,E,mode", SORT_CASES)
+def test_moe_sorting_bit_exact(T, K, E, mode):
+    ids, w = O.route(O.normal((T, E), 0, 4), K, mode)
+    if T >= 100:
+        ids[::7, 0] = -1
+        ids[::11, K - 1] = E + 3
+    ref = O.moe_sorting(ids, w, E, 128)
+    got = M.moe_sorting(to_dev(ids), to_dev(w), E, 128)
+    torch.cuda.synchronize()
+    assert (got[0].cpu().numpy() == ref["sorted_token_ids"]).all()
+    assert (got[1].cpu().numpy().view(np.uint32) == ref["sorted_weights"].view(np.uint32)).all()
+    assert (got[2].cpu().numpy() == ref["sorted_expert_ids"]).all()
+    assert int(got[3].item()) == int(ref["num_tokens_post_pad"][0])
+
+
+@pytest.mark.parametrize("bm", [1, 16, 32, 64, 256])
+def test_moe_sorting_other_block_sizes(bm):
+    ids, w = O.route(O.normal((500, 12), 1, 4), 3, "softmax")
+    ref = O.moe_sorting(ids, w, 12, bm)
+    got = M.moe_sorting(to_dev(ids), to_dev(w), 12, bm)
+    torch.cuda.synchronize()
+    assert (got[0].cpu().numpy() == ref["sorted_token_ids"]).all()
+    assert (got[2].cpu().numpy() == ref["sorted_expert_ids"]).all()
+    assert int(got[3].item()) == int(ref["num_tokens_post_pad"][0])
+
+
+def test_moe_sorting_skewed_and_all_one_expert():
+    T, K, E = 2000, 2, 8
+    ids = np.zeros((T, K), np.int32)
+    ids[:, 1] = 5                                   # only experts 0 and 5 are hit
+    w = np.full((T, K), 0.5, np.float32)
+    ref = O.moe_sorting(ids, w, E, 128)
+    got = M.moe_sorting(to_dev(ids), to_dev(w), E, 128)
+    torch.cuda.synchronize()
+    assert (got[0].cpu().numpy() == ref["sorted_token_ids"]).all()
+    assert (got[2].cpu().numpy() == ref["sorted_expert_ids"]).all()
+
+
+def test_sort_stage_inside_fused_moe_is_bit_exact():
+    d = O.make_inputs(**O.CONFIGS["C0"])
+    _, args = run_gpu(d)
+    lay = M.workspace_layout(traits_for(0), args)
+    ref = O.moe_sorting(d["topk_ids"], d["topk_w"], 8, 128)
+    ws = args.workspace
+    cap = lay["capacity"]
+
+    def region(name, n, dt):
+        return ws[lay[name]:lay[name] + 4 * n].view(dt).cpu().numpy()
+    assert (region("sorted_token_ids", cap, torch.int32) == ref["sorted_token_ids"]).all()
+    assert (region("sorted_rows", cap, torch.int32) == ref["sorted_rows"]).all()
+    assert (region("sorted_weights", cap, torch.int32) == ref["sorted_weights"].view(np.int32)).all()
+    assert (region("sorted_expert_ids", cap // 128, torch.int32) == ref["sorted_expert_ids"]).all()
+    assert (region("mblk_cum", 9, torch.int32) == ref["mblk_cum"]).all()
+    assert int(region("meta", 2, torch.int32)[0]) == int(ref["num_tokens_post_pad"][0])
+
+
+# ------------------------------------------------------------------------------ fused MoE
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_c0_matches_oracle_and_golden(quant):
+    d = O.make_inputs(**{**O.CONFIGS["C0"], "quant": quant})
+    got, _ = run_gpu(d)
+    check(d, got, run_oracle(d))
+    g = np.load(os.path.join(GOLD, "c0.npz"))
+    head = g[f"out_q{quant}_head"]
+    check(d, got[: len(head)], head)
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("T,H,I,E,K", [(1, 256, 128, 1, 1), (77, 256, 384, 5, 3), (16, 1024, 2048, 8, 2),
+                                       (300, 512, 256, 16, 4), (129, 768, 640, 3, 2)])
+def test_ragged_shapes(quant, T, H, I, E, K):
+    d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=T)
+    got, _ = run_gpu(d)
+    check(d, got, run_oracle(d))
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_invalid_expert_ids_are_skipped(quant):
+    d = O.make_inputs(64, 256, 256, 6, 3, quant, "softmax", seed=5)
+    d["topk_ids"][4, 1] = -1
+    d["topk_ids"][9, :] = 6
+    d["topk_ids"][10, 0] = 1000
+    got, _ = run_gpu(d)
+    check(d, got, run_oracle(d))
+    assert (got[9] == 0).all()
+
+
+def test_empty_experts_and_skew():
+    d = O.make_inputs(512, 256, 256, 8, 2, 0, "softmax", seed=6)
+    d["topk_ids"][:, 0] = 2
+    d["topk_ids"][:, 1] = 7
+    got, _ = run_gpu(d)
+    check(d, got, run_oracle(d))
+
+
+def test_tiny_sigmoid_golden():
+    cfg = dict(T=48, H=256, I=256, E=16, K=4, routing="sigmoid")
+    g = np.load(os.path.join(GOLD, "tiny_sigmoid.npz"))
+    for quant in (0, 1):
+        d = O.make_inputs(quant=quant, **cfg)
+        got, _ = run_gpu(d)
+        check(d, got[:16], g[f"out_q{quant}_head"])
+
+
+def test_zero_tokens_is_a_no_op():
+    d = O.make_inputs(4, 256, 128, 2, 1, 0, "softmax", seed=7)
+    args = args_for(d)
+    args.a = args.a[:0].contiguous()
+    args.topk_ids = args.topk_ids[:0].contiguous()
+    args.topk_weight = args.topk_weight[:0].contiguous()
+    out = M.fused_moe(traits_for(0), args)
+    torch.cuda.synchronize()
+    assert out.shape == (0, 256)
+
+
+# ------------------------------------------------------------------------------ properties
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_linear_in_topk_weight_bit_exact(quant):
+    d = O.make_inputs(200, 512, 256, 8, 2, quant, "softmax", seed=8)
+    a, _ = run_gpu(d)
+    d2 = dict(d)
+    d2["topk_w"] = d["topk_w"] * np.float32(0.25)
+    b, _ = run_gpu(d2)
+    assert (O.bf16_to_f32(b) == 0.25 * O.bf16_to_f32(a)).all()
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_token_permutation_permutes_output_bit_exact(quant):
+    d = O.make_inputs(300, 256, 256, 8, 2, quant, "softmax", seed=9)
+    a, _ = run_gpu(d)
+    perm = np.random.default_rng(0).permutation(300)
+    d2 = dict(d)
+    for k in ("x", "topk_ids", "topk_w"):
+        d2[k] = np.ascontiguousarray(d[k][perm])
+    b, _ = run_gpu(d2)
+    assert (b == a[perm]).all()
+
+
+def test_repeat_runs_are_deterministic():
+    d = O.make_inputs(500, 512, 512, 8, 2, 0, "softmax", seed=10)
+    a, _ = run_gpu(d)
+    for _ in range(3):
+        b, _ = run_gpu(d)
+        assert (a == b).all()
+
+
+# ------------------------------------------------------------------------------ full-size configurations
+
+def _full_size(T, H, I, E, K, quant, n_check=24):
+    """Inputs generated on the device at the configuration's full size; the oracle evaluates
+    a random subset of tokens (each token's output depends only on its own row)."""
+    torch.manual_seed(0)
+    dev = "cuda:0"
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, device=dev)
+    ids, w = O.route(logits.cpu().numpy(), K, "softmax")
+    if quant == 0:
+        w1 = (torch.randn(E, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)
+        w2 = (torch.randn(E, H, I, device=dev) * 0.02).to(torch.bfloat16)
+        s1 = s2 = None
+        w1_np, w2_np = out_bits(w1), out_bits(w2)
+    else:
+        def qw(rows, cols):
+            wf = torch.randn(E * rows, cols, device=dev) * 0.02
+            s = wf.abs().amax(dim=1) / 448.0
+            q = (wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+            return q.view(E, rows, cols), s.view(E, rows).contiguous()
+        w1, s1 = qw(2 * I, H)
+        w2, s2 = qw(H, I)
+        w1_np, w2_np = w1.cpu().numpy(), w2.cpu().numpy()
+    args = M.FusedMoeArgs(a=x, g=w1, d=w2, topk_ids=to_dev(ids), topk_weight=to_dev(w), g_scale=s1, d_scale=s2)
+    out = M.fused_moe(traits_for(quant), args)
+    torch.cuda.synchronize()
+    assert api.check_status(args.workspace) == 0
+    sel = np.random.default_rng(1).choice(T, size=min(n_check, T), replace=False).astype(np.int32)
+    ref = O.fused_moe(out_bits(x), w1_np, w2_np, ids, w, quant,
+                      None if s1 is None else s1.cpu().numpy(), None if s2 is None else s2.cpu().numpy(), sel=sel)
+    got = out_bits(out)[sel]
+    check(dict(quant=quant), got, ref)
+
+
+def test_full_size_mixtral_prefill_bf16():
+    _full_size(4096, 4096, 14336, 8, 2, 0)
+
+
+def test_full_size_mixtral_prefill_fp8():
+    _full_size(8192, 4096, 14336, 8, 2, 1)
+
+
+def test_full_size_decode_fp8():
+    _full_size(16, 4096, 14336, 8, 2, 1, n_check=16)

@@ -68,6 +68,16 @@ def lib() -> ctypes.CDLL:
                                ctypes.POINTER(ctypes.c_float)]
         l.fmoe_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         l.fmoe_launches_per_run.argtypes = [ctypes.POINTER(_Traits)]
+        l.fmoe_profile_create.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]
+        l.fmoe_run_profiled.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.c_void_p,
+                                        ctypes.c_void_p]
+        l.fmoe_profile_read.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_float),
+                                        ctypes.POINTER(ctypes.c_int32)]
+        l.fmoe_profile_destroy.argtypes = [ctypes.c_void_p]
+        l.fmoe_gather_rows.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                       ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        l.fmoe_combine_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                        ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
         _lib = l
     return _lib
 
@@ -213,3 +223,63 @@ def moe_sorting(topk_ids: torch.Tensor, topk_weight: torch.Tensor, num_experts: 
                            ids.data_ptr(), w.data_ptr(), eids.data_ptr(), npp.data_ptr(),
                            _stream_ptr(stream)))
     return ids, w, eids, npp
+
+
+STAGES = ("sort", "gather", "gemm1", "quant_y", "gemm2", "combine")
+
+
+class StageProfile:
+    """Per-kernel timing of fused_moe runs: events are recorded between the kernels and read
+    after the timed loop, so nothing synchronises inside it."""
+
+    def __init__(self, max_runs: int):
+        self._h = ctypes.c_void_p()
+        _check(lib().fmoe_profile_create(max_runs, ctypes.byref(self._h)))
+
+    def run(self, traits: FusedMoeTraits, args: FusedMoeArgs, stream=None):
+        t, a = traits.to_c(), args.to_c()
+        _check(lib().fmoe_run_profiled(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream), self._h))
+        return args.o
+
+    def read(self) -> dict:
+        """Waits for the recorded runs; returns {'runs': n, stage: total_ms, ...}."""
+        ms = (ctypes.c_float * 6)()
+        n = ctypes.c_int32(0)
+        _check(lib().fmoe_profile_read(self._h, ms, ctypes.byref(n)))
+        d = {name: float(ms[i]) for i, name in enumerate(STAGES)}
+        d["runs"] = int(n.value)
+        return d
+
+    def close(self):
+        if self._h:
+            lib().fmoe_profile_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def gather_rows(src: torch.Tensor, row_ids: torch.Tensor, n_rows_dev: torch.Tensor,
+                out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """out[i] = src[row_ids[i]] for i < n_rows_dev[0] (bf16 rows; ids outside the source give
+    zero rows).  The expert-parallel dispatch uses it to pack rows per destination rank."""
+    n = row_ids.numel()
+    if out is None:
+        out = torch.empty(n, src.shape[1], dtype=src.dtype, device=src.device)
+    _check(lib().fmoe_gather_rows(src.data_ptr(), src.shape[0], src.shape[1], row_ids.data_ptr(), n,
+                                  n_rows_dev.data_ptr(), out.data_ptr(), _stream_ptr(stream)))
+    return out
+
+
+def combine_rows(rows: torch.Tensor, index: torch.Tensor, T: int, K: int,
+                 out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """out[t] = bf16(sum_k rows[index[t*K+k]]), k ascending, f32 accumulation, index < 0 skipped."""
+    H = rows.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=rows.device)
+    _check(lib().fmoe_combine_rows(rows.data_ptr(), index.data_ptr(), T, K, H, out.data_ptr(),
+                                   _stream_ptr(stream)))
+    return out

@@ -162,7 +162,13 @@ int fmoe_launches_per_run(const fmoe_traits_c* traits) {
   return traits->quant == FMOE_QUANT_NONE ? 5 : 6;
 }
 
-int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_v, float* ms_out) {
+// Stage boundaries at which run_impl records an event when given an event array:
+// 0 start, 1 after sort, 2 after gather, 3 after gemm1, 4 after quant of y (== 3 for bf16),
+// 5 after gemm2, 6 after combine.
+constexpr int kStageEvents = 7;
+
+static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_v, float* ms_out,
+                    cudaEvent_t* stage_ev) {
   int rc = validate_traits(traits);
   if (rc == FMOE_OK) rc = validate_dims(traits, args);
   if (rc != FMOE_OK) return rc;
@@ -178,7 +184,11 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
     return fail(FMOE_ERR_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)a.workspace_bytes,
                 (unsigned long long)plan.l.total_bytes);
   if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return fail(FMOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-  if (a.T == 0) return FMOE_OK;
+  if (a.T == 0) {
+    if (stage_ev)
+      for (int i = 0; i < kStageEvents; ++i) FMOE_CUDA(cudaEventRecord(stage_ev[i], static_cast<cudaStream_t>(stream_v)));
+    return FMOE_OK;
+  }
   rc = set_device_for(a.x);
   if (rc != FMOE_OK) return rc;
 
@@ -200,7 +210,9 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
   float* y_scale = fp8 ? reinterpret_cast<float*>(ws + l.y_scale) : nullptr;
   float* slots = reinterpret_cast<float*>(ws + l.slots);
 
+#define FMOE_STAGE(i) do { if (stage_ev) FMOE_CUDA(cudaEventRecord(stage_ev[i], stream)); } while (0)
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  FMOE_STAGE(0);
   if (ms_out) {
     FMOE_CUDA(cudaEventCreate(&ev0));
     FMOE_CUDA(cudaEventCreate(&ev1));
@@ -210,8 +222,10 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
   FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
                                      sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
                                      mblk_cum, status, stream));
+  FMOE_STAGE(1);
   FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, fp8 ? 1 : 0,
                                      a_sorted, a_scale, stream));
+  FMOE_STAGE(2);
 
   fmoe::GemmLaunch g{};
   int drv = 0;
@@ -231,6 +245,7 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
   g.out = y; g.ld_out = a.I;
   if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "gemm1 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+  FMOE_STAGE(3);
 
   const void* a2 = y;
   if (fp8) {
@@ -238,6 +253,7 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
                                        yq, y_scale, stream));
     a2 = yq;
   }
+  FMOE_STAGE(4);
   // gemm2: [cap, I] x W2[E, H, I]^T * topk_weight -> slots [T*K, H]
   g.epilogue = fmoe::kEpiScaledSlots;
   g.a = a2; g.b = a.w2; g.k_elems = a.I;
@@ -247,8 +263,11 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
   g.out = slots; g.ld_out = a.H;
   if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "gemm2 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+  FMOE_STAGE(5);
 
   FMOE_CUDA(fmoe::launch_combine(slots, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream));
+  FMOE_STAGE(6);
+#undef FMOE_STAGE
 
   if (ms_out) {
     FMOE_CUDA(cudaEventRecord(ev1, stream));
@@ -260,6 +279,88 @@ int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream_
     FMOE_CUDA(cudaMemcpy(&st, status, sizeof(st), cudaMemcpyDeviceToHost));
     if (st != 0) return fail(FMOE_ERR_DEVICE_TIMEOUT, "device status word 0x%x: a bounded wait ran out", st);
   }
+  return FMOE_OK;
+}
+
+int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream, float* ms_out) {
+  return run_impl(traits, args, stream, ms_out, nullptr);
+}
+
+// ---- per-stage timing: events are recorded between the kernels of each run and read back
+// later, so the timed loop itself never synchronises.
+struct fmoe_profile {
+  int max_runs;
+  int runs;
+  cudaEvent_t* ev;   // [max_runs][kStageEvents]
+};
+
+int fmoe_profile_create(int32_t max_runs, void** handle) {
+  if (!handle || max_runs <= 0) return fail(FMOE_ERR_INVALID_ARG, "handle and a positive run count are required");
+  fmoe_profile* p = new fmoe_profile{max_runs, 0, new cudaEvent_t[static_cast<size_t>(max_runs) * kStageEvents]};
+  for (int i = 0; i < max_runs * kStageEvents; ++i) {
+    if (cudaEventCreate(&p->ev[i]) != cudaSuccess) return fail(FMOE_ERR_CUDA, "cudaEventCreate failed");
+  }
+  *handle = p;
+  return FMOE_OK;
+}
+
+int fmoe_run_profiled(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream, void* handle) {
+  fmoe_profile* p = static_cast<fmoe_profile*>(handle);
+  if (!p) return fail(FMOE_ERR_INVALID_ARG, "profile handle is null");
+  if (p->runs >= p->max_runs) return fail(FMOE_ERR_INVALID_ARG, "profile handle is full (%d runs)", p->max_runs);
+  int rc = run_impl(traits, args, stream, nullptr, p->ev + static_cast<size_t>(p->runs) * kStageEvents);
+  if (rc == FMOE_OK) p->runs++;
+  return rc;
+}
+
+int fmoe_profile_read(void* handle, float* stage_ms, int32_t* runs) {
+  fmoe_profile* p = static_cast<fmoe_profile*>(handle);
+  if (!p || !stage_ms) return fail(FMOE_ERR_INVALID_ARG, "handle and stage_ms are required");
+  for (int sidx = 0; sidx < kStageEvents - 1; ++sidx) stage_ms[sidx] = 0.f;
+  for (int r = 0; r < p->runs; ++r) {
+    cudaEvent_t* e = p->ev + static_cast<size_t>(r) * kStageEvents;
+    FMOE_CUDA(cudaEventSynchronize(e[kStageEvents - 1]));
+    for (int sidx = 0; sidx < kStageEvents - 1; ++sidx) {
+      float ms = 0.f;
+      FMOE_CUDA(cudaEventElapsedTime(&ms, e[sidx], e[sidx + 1]));
+      stage_ms[sidx] += ms;
+    }
+  }
+  if (runs) *runs = p->runs;
+  p->runs = 0;
+  return FMOE_OK;
+}
+
+int fmoe_profile_destroy(void* handle) {
+  fmoe_profile* p = static_cast<fmoe_profile*>(handle);
+  if (!p) return FMOE_OK;
+  for (int i = 0; i < p->max_runs * kStageEvents; ++i) cudaEventDestroy(p->ev[i]);
+  delete[] p->ev;
+  delete p;
+  return FMOE_OK;
+}
+
+// ---- expert-parallel helpers: pack rows for the dispatch, reduce the returned rows.
+int fmoe_gather_rows(const void* src, int32_t n_src, int32_t cols, const int32_t* row_ids, int32_t n_rows,
+                     const int32_t* n_rows_dev, void* dst, void* stream) {
+  if (!src || !row_ids || !dst || !n_rows_dev) return fail(FMOE_ERR_INVALID_ARG, "src, row_ids, n_rows_dev and dst are required");
+  if (cols <= 0 || cols % 8) return fail(FMOE_ERR_UNSUPPORTED, "cols must be a positive multiple of 8");
+  if (n_rows <= 0) return FMOE_OK;
+  int rc = set_device_for(src);
+  if (rc != FMOE_OK) return rc;
+  FMOE_CUDA(fmoe::launch_gather_rows(src, n_src, cols, row_ids, n_rows_dev, n_rows, 0, dst, nullptr,
+                                     static_cast<cudaStream_t>(stream)));
+  return FMOE_OK;
+}
+
+int fmoe_combine_rows(const void* rows, const int32_t* index, int32_t T, int32_t K, int32_t H, void* out,
+                      void* stream) {
+  if (!rows || !index || !out) return fail(FMOE_ERR_INVALID_ARG, "rows, index and out are required");
+  if (H <= 0 || H % 8) return fail(FMOE_ERR_UNSUPPORTED, "H must be a positive multiple of 8");
+  if (T <= 0) return FMOE_OK;
+  int rc = set_device_for(rows);
+  if (rc != FMOE_OK) return rc;
+  FMOE_CUDA(fmoe::launch_combine_rows(rows, index, T, K, H, out, static_cast<cudaStream_t>(stream)));
   return FMOE_OK;
 }
 

@@ -27,6 +27,11 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
 cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream);
 
+// out[t, :] = bf16( sum_k rows[index[t*K + k], :] ), f32 accumulation, index < 0 skipped;
+// rows are bf16 [*, H].
+cudaError_t launch_combine_rows(const void* rows, const int32_t* index, int T, int K, int H,
+                                void* out, cudaStream_t stream);
+
 struct GemmLaunch {
   bool fp8;
   int epilogue;                 // kEpiSiluMul / kEpiScaledSlots

@@ -136,7 +136,40 @@ combine_kernel(const float4* __restrict__ slots, const int32_t* __restrict__ top
   }
 }
 
+// Expert-parallel combine: bf16 partial rows picked through an index, f32 sum in k order.
+__global__ void __launch_bounds__(kRowThreads)
+combine_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ index, int K, int H,
+                    uint4* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int nvec = H >> 3;
+  for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < K; ++k) {
+      const int r = index[t * K + k];
+      if (r < 0) continue;
+      float f[8];
+      unpack8(rows[static_cast<size_t>(r) * nvec + i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    out[static_cast<size_t>(t) * nvec + i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_combine_rows(const void* rows, const int32_t* index, int T, int K, int H,
+                                void* out, cudaStream_t stream) {
+  combine_rows_kernel<<<T, kRowThreads, 0, stream>>>(reinterpret_cast<const uint4*>(rows), index, K, H,
+                                                     reinterpret_cast<uint4*>(out));
+  return cudaGetLastError();
+}
 
 cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
