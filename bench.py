@@ -315,6 +315,17 @@ def run_gpu(a, c):
 
     # per-kernel durations over the same number of steps (single GPU: events between kernels)
     stage = None
+    if a.kernel_only:
+        if sampler:
+            sampler.stop()
+        if rank == 0:
+            ms_step = ms_total / a.steps
+            print(json.dumps({"metric": "fused_moe_tflops", "value": flops_per_step(c) / ms_step / 1e9,
+                              "unit": "TFLOP/s", "n_gpus": a.gpus, "steps": a.steps, "ms_per_step": ms_step,
+                              "config": workload_config(c, a.gpus), "clocks": clocks, "kernel_only": True}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if world == 1:
         prof = api.StageProfile(a.steps)
         barrier()
@@ -424,8 +435,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="C1", choices=sorted(CONFIGS))
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override the token count (small cases for profiler captures)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the device-resident timed loop: no stage profile, e2e or CPU baseline")
     a = ap.parse_args()
-    c = CONFIGS[a.config]
+    c = dict(CONFIGS[a.config])
+    if a.tokens > 0:
+        c["T"] = a.tokens
+        c["label"] += f"-tokens{a.tokens}"
     if a.impl == "reference":
         run_reference(a, c)
     else:

@@ -173,6 +173,12 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   if (rc == FMOE_OK) rc = validate_dims(traits, args);
   if (rc != FMOE_OK) return rc;
   const fmoe_args_c& a = *args;
+  if (a.T == 0) {   // nothing to do; an empty batch may legitimately come with null pointers
+    if (stage_ev)
+      for (int i = 0; i < kStageEvents; ++i) FMOE_CUDA(cudaEventRecord(stage_ev[i], static_cast<cudaStream_t>(stream_v)));
+    if (ms_out) *ms_out = 0.f;
+    return FMOE_OK;
+  }
   if (!a.x || !a.w1 || !a.w2 || !a.topk_ids || !a.topk_weight || !a.out)
     return fail(FMOE_ERR_INVALID_ARG, "x, w1, w2, topk_ids, topk_weight and out are required");
   const bool fp8 = traits->quant != FMOE_QUANT_NONE;
@@ -184,11 +190,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     return fail(FMOE_ERR_WORKSPACE, "workspace has %llu bytes, %llu needed", (unsigned long long)a.workspace_bytes,
                 (unsigned long long)plan.l.total_bytes);
   if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return fail(FMOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-  if (a.T == 0) {
-    if (stage_ev)
-      for (int i = 0; i < kStageEvents; ++i) FMOE_CUDA(cudaEventRecord(stage_ev[i], static_cast<cudaStream_t>(stream_v)));
-    return FMOE_OK;
-  }
+
   rc = set_device_for(a.x);
   if (rc != FMOE_OK) return rc;
 
