@@ -42,8 +42,9 @@ CONFIGS = {
 QUANT_NAME = {0: "none", 1: "token_channel"}
 
 # DRAM bytes (read + write) of one gate+up GEMM launch on the benchmark workload, from the
-# ncu capture summarised under profiles/ (null until a capture has been taken).
-GEMM1_DRAM_TRAFFIC_BYTES = {"C1": None, "C2": None, "C3": None}
+# ncu capture summarised in profiles/grouped_gemm_bf16_mixtral_prefill.md (None where no
+# capture of that configuration has been taken).
+GEMM1_DRAM_TRAFFIC_BYTES = {"C1": 2199174144, "C2": None, "C3": None}
 
 
 def measured_peaks():

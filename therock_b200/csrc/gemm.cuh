@@ -30,7 +30,7 @@ constexpr int kBBytes = kTileN * kStageKBytes;             // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;             // 48 KiB
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kSmemMisc = 4096;
+constexpr int kSmemMisc = 8192;          // barriers + per-expert block table (<= 1025 ints)
 constexpr int kGemmSmemBytes = kStages * kStageBytes + kSmemMisc + 1024;  // +1024 alignment slack
 
 enum : int { kEpiSiluMul = 1, kEpiScaledSlots = 2 };
@@ -63,7 +63,7 @@ struct TileCoord {
 
 // tile -> (expert, n-block, m-block): experts in order, then n-blocks, then that expert's
 // m-blocks fastest, so CTAs running side by side share the same weight slabs through L2.
-__device__ __forceinline__ TileCoord decode_tile(int tile, const int* __restrict__ cum, int E,
+__device__ __forceinline__ TileCoord decode_tile(int tile, const int* cum, int E,
                                                  int n_blocks) {
   int lo = 1, hi = E;
   while (lo < hi) {
@@ -80,7 +80,8 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const int* __restrict
   return t;
 }
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+// SiLU with the fast exponential and division (a few ulp; far inside the bf16 rounding of y).
+__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 template <bool kFp8, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -97,12 +98,16 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   uint64_t* acc_empty_bar = acc_full_bar + 2;                        // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* cum_s = reinterpret_cast<int*>(misc + 256);                   // [E + 1] copy of mblk_cum
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements per stage
   constexpr int kUmmaKBytes = 32;                   // one MMA consumes 32 bytes of K per row
 
+  // The block table is read on every tile boundary by the producer; keep it on chip so the
+  // decode does not sit on the critical path with dependent global loads.
+  for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
@@ -125,7 +130,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.mblk_cum[p.num_experts] * p.n_blocks;
+  const int total_tiles = cum_s[p.num_experts] * p.n_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -136,7 +141,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord tc = decode_tile(tile, p.mblk_cum, p.num_experts, p.n_blocks);
+        const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
         const int a_row = tc.m_blk * kBlockM;
         const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
         const int b_row1 = b_row0 + p.second_slab_offset;
@@ -207,7 +212,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const TileCoord tc = decode_tile(tile, p.mblk_cum, p.num_experts, p.n_blocks);
+      const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
       const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
       // Per-output-channel scales of this tile's two slabs (same addresses for the whole
       // warp, so these are broadcast loads served by L1).
@@ -225,27 +230,40 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (kEpi == kEpiSiluMul) {
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) +
                               static_cast<size_t>(slot) * p.ld_out + tc.n_blk * kSlabRows;
-#pragma unroll 1
+        // Software pipeline over 32-column chunks: the TMEM loads of chunk c+1 are in flight
+        // while chunk c is scaled, activated and stored.
+        uint32_t g[2][32], u[2][32];
+        ptx::tmem_ld_32x32(t_row, g[0]);
+        ptx::tmem_ld_32x32(t_row + kSlabRows, u[0]);
+#pragma unroll
         for (int c = 0; c < kSlabRows / 32; ++c) {
-          uint32_t g[32], u[32];
-          ptx::tmem_ld_32x32(t_row + c * 32, g);
-          ptx::tmem_ld_32x32(t_row + kSlabRows + c * 32, u);
+          const int cur = c & 1;
           ptx::tmem_ld_wait();
+          if (c + 1 < kSlabRows / 32) {
+            ptx::tmem_ld_32x32(t_row + (c + 1) * 32, g[cur ^ 1]);
+            ptx::tmem_ld_32x32(t_row + kSlabRows + (c + 1) * 32, u[cur ^ 1]);
+          }
           uint32_t packed[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float g0 = __uint_as_float(g[j]), g1 = __uint_as_float(g[j + 1]);
-            float u0 = __uint_as_float(u[j]), u1 = __uint_as_float(u[j + 1]);
-            if (p.b_scale != nullptr) {
-              const float2 sg = __ldg(reinterpret_cast<const float2*>(bs0 + c * 32 + j));
-              const float2 su = __ldg(reinterpret_cast<const float2*>(bs1 + c * 32 + j));
-              g0 = (g0 * a_s) * sg.x;
-              g1 = (g1 * a_s) * sg.y;
-              u0 = (u0 * a_s) * su.x;
-              u1 = (u1 * a_s) * su.y;
+          for (int q = 0; q < 8; ++q) {
+            float gv[4], uv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              gv[j] = __uint_as_float(g[cur][4 * q + j]);
+              uv[j] = __uint_as_float(u[cur][4 * q + j]);
             }
-            __nv_bfloat162 v = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
-            packed[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+            if (p.b_scale != nullptr) {
+              const float4 sg = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+              const float4 su = __ldg(reinterpret_cast<const float4*>(bs1 + c * 32 + 4 * q));
+              gv[0] = (gv[0] * a_s) * sg.x; gv[1] = (gv[1] * a_s) * sg.y;
+              gv[2] = (gv[2] * a_s) * sg.z; gv[3] = (gv[3] * a_s) * sg.w;
+              uv[0] = (uv[0] * a_s) * su.x; uv[1] = (uv[1] * a_s) * su.y;
+              uv[2] = (uv[2] * a_s) * su.z; uv[3] = (uv[3] * a_s) * su.w;
+            }
+            __nv_bfloat162 v0 = __floats2bfloat162_rn(silu(gv[0]) * uv[0], silu(gv[1]) * uv[1]);
+            __nv_bfloat162 v1 = __floats2bfloat162_rn(silu(gv[2]) * uv[2], silu(gv[3]) * uv[3]);
+            packed[2 * q] = *reinterpret_cast<uint32_t*>(&v0);
+            packed[2 * q + 1] = *reinterpret_cast<uint32_t*>(&v1);
           }
           uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
 #pragma unroll
@@ -257,27 +275,27 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         const float w = p.sorted_weights[slot];
         float* orow = reinterpret_cast<float*>(p.out) +
                       static_cast<size_t>(row < 0 ? 0 : row) * p.ld_out + tc.n_blk * kTileN;
-#pragma unroll 1
+        uint32_t v[2][32];
+        ptx::tmem_ld_32x32(t_row, v[0]);
+#pragma unroll
         for (int c = 0; c < kTileN / 32; ++c) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32(t_row + c * 32, v);
+          const int cur = c & 1;
           ptx::tmem_ld_wait();
+          if (c + 1 < kTileN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, v[cur ^ 1]);
           if (row >= 0) {
             float4* dst = reinterpret_cast<float4*>(orow + c * 32);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               float f[4];
-              float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
-              // second GEMM: the tile's 256 columns are 256 consecutive output channels
-              if (p.b_scale != nullptr) sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
-              const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float x = __uint_as_float(v[4 * q + j]);
-                if (p.b_scale != nullptr) x = (x * a_s) * scv[j];
-                f[j] = w * x;
+              for (int j = 0; j < 4; ++j) f[j] = __uint_as_float(v[cur][4 * q + j]);
+              if (p.b_scale != nullptr) {
+                // second GEMM: the tile's 256 columns are 256 consecutive output channels
+                const float4 sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+                f[0] = (f[0] * a_s) * sc.x; f[1] = (f[1] * a_s) * sc.y;
+                f[2] = (f[2] * a_s) * sc.z; f[3] = (f[3] * a_s) * sc.w;
               }
-              dst[q] = make_float4(f[0], f[1], f[2], f[3]);
+              dst[q] = make_float4(w * f[0], w * f[1], w * f[2], w * f[3]);
             }
           }
         }
