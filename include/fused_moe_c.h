@@ -135,6 +135,25 @@ FMOE_API int fmoe_get_workspace_size(const fmoe_traits_c* traits, const fmoe_arg
 FMOE_API int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream,
                       float* ms_out);
 
+/* fmoe_run for callers that cannot allocate device memory (no counterpart in the reference:
+ * ck_tile always takes its workspace from the caller).  Meant for hosts that receive only
+ * input and output buffers -- a plugin slot of a serving engine, a foreign-function caller
+ * without a CUDA allocator, a loop where cudaMalloc is forbidden because it stalls the
+ * device.  Inputs and outputs are passed as for fmoe_run; args->workspace is ignored and
+ * the scratch comes from an array of FMOE_STATIC_WS_BYTES built into the library (each GPU
+ * that loads the library holds that much until the process ends).  Calls whose workspace
+ * (fmoe_get_workspace_size) exceeds the limit return FMOE_ERR_WORKSPACE.  The call itself
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ * The first call on each device looks up the array's device address; make that first
+ * call outside any stream capture.  All calls on a device share the one array and it keeps
+ * the previous call's contents (everything later stages read is rewritten by the call's
+ * first kernel), so two calls that may overlap on the GPU -- different streams, or
+ * different threads -- race: serialise them on one stream.  Asynchronous on `stream`.
+ * The status word of a bounded device wait is not readable through this variant; use
+ * fmoe_run with fmoe_check_status where that is needed. */
+#define FMOE_STATIC_WS_BYTES (64u * 1024u * 1024u)
+FMOE_API int fmoe_run_static_ws(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream);
+
 /* Reads the device status word of a workspace after the stream has been synchronised:
  * 0 = clean, otherwise the code a kernel stored when a bounded wait ran out. */
 FMOE_API int fmoe_check_status(const void* workspace, void* stream, int32_t* status_out);

@@ -66,6 +66,7 @@ def lib() -> ctypes.CDLL:
                                               ctypes.POINTER(ctypes.c_uint64)]
         l.fmoe_run.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.c_void_p,
                                ctypes.POINTER(ctypes.c_float)]
+        l.fmoe_run_static_ws.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.c_void_p]
         l.fmoe_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         l.fmoe_launches_per_run.argtypes = [ctypes.POINTER(_Traits)]
         l.fmoe_profile_create.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]
@@ -283,3 +284,18 @@ def combine_rows(rows: torch.Tensor, index: torch.Tensor, T: int, K: int,
     _check(lib().fmoe_combine_rows(rows.data_ptr(), index.data_ptr(), T, K, H, out.data_ptr(),
                                    _stream_ptr(stream)))
     return out
+
+
+STATIC_WS_BYTES = 64 * 1024 * 1024
+
+
+def fused_moe_static_ws(traits: FusedMoeTraits, args: FusedMoeArgs, stream=None) -> torch.Tensor:
+    """fused_moe for hosts that may not allocate device memory: the scratch comes from the
+    64 MiB array built into the library (fmoe_run_static_ws).  The caller passes inputs and
+    the output tensor; nothing is allocated here either, so args.o is required.  Calls on
+    one device share that array: keep them on one stream."""
+    if args.o is None:
+        raise FmoeError(-1, "the output tensor must be provided (this entry point allocates nothing)")
+    t, a = traits.to_c(), args.to_c()
+    _check(lib().fmoe_run_static_ws(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream)))
+    return args.o

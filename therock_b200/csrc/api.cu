@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/fused_moe_c.h"
 #include "gemm.cuh"
@@ -340,6 +341,64 @@ int fmoe_profile_destroy(void* handle) {
   delete[] p->ev;
   delete p;
   return FMOE_OK;
+}
+
+// ---- entry point that allocates nothing: the workspace lives inside the library image.
+//
+// Some hosts of this operator are not allowed to obtain device memory at all: a plugin
+// slot in a serving engine that hands the operator only its input and output tensors, a
+// foreign-function caller with no CUDA allocator of its own, or a latency-critical loop in
+// which cudaMalloc is banned because it synchronises the whole device.  For them the
+// scratch the operator needs is this fixed array.  It is part of the loaded module, so
+// every GPU that loads the library keeps these FMOE_STATIC_WS_BYTES reserved until the
+// process exits, which is why the limit is modest.
+static __device__ __align__(256) unsigned char g_fmoe_static_ws[FMOE_STATIC_WS_BYTES];
+
+namespace {
+constexpr int kStaticWsMaxDevices = 64;
+void* g_static_ws_addr[kStaticWsMaxDevices] = {nullptr};   // device address of the array, per GPU
+std::mutex g_static_ws_mu;
+}  // namespace
+
+int fmoe_run_static_ws(const fmoe_traits_c* traits, const fmoe_args_c* args, void* stream) {
+  int rc = validate_traits(traits);
+  if (rc == FMOE_OK) rc = validate_dims(traits, args);
+  if (rc != FMOE_OK) return rc;
+  Plan plan;
+  make_plan(traits, args, &plan);
+  if (plan.l.total_bytes > static_cast<uint64_t>(FMOE_STATIC_WS_BYTES))
+    return fail(FMOE_ERR_WORKSPACE,
+                "this call needs %llu bytes of scratch but the built-in workspace holds %llu; "
+                "use fmoe_run with a caller-provided workspace",
+                (unsigned long long)plan.l.total_bytes, (unsigned long long)FMOE_STATIC_WS_BYTES);
+  if (args->T > 0 && args->x) {
+    rc = set_device_for(args->x);
+    if (rc != FMOE_OK) return rc;
+  }
+  int dev = 0;
+  FMOE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kStaticWsMaxDevices) return fail(FMOE_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  void* ws = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_ws_mu);
+    if (g_static_ws_addr[dev] == nullptr) {
+      // In host code the array's name is only a handle; the address kernels can use has to
+      // be asked for, once per device, with that device current.
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_fmoe_static_ws);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(FMOE_ERR_CUDA, "cudaGetSymbolAddress(static workspace) failed on device %d: %s", dev,
+                    cudaGetErrorString(e));
+      g_static_ws_addr[dev] = p;
+    }
+    ws = g_static_ws_addr[dev];
+  }
+  fmoe_args_c a = *args;
+  a.workspace = ws;
+  a.workspace_bytes = FMOE_STATIC_WS_BYTES;
+  // The sorting kernel rewrites every word later kernels read (pad slots, block ids, the
+  // status word), so nothing left over from the previous call needs clearing here.
+  return run_impl(traits, &a, stream, nullptr, nullptr);
 }
 
 // ---- expert-parallel helpers: pack rows for the dispatch, reduce the returned rows.
