@@ -239,7 +239,14 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   g.sorted_weights = sorted_w;
   g.status = status;
   g.max_m_blocks = static_cast<int>(plan.cap / fmoe::kBlockM);
+  // Kernel flavour.  The CTA-pair kernel moves half as much of the weight operand per flop
+  // but pads every expert to an even number of row blocks; with few rows per expert that
+  // padding costs more than the pairing saves in the first GEMM (measured on the Mixtral
+  // shapes: break-even near 1.5k routed rows per expert).
+  const int forced_mode = fmoe::gemm_mode_from_env();
+  const long long rows_per_expert = static_cast<long long>(a.T) * a.K / a.E;
   // gemm1: [cap, H] x W1[E, 2I, H]^T -> SiLU(gate) * up -> y [cap, I]
+  g.mode = forced_mode ? forced_mode : (rows_per_expert >= 1536 ? 2 : 1);
   g.epilogue = fmoe::kEpiSiluMul;
   g.a = a_sorted; g.a_rows = plan.cap; g.b = a.w1; g.k_elems = a.H;
   g.b_rows_per_expert = 2 * a.I;
@@ -258,6 +265,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   }
   FMOE_STAGE(4);
   // gemm2: [cap, I] x W2[E, H, I]^T * topk_weight -> slots [T*K, H]
+  g.mode = forced_mode ? forced_mode : (rows_per_expert >= 256 ? 2 : 1);
   g.epilogue = fmoe::kEpiScaledSlots;
   g.a = a2; g.b = a.w2; g.k_elems = a.I;
   g.b_rows_per_expert = a.H;

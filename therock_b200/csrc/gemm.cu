@@ -1,6 +1,8 @@
 // Host side of the grouped GEMM: TMA descriptors and the persistent launch.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "gemm.cuh"
@@ -78,6 +80,35 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const G
   return cudaGetLastError();
 }
 
+template <bool kFp8, int kEpi>
+cudaError_t launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                                int grid, cudaStream_t stream) {
+  static bool configured[kMaxDevices] = {false};
+  const int dev = current_device();
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_pair_kernel<kFp8, kEpi>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  fmoe_grouped_gemm_pair_kernel<kFp8, kEpi><<<grid, kGemmThreads, kPairSmemBytes, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// FMOE_GEMM_MODE=1cta / 2cta forces one kernel flavour for every GEMM (used to compare them);
+// unset, the caller's per-GEMM choice stands.  Returns 0 (no override), 1 or 2.
+int gemm_mode_from_env() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("FMOE_GEMM_MODE");
+    mode = !e ? 0 : (std::strcmp(e, "1cta") == 0 ? 1 : (std::strcmp(e, "2cta") == 0 ? 2 : 0));
+  }
+  return mode;
+}
+
+namespace {
 }  // namespace
 
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
@@ -107,6 +138,21 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   p.status = g.status;
   p.desc_template = g.desc_template_override ? g.desc_template_override : ptx::sw128_kmajor_desc_template();
   p.idesc = g.idesc_override ? g.idesc_override : ptx::make_idesc(g.fp8 ? 0u : 1u, kBlockM, kTileN);
+  const bool pair = g.mode == 2;
+  if (pair) {
+    if (!g.idesc_override) p.idesc = ptx::make_idesc(g.fp8 ? 0u : 1u, 2 * kBlockM, kTileN);
+    // upper bound on pair tiles: every expert may add one half-empty pair
+    const long long max_pairs = (static_cast<long long>(g.max_m_blocks) + g.num_experts + 1) / 2;
+    const long long max_tiles = max_pairs * g.n_blocks;
+    const int clusters = sm_count() / 2;
+    const int grid = 2 * static_cast<int>(max_tiles < clusters ? (max_tiles > 0 ? max_tiles : 1) : clusters);
+    if (g.fp8) {
+      return g.epilogue == kEpiSiluMul ? launch_pair_variant<true, kEpiSiluMul>(ta, tb, p, grid, stream)
+                                       : launch_pair_variant<true, kEpiScaledSlots>(ta, tb, p, grid, stream);
+    }
+    return g.epilogue == kEpiSiluMul ? launch_pair_variant<false, kEpiSiluMul>(ta, tb, p, grid, stream)
+                                     : launch_pair_variant<false, kEpiScaledSlots>(ta, tb, p, grid, stream);
+  }
   const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
   const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
   if (g.fp8) {

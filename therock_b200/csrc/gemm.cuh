@@ -83,6 +83,88 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const int* cum, int E
 // SiLU with the fast exponential and division (a few ulp; far inside the bf16 rounding of y).
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
+// Fused epilogue of one 128 x 256 accumulator held in TMEM (this thread owns one row).
+//   kEpiSiluMul    : columns 0..127 gate, 128..255 up -> bf16 y[slot, n_blk*128 ..] = SiLU(g)*u
+//   kEpiScaledSlots: 256 output channels -> f32 slots[row, n_blk*256 ..] = w * acc
+// fp8: acc is first multiplied by the row's activation scale and the channel's weight scale.
+template <int kEpi>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_row, int slot, int n_blk,
+                                              const float* bs0, const float* bs1, float a_s) {
+  if (kEpi == kEpiSiluMul) {
+    __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) +
+                          static_cast<size_t>(slot) * p.ld_out + n_blk * kSlabRows;
+    // Software pipeline over 32-column chunks: the TMEM loads of chunk c+1 are in flight
+    // while chunk c is scaled, activated and stored.
+    uint32_t g[2][32], u[2][32];
+    ptx::tmem_ld_32x32(t_row, g[0]);
+    ptx::tmem_ld_32x32(t_row + kSlabRows, u[0]);
+#pragma unroll
+    for (int c = 0; c < kSlabRows / 32; ++c) {
+      const int cur = c & 1;
+      ptx::tmem_ld_wait();
+      if (c + 1 < kSlabRows / 32) {
+        ptx::tmem_ld_32x32(t_row + (c + 1) * 32, g[cur ^ 1]);
+        ptx::tmem_ld_32x32(t_row + kSlabRows + (c + 1) * 32, u[cur ^ 1]);
+      }
+      uint32_t packed[16];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float gv[4], uv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          gv[j] = __uint_as_float(g[cur][4 * q + j]);
+          uv[j] = __uint_as_float(u[cur][4 * q + j]);
+        }
+        if (p.b_scale != nullptr) {
+          const float4 sg = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+          const float4 su = __ldg(reinterpret_cast<const float4*>(bs1 + c * 32 + 4 * q));
+          gv[0] = (gv[0] * a_s) * sg.x; gv[1] = (gv[1] * a_s) * sg.y;
+          gv[2] = (gv[2] * a_s) * sg.z; gv[3] = (gv[3] * a_s) * sg.w;
+          uv[0] = (uv[0] * a_s) * su.x; uv[1] = (uv[1] * a_s) * su.y;
+          uv[2] = (uv[2] * a_s) * su.z; uv[3] = (uv[3] * a_s) * su.w;
+        }
+        __nv_bfloat162 v0 = __floats2bfloat162_rn(silu(gv[0]) * uv[0], silu(gv[1]) * uv[1]);
+        __nv_bfloat162 v1 = __floats2bfloat162_rn(silu(gv[2]) * uv[2], silu(gv[3]) * uv[3]);
+        packed[2 * q] = *reinterpret_cast<uint32_t*>(&v0);
+        packed[2 * q + 1] = *reinterpret_cast<uint32_t*>(&v1);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    }
+  } else {
+    const int row = p.sorted_rows[slot];
+    const float w = p.sorted_weights[slot];
+    float* orow = reinterpret_cast<float*>(p.out) +
+                  static_cast<size_t>(row < 0 ? 0 : row) * p.ld_out + n_blk * kTileN;
+    uint32_t v[2][32];
+    ptx::tmem_ld_32x32(t_row, v[0]);
+#pragma unroll
+    for (int c = 0; c < kTileN / 32; ++c) {
+      const int cur = c & 1;
+      ptx::tmem_ld_wait();
+      if (c + 1 < kTileN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, v[cur ^ 1]);
+      if (row >= 0) {
+        float4* dst = reinterpret_cast<float4*>(orow + c * 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float f[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) f[j] = __uint_as_float(v[cur][4 * q + j]);
+          if (p.b_scale != nullptr) {
+            // second GEMM: the tile's 256 columns are 256 consecutive output channels
+            const float4 sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+            f[0] = (f[0] * a_s) * sc.x; f[1] = (f[1] * a_s) * sc.y;
+            f[2] = (f[2] * a_s) * sc.z; f[3] = (f[3] * a_s) * sc.w;
+          }
+          dst[q] = make_float4(w * f[0], w * f[1], w * f[2], w * f[3]);
+        }
+      }
+    }
+  }
+}
+
 template <bool kFp8, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -227,79 +309,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      if (kEpi == kEpiSiluMul) {
-        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) +
-                              static_cast<size_t>(slot) * p.ld_out + tc.n_blk * kSlabRows;
-        // Software pipeline over 32-column chunks: the TMEM loads of chunk c+1 are in flight
-        // while chunk c is scaled, activated and stored.
-        uint32_t g[2][32], u[2][32];
-        ptx::tmem_ld_32x32(t_row, g[0]);
-        ptx::tmem_ld_32x32(t_row + kSlabRows, u[0]);
-#pragma unroll
-        for (int c = 0; c < kSlabRows / 32; ++c) {
-          const int cur = c & 1;
-          ptx::tmem_ld_wait();
-          if (c + 1 < kSlabRows / 32) {
-            ptx::tmem_ld_32x32(t_row + (c + 1) * 32, g[cur ^ 1]);
-            ptx::tmem_ld_32x32(t_row + kSlabRows + (c + 1) * 32, u[cur ^ 1]);
-          }
-          uint32_t packed[16];
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float gv[4], uv[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              gv[j] = __uint_as_float(g[cur][4 * q + j]);
-              uv[j] = __uint_as_float(u[cur][4 * q + j]);
-            }
-            if (p.b_scale != nullptr) {
-              const float4 sg = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
-              const float4 su = __ldg(reinterpret_cast<const float4*>(bs1 + c * 32 + 4 * q));
-              gv[0] = (gv[0] * a_s) * sg.x; gv[1] = (gv[1] * a_s) * sg.y;
-              gv[2] = (gv[2] * a_s) * sg.z; gv[3] = (gv[3] * a_s) * sg.w;
-              uv[0] = (uv[0] * a_s) * su.x; uv[1] = (uv[1] * a_s) * su.y;
-              uv[2] = (uv[2] * a_s) * su.z; uv[3] = (uv[3] * a_s) * su.w;
-            }
-            __nv_bfloat162 v0 = __floats2bfloat162_rn(silu(gv[0]) * uv[0], silu(gv[1]) * uv[1]);
-            __nv_bfloat162 v1 = __floats2bfloat162_rn(silu(gv[2]) * uv[2], silu(gv[3]) * uv[3]);
-            packed[2 * q] = *reinterpret_cast<uint32_t*>(&v0);
-            packed[2 * q + 1] = *reinterpret_cast<uint32_t*>(&v1);
-          }
-          uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
-      } else {
-        const int row = p.sorted_rows[slot];
-        const float w = p.sorted_weights[slot];
-        float* orow = reinterpret_cast<float*>(p.out) +
-                      static_cast<size_t>(row < 0 ? 0 : row) * p.ld_out + tc.n_blk * kTileN;
-        uint32_t v[2][32];
-        ptx::tmem_ld_32x32(t_row, v[0]);
-#pragma unroll
-        for (int c = 0; c < kTileN / 32; ++c) {
-          const int cur = c & 1;
-          ptx::tmem_ld_wait();
-          if (c + 1 < kTileN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, v[cur ^ 1]);
-          if (row >= 0) {
-            float4* dst = reinterpret_cast<float4*>(orow + c * 32);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              float f[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) f[j] = __uint_as_float(v[cur][4 * q + j]);
-              if (p.b_scale != nullptr) {
-                // second GEMM: the tile's 256 columns are 256 consecutive output channels
-                const float4 sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
-                f[0] = (f[0] * a_s) * sc.x; f[1] = (f[1] * a_s) * sc.y;
-                f[2] = (f[2] * a_s) * sc.z; f[3] = (f[3] * a_s) * sc.w;
-              }
-              dst[q] = make_float4(w * f[0], w * f[1], w * f[2], w * f[3]);
-            }
-          }
-        }
-      }
+      epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&acc_empty_bar[acc]));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -312,6 +322,217 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ============================================================================= CTA-pair variant
+// Two CTAs of a cluster (two SMs) compute one 256-row x 256-column tile with
+// tcgen05.mma.cta_group::2: CTA rank r stages the A rows of row block (2*pair + r) and the
+// r-th 128-row slab of B (gate slab / up slab for the first GEMM), so every SM fetches half as
+// much of the weight operand per flop as the single-CTA kernel.  Rank 0 issues the MMAs for
+// both SMs; each CTA's tensor memory receives its own 128 accumulator rows and runs its own
+// epilogue.  An expert with an odd number of row blocks leaves the second half of its last
+// pair without rows: that half computes on whatever the next block holds and skips its
+// epilogue.
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kABytes + kSlabRows * kStageKBytes;   // 16 KiB A + 16 KiB B slab
+constexpr int kPairSmemMisc = 9216;                                   // barriers + two expert tables
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairSmemMisc + 1024;
+
+struct PairTile {
+  int expert, n_blk, m_blk0, m_end;   // m_blk0: first row block of the pair; m_end: expert's end
+};
+
+__device__ __forceinline__ PairTile decode_pair_tile(int tile, const int* cum, const int* pair_cum,
+                                                     int E, int n_blocks) {
+  int lo = 1, hi = E;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (pair_cum[mid] * n_blocks > tile) hi = mid; else lo = mid + 1;
+  }
+  PairTile t;
+  t.expert = lo - 1;
+  const int pbase = pair_cum[t.expert];
+  const int pcnt = pair_cum[t.expert + 1] - pbase;
+  const int local = tile - pbase * n_blocks;
+  t.n_blk = local / pcnt;
+  t.m_blk0 = cum[t.expert] + 2 * (local % pcnt);
+  t.m_end = cum[t.expert + 1];
+  return t;
+}
+
+template <bool kFp8, int kEpi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
+                              const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* misc = smem + kPairStages * kPairStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);            // [kPairStages] used in rank 0
+  uint64_t* empty_bar = full_bar + kPairStages;                      // [kPairStages] both ranks
+  uint64_t* acc_full_bar = empty_bar + kPairStages;                  // [2] both ranks
+  uint64_t* acc_empty_bar = acc_full_bar + 2;                        // [2] used in rank 0
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* cum_s = reinterpret_cast<int*>(misc + 256);                   // [E + 1]
+  int* pair_cum_s = cum_s + 1032;                                    // [E + 1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  constexpr int kElemsPerStage = kFp8 ? 128 : 64;
+  constexpr int kUmmaKBytes = 32;
+
+  for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&acc_full_bar[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&acc_empty_bar[b]), 8);     // 4 epilogue warps in each CTA
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    pair_cum_s[0] = 0;
+    for (int e = 0; e < p.num_experts; ++e) {
+      run += (cum_s[e + 1] - cum_s[e] + 1) >> 1;
+      pair_cum_s[e + 1] = run;
+    }
+  }
+  ptx::tc_fence_before();
+  ptx::cluster_sync_all();      // barriers of both CTAs are initialised before anyone signals them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = pair_cum_s[p.num_experts] * p.n_blocks;
+  const int first_tile = blockIdx.x >> 1;
+  const int tile_step = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both ranks)
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tm_a);
+      ptx::prefetch_tensormap(&tm_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+        const PairTile tc = decode_pair_tile(tile, cum_s, pair_cum_s, p.num_experts, p.n_blocks);
+        const int a_row = (tc.m_blk0 + static_cast<int>(rank)) * kBlockM;
+        const int b_row = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride +
+                          (rank ? p.second_slab_offset : 0);
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          // completion bytes of both CTAs are credited to rank 0's barrier
+          const uint32_t full0 = ptx::map_to_rank(ptx::smem_u32(&full_bar[stage]), 0);
+          const uint32_t sa = ptx::smem_u32(smem + stage * kPairStageBytes);
+          if (rank == 0) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2 * kPairStageBytes);
+          const int kx = k * kElemsPerStage;
+          ptx::tma_load_2d_pair(sa, &tm_a, full0, kx, a_row);
+          ptx::tma_load_2d_pair(sa + kABytes, &tm_b, full0, kx, b_row);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x11);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (rank 0 only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kTileN);
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * kPairStageBytes);
+          const uint64_t da = ptx::make_smem_desc(p.desc_template, sa);
+          const uint64_t db = ptx::make_smem_desc(p.desc_template, sa + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
+            const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
+            const uint32_t accum = (k | kk) ? 1u : 0u;
+            if (kFp8) ptx::umma_f8_pair(d_tmem, da + adv, db + adv, p.idesc, accum);
+            else      ptx::umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, accum);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          const uint32_t e_local = ptx::smem_u32(&empty_bar[stage]);
+          ptx::umma_commit_pair(e_local);
+          ptx::umma_commit_pair(ptx::map_to_rank(e_local, 1));
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        const uint32_t f_local = ptx::smem_u32(&acc_full_bar[acc]);
+        ptx::umma_commit_pair(f_local);
+        ptx::umma_commit_pair(ptx::map_to_rank(f_local, 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x12);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both ranks)
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+      const PairTile tc = decode_pair_tile(tile, cum_s, pair_cum_s, p.num_experts, p.n_blocks);
+      const int m_blk = tc.m_blk0 + static_cast<int>(rank);
+      const bool valid = m_blk < tc.m_end;
+      const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
+      const float* bs0 = p.b_scale ? p.b_scale + b_row0 : nullptr;
+      const float* bs1 = p.b_scale ? bs0 + p.second_slab_offset : nullptr;
+      const int slot = m_blk * kBlockM + quad * 32 + lane;
+      const float a_s = (p.a_scale && valid) ? p.a_scale[slot] : 1.0f;
+      if (!ptx::mbar_wait(ptx::smem_u32(&acc_full_bar[acc]), acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(acc * kTileN);
+      if (valid) epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_u32(&acc_empty_bar[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (!ok && threadIdx.x == 64) atomicExch(p.status, kStatusGemmTimeout | 0x13);
+  }
+
+  // Neither CTA may leave while its partner can still signal its barriers or read its
+  // shared memory through a pair MMA.
+  ptx::tc_fence_before();
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 

@@ -51,11 +51,15 @@ struct GemmLaunch {
   int ld_out;
   int32_t* status;
   int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
+  int mode;                     // 2 = CTA-pair kernel (cta_group::2), anything else = single-CTA kernel
   uint64_t desc_template_override;  // 0 = the library's descriptor encoding (diagnostics only)
   uint32_t idesc_override;          // 0 = the library's instruction descriptor
 };
 // Returns cudaSuccess or the failing CUDA error; *drv_err receives a CUresult when the
 // tensor-map encode fails.
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err);
+
+// 0 = no override, 1 / 2 = FMOE_GEMM_MODE forces the single-CTA / CTA-pair kernel.
+int gemm_mode_from_env();
 
 }  // namespace fmoe
