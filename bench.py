@@ -38,8 +38,35 @@ CONFIGS = {
     "C1": dict(T=4096, H=4096, I=14336, E=8, K=2, quant=0, label="mixtral-8x7b-prefill-bf16"),
     "C2": dict(T=8192, H=4096, I=14336, E=8, K=2, quant=1, label="mixtral-8x7b-prefill-fp8"),
     "C3": dict(T=16, H=4096, I=14336, E=8, K=2, quant=1, label="mixtral-8x7b-decode-fp8"),
+    "C4": dict(T=8192, H=7168, I=2048, E=256, K=8, quant=2, routing="sigmoid",
+               label="deepseek-v3-shape-fp8-block128"),
 }
-QUANT_NAME = {0: "none", 1: "token_channel"}
+QUANT_NAME = {0: "none", 1: "token_channel", 2: "block128"}
+
+
+def quantise_weight(wf, quant):
+    """f32 [rows, cols] on the device -> (stored tensor, scales or None)."""
+    import torch
+    if quant == 0:
+        return wf.to(torch.bfloat16), None
+    if quant == 1:
+        s = wf.abs().amax(dim=1) / 448.0
+        s = torch.where(s > 0, s, torch.ones_like(s))
+        return (wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8), s
+    rows, cols = wf.shape
+    blocks = wf.view(rows // 128, 128, cols // 128, 128)
+    s = blocks.abs().amax(dim=(1, 3)) / 448.0
+    s = torch.where(s > 0, s, torch.ones_like(s))
+    q = (blocks / s[:, None, :, None]).to(torch.float8_e4m3fn).view(torch.uint8).view(rows, cols)
+    return q, s.contiguous()
+
+
+def route_on_device(logits, K, mode):
+    import torch
+    p = torch.softmax(logits, dim=-1) if mode == "softmax" else torch.sigmoid(logits)
+    w, ids = torch.topk(p, K, dim=-1)
+    w = (w / w.sum(dim=-1, keepdim=True)).float().contiguous()
+    return ids.to(torch.int32).contiguous(), w
 
 # DRAM bytes (read + write) of one gate+up GEMM launch on the benchmark workload, from the
 # ncu capture summarised in profiles/grouped_gemm_bf16_mixtral_prefill.md (None where no
@@ -126,18 +153,15 @@ def make_host_inputs(c, seed=0):
     g.manual_seed(seed)
     x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
     logits = torch.randn(T, E, generator=g, device=dev).cpu().numpy()
-    ids, w = O.route(logits, K, "softmax")
+    ids, w = O.route(logits, K, c.get("routing", "softmax"))
 
     def weights(rows, cols):
         out_q, out_s = [], []
         for _ in range(E):
-            wf = torch.randn(rows, cols, generator=g, device=dev) * 0.02
-            if quant == 0:
-                out_q.append(wf.to(torch.bfloat16).view(torch.int16).cpu())
-            else:
-                s = wf.abs().amax(dim=1) / 448.0
-                out_q.append((wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).cpu())
-                out_s.append(s.cpu())
+            q, sc = quantise_weight(torch.randn(rows, cols, generator=g, device=dev) * 0.02, quant)
+            out_q.append((q.view(torch.int16) if quant == 0 else q).cpu())
+            if sc is not None:
+                out_s.append(sc.cpu())
         q = torch.stack(out_q).numpy()
         return (q.view(np.uint16) if quant == 0 else q), (torch.stack(out_s).numpy() if out_s else None)
 
@@ -220,24 +244,17 @@ def device_inputs(c, dev, rank=0, world=1, seed=0):
     g.manual_seed(seed)
     x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
     logits = torch.randn(T, E, generator=g, device=dev)
-    p = torch.softmax(logits, dim=-1)
-    w, ids = torch.topk(p, K, dim=-1)
-    w = (w / w.sum(dim=-1, keepdim=True)).float().contiguous()
-    ids = ids.to(torch.int32).contiguous()
+    ids, w = route_on_device(logits, K, c.get("routing", "softmax"))
     e_local = E // world
     w1s, w2s, s1s, s2s = [], [], [], []
     for e in range(rank * e_local, (rank + 1) * e_local):
         ge = torch.Generator(device=dev)
         ge.manual_seed(seed * 1000003 + 17 + e)
         for rows, cols, wl, sl in ((2 * I, H, w1s, s1s), (H, I, w2s, s2s)):
-            wf = torch.randn(rows, cols, generator=ge, device=dev) * 0.02
-            if quant == 0:
-                wl.append(wf.to(torch.bfloat16))
-            else:
-                s = wf.abs().amax(dim=1) / 448.0
-                wl.append((wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8))
-                sl.append(s)
-            del wf
+            q, sc = quantise_weight(torch.randn(rows, cols, generator=ge, device=dev) * 0.02, quant)
+            wl.append(q)
+            if sc is not None:
+                sl.append(sc)
     w1, w2 = torch.stack(w1s), torch.stack(w2s)
     s1 = torch.stack(s1s).contiguous() if s1s else None
     s2 = torch.stack(s2s).contiguous() if s2s else None

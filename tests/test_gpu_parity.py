@@ -92,7 +92,7 @@ def test_sort_stage_inside_fused_moe_is_bit_exact():
 
 # ------------------------------------------------------------------------------ fused MoE
 
-@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("quant", [0, 1, 2])
 def test_c0_matches_oracle_and_golden(quant):
     d = O.make_inputs(**{**O.CONFIGS["C0"], "quant": quant})
     got, _ = run_gpu(d)
@@ -102,7 +102,7 @@ def test_c0_matches_oracle_and_golden(quant):
     check(d, got[: len(head)], head)
 
 
-@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("quant", [0, 1, 2])
 @pytest.mark.parametrize("T,H,I,E,K", [(1, 256, 128, 1, 1), (77, 256, 384, 5, 3), (16, 1024, 2048, 8, 2),
                                        (300, 512, 256, 16, 4), (129, 768, 640, 3, 2)])
 def test_ragged_shapes(quant, T, H, I, E, K):
@@ -111,7 +111,7 @@ def test_ragged_shapes(quant, T, H, I, E, K):
     check(d, got, run_oracle(d))
 
 
-@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("quant", [0, 1, 2])
 def test_invalid_expert_ids_are_skipped(quant):
     d = O.make_inputs(64, 256, 256, 6, 3, quant, "softmax", seed=5)
     d["topk_ids"][4, 1] = -1
@@ -133,7 +133,7 @@ def test_empty_experts_and_skew():
 def test_tiny_sigmoid_golden():
     cfg = dict(T=48, H=256, I=256, E=16, K=4, routing="sigmoid")
     g = np.load(os.path.join(GOLD, "tiny_sigmoid.npz"))
-    for quant in (0, 1):
+    for quant in (0, 1, 2):
         d = O.make_inputs(quant=quant, **cfg)
         got, _ = run_gpu(d)
         check(d, got[:16], g[f"out_q{quant}_head"])
@@ -152,7 +152,7 @@ def test_zero_tokens_is_a_no_op():
 
 # ------------------------------------------------------------------------------ properties
 
-@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("quant", [0, 1, 2])
 def test_linear_in_topk_weight_bit_exact(quant):
     d = O.make_inputs(200, 512, 256, 8, 2, quant, "softmax", seed=8)
     a, _ = run_gpu(d)
@@ -162,7 +162,7 @@ def test_linear_in_topk_weight_bit_exact(quant):
     assert (O.bf16_to_f32(b) == 0.25 * O.bf16_to_f32(a)).all()
 
 
-@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("quant", [0, 1, 2])
 def test_token_permutation_permutes_output_bit_exact(quant):
     d = O.make_inputs(300, 256, 256, 8, 2, quant, "softmax", seed=9)
     a, _ = run_gpu(d)
@@ -184,46 +184,47 @@ def test_repeat_runs_are_deterministic():
 
 # ------------------------------------------------------------------------------ full-size configurations
 
-def _full_size(T, H, I, E, K, quant, n_check=24):
-    """Inputs generated on the device at the configuration's full size; the oracle evaluates
-    a random subset of tokens (each token's output depends only on its own row)."""
-    torch.manual_seed(0)
-    dev = "cuda:0"
-    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
-    logits = torch.randn(T, E, device=dev)
-    ids, w = O.route(logits.cpu().numpy(), K, "softmax")
-    if quant == 0:
-        w1 = (torch.randn(E, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)
-        w2 = (torch.randn(E, H, I, device=dev) * 0.02).to(torch.bfloat16)
-        s1 = s2 = None
-        w1_np, w2_np = out_bits(w1), out_bits(w2)
-    else:
-        def qw(rows, cols):
-            wf = torch.randn(E * rows, cols, device=dev) * 0.02
-            s = wf.abs().amax(dim=1) / 448.0
-            q = (wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
-            return q.view(E, rows, cols), s.view(E, rows).contiguous()
-        w1, s1 = qw(2 * I, H)
-        w2, s2 = qw(H, I)
-        w1_np, w2_np = w1.cpu().numpy(), w2.cpu().numpy()
-    args = M.FusedMoeArgs(a=x, g=w1, d=w2, topk_ids=to_dev(ids), topk_weight=to_dev(w), g_scale=s1, d_scale=s2)
+def _full_size(name, n_check=24):
+    """Inputs generated on the device at the configuration's full size (the benchmark's own
+    generator); the oracle evaluates a random subset of tokens (each token's output depends
+    only on its own row)."""
+    import bench
+    c = bench.CONFIGS[name]
+    quant, T = c["quant"], c["T"]
+    d = bench.device_inputs(c, torch.device("cuda:0"))
+    args = M.FusedMoeArgs(a=d["x"], g=d["w1"], d=d["w2"], topk_ids=d["ids"], topk_weight=d["w"],
+                          g_scale=d["s1"], d_scale=d["s2"])
     out = M.fused_moe(traits_for(quant), args)
     torch.cuda.synchronize()
     assert api.check_status(args.workspace) == 0
     sel = np.random.default_rng(1).choice(T, size=min(n_check, T), replace=False).astype(np.int32)
-    ref = O.fused_moe(out_bits(x), w1_np, w2_np, ids, w, quant,
-                      None if s1 is None else s1.cpu().numpy(), None if s2 is None else s2.cpu().numpy(), sel=sel)
-    got = out_bits(out)[sel]
-    check(dict(quant=quant), got, ref)
+    w1 = out_bits(d["w1"]) if quant == 0 else d["w1"].cpu().numpy()
+    w2 = out_bits(d["w2"]) if quant == 0 else d["w2"].cpu().numpy()
+    ref = O.fused_moe(out_bits(d["x"]), w1, w2, d["ids"].cpu().numpy(), d["w"].cpu().numpy(), quant,
+                      None if d["s1"] is None else d["s1"].cpu().numpy(),
+                      None if d["s2"] is None else d["s2"].cpu().numpy(), sel=sel)
+    check(dict(quant=quant), out_bits(out)[sel], ref)
 
 
 def test_full_size_mixtral_prefill_bf16():
-    _full_size(4096, 4096, 14336, 8, 2, 0)
+    _full_size("C1")
 
 
 def test_full_size_mixtral_prefill_fp8():
-    _full_size(8192, 4096, 14336, 8, 2, 1)
+    _full_size("C2")
 
 
 def test_full_size_decode_fp8():
-    _full_size(16, 4096, 14336, 8, 2, 1, n_check=16)
+    _full_size("C3", n_check=16)
+
+
+def test_full_size_deepseek_block_scaled_fp8():
+    _full_size("C4", n_check=16)
+
+
+def test_deepseek_shape_block_scaled_reduced():
+    """The fine-grained configuration (256 experts, top-8, sigmoid routing, 1x128 / 128x128
+    scales) at a reduced token count and expert width that the oracle finishes in seconds."""
+    d = O.make_inputs(512, 1024, 256, 256, 8, 2, "sigmoid", seed=3)
+    got, _ = run_gpu(d)
+    check(d, got, run_oracle(d))

@@ -41,8 +41,6 @@ int validate_traits(const fmoe_traits_c* t) {
   if (t->activation != FMOE_ACT_SILU) return fail(FMOE_ERR_UNSUPPORTED, "only SiLU activation is built");
   if (t->gate_only != 0) return fail(FMOE_ERR_UNSUPPORTED, "gate_only variant is not built");
   if (t->block_m != fmoe::kBlockM) return fail(FMOE_ERR_UNSUPPORTED, "block_m must be %d", fmoe::kBlockM);
-  if (t->quant == FMOE_QUANT_BLOCK128)
-    return fail(FMOE_ERR_UNSUPPORTED, "block128 quantisation is not built yet");
   return FMOE_OK;
 }
 
@@ -55,7 +53,8 @@ int validate_dims(const fmoe_traits_c* t, const fmoe_args_c* a) {
   if (a->I % fmoe::kSlabRows) return fail(FMOE_ERR_UNSUPPORTED, "intermediate size must be a multiple of %d", fmoe::kSlabRows);
   if (a->H % fmoe::kTileN) return fail(FMOE_ERR_UNSUPPORTED, "hidden size must be a multiple of %d", fmoe::kTileN);
   if (static_cast<int64_t>(a->T) * a->K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
-  (void)t;
+  if (t->quant == FMOE_QUANT_BLOCK128 && (a->H % 128 || a->I % 128))
+    return fail(FMOE_ERR_UNSUPPORTED, "block128 needs hidden and intermediate sizes that are multiples of 128");
   return FMOE_OK;
 }
 
@@ -74,10 +73,11 @@ int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
   l.sorted_expert_ids = take(cap / t->block_m * 4);
   l.mblk_cum = take((a->E + 1) * 4);
   l.a_sorted = take(static_cast<uint64_t>(cap) * a->H * (fp8 ? 1 : 2));
-  l.a_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 : 0);
+  const bool blk = t->quant == FMOE_QUANT_BLOCK128;
+  l.a_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 * (blk ? a->H / 128 : 1) : 0);
   l.y = take(static_cast<uint64_t>(cap) * a->I * 2);
   l.y_quant = take(fp8 ? static_cast<uint64_t>(cap) * a->I : 0);
-  l.y_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 : 0);
+  l.y_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 * (blk ? a->I / 128 : 1) : 0);
   l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * 4);
   l.total_bytes = off;
   return FMOE_OK;
@@ -226,13 +226,16 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
                                      sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
                                      mblk_cum, status, stream));
   FMOE_STAGE(1);
-  FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, fp8 ? 1 : 0,
+  const bool blk = traits->quant == FMOE_QUANT_BLOCK128;
+  const int qmode = !fp8 ? 0 : (blk ? 2 : 1);
+  FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
                                      a_sorted, a_scale, stream));
   FMOE_STAGE(2);
 
   fmoe::GemmLaunch g{};
   int drv = 0;
   g.fp8 = fp8;
+  g.block_scale = blk;
   g.num_experts = a.E;
   g.mblk_cum = mblk_cum;
   g.sorted_rows = sorted_rows;
@@ -259,7 +262,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
 
   const void* a2 = y;
   if (fp8) {
-    FMOE_CUDA(fmoe::launch_gather_rows(y, static_cast<int>(plan.cap), a.I, nullptr, num_post_pad, plan.cap, 1,
+    FMOE_CUDA(fmoe::launch_gather_rows(y, static_cast<int>(plan.cap), a.I, nullptr, num_post_pad, plan.cap, qmode,
                                        yq, y_scale, stream));
     a2 = yq;
   }

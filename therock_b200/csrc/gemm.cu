@@ -138,6 +138,32 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   p.status = g.status;
   p.desc_template = g.desc_template_override ? g.desc_template_override : ptx::sw128_kmajor_desc_template();
   p.idesc = g.idesc_override ? g.idesc_override : ptx::make_idesc(g.fp8 ? 0u : 1u, kBlockM, kTileN);
+  if (g.block_scale) {
+    BlockGemmParams bp;
+    bp.g = p;
+    bp.g.a_scale = nullptr;
+    bp.g.b_scale = nullptr;
+    bp.a_scale = g.a_scale;
+    bp.b_scale = g.b_scale;
+    bp.k_blocks = p.k_iters;
+    const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
+    const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
+    static bool configured[kMaxDevices][2] = {{false}};
+    const int dev = current_device();
+    const int which = g.epilogue == kEpiSiluMul ? 0 : 1;
+    if (!configured[dev][which]) {
+      cudaError_t e = which == 0
+          ? cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiSiluMul>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes)
+          : cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiScaledSlots>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+      if (e != cudaSuccess) return e;
+      configured[dev][which] = true;
+    }
+    if (which == 0)
+      fmoe_grouped_gemm_block_kernel<kEpiSiluMul><<<grid, kBlockGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, bp);
+    else
+      fmoe_grouped_gemm_block_kernel<kEpiScaledSlots><<<grid, kBlockGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, bp);
+    return cudaGetLastError();
+  }
   const bool pair = g.mode == 2;
   if (pair) {
     if (!g.idesc_override) p.idesc = ptx::make_idesc(g.fp8 ? 0u : 1u, 2 * kBlockM, kTileN);

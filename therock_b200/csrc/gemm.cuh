@@ -536,4 +536,227 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
 }
 
+// ============================================================================= block-scaled fp8
+// 1x128 activation groups x 128x128 weight blocks: the scale changes every 128 elements of
+// K, which is exactly one pipeline stage of e4m3.  The MMAs of one stage therefore write a
+// *partial* product into one of two 256-column TMEM buffers (no accumulation across stages)
+// and eight epilogue warps promote it: acc += partial * (s_act[row, kb] * s_w[nblock, kb]),
+// with the running sums in registers (128 per thread).  Thread (quadrant q, half h) owns
+// row 32q+lane and, for the first GEMM, gate columns [64h, 64h+64) and the matching up
+// columns, so SiLU(gate)*up needs no exchange; for the second GEMM it owns output channels
+// [128h, 128h+128), one weight-scale block.
+constexpr int kBlockGemmThreads = 64 + 256;   // producer warp, MMA warp, 8 epilogue warps
+constexpr int kBlockStages = 4;
+
+struct BlockGemmParams {
+  GemmParams g;                 // a_scale / b_scale of g are unused here
+  const float* a_scale;         // [cap, k_blocks] per sorted row and 128-wide K group
+  const float* b_scale;         // [E * b_rows_per_expert / 128, k_blocks]
+  int k_blocks;                 // K / 128 (== g.k_iters)
+};
+
+template <int kEpi>
+__global__ void __launch_bounds__(kBlockGemmThreads, 1)
+fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
+                               const __grid_constant__ CUtensorMap tm_b, const BlockGemmParams bp) {
+  const GemmParams& p = bp.g;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* misc = smem + kBlockStages * kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);
+  uint64_t* empty_bar = full_bar + kBlockStages;
+  uint64_t* part_full_bar = empty_bar + kBlockStages;                // [2] partial product ready
+  uint64_t* part_empty_bar = part_full_bar + 2;                      // [2] partial consumed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* cum_s = reinterpret_cast<int*>(misc + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int kUmmaKBytes = 32;
+
+  for (int i = threadIdx.x; i <= p.num_experts; i += kBlockGemmThreads) cum_s[i] = p.mblk_cum[i];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBlockStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&part_full_bar[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&part_empty_bar[b]), 8);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = cum_s[p.num_experts] * p.n_blocks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tm_a);
+      ptx::prefetch_tensormap(&tm_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
+        const int a_row = tc.m_blk * kBlockM;
+        const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
+        const int b_row1 = b_row0 + p.second_slab_offset;
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&full_bar[stage]);
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+          ptx::mbar_arrive_expect_tx(full, kStageBytes);
+          const int kx = k * 128;
+          ptx::tma_load_2d(sa, &tm_a, full, kx, a_row);
+          ptx::tma_load_2d(sb, &tm_b, full, kx, b_row0);
+          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, kx, b_row1);
+          if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x21);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int k = 0; k < p.k_iters; ++k) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&part_empty_bar[buf]), buf_phase ^ 1u, abort_flag) ||
+              !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kTileN);
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint64_t da = ptx::make_smem_desc(p.desc_template, sa);
+          const uint64_t db = ptx::make_smem_desc(p.desc_template, sa + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
+            const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
+            ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, kk ? 1u : 0u);   // fresh partial per stage
+          }
+          ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
+          ptx::umma_commit(ptx::smem_u32(&part_full_bar[buf]));
+          if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
+          if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x22);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    bool ok = true;
+    const int kb_n = bp.k_blocks;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
+      const int slot = tc.m_blk * kBlockM + quad * 32 + lane;
+      const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
+      const float* sa_row = bp.a_scale + static_cast<size_t>(slot) * kb_n;
+      // weight-scale rows (one per 128 weight rows) this thread needs
+      const float* sb0;
+      const float* sb1;
+      if (kEpi == kEpiSiluMul) {
+        sb0 = bp.b_scale + static_cast<size_t>(b_row0 / 128) * kb_n;                          // gate slab
+        sb1 = bp.b_scale + static_cast<size_t>((b_row0 + p.second_slab_offset) / 128) * kb_n; // up slab
+      } else {
+        sb0 = bp.b_scale + static_cast<size_t>(b_row0 / 128 + half) * kb_n;
+        sb1 = sb0;
+      }
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+      // TMEM columns of this thread's two 64-column runs
+      const int col0 = (kEpi == kEpiSiluMul) ? half * 64 : half * 128;
+      const int col1 = (kEpi == kEpiSiluMul) ? kSlabRows + half * 64 : half * 128 + 64;
+      float s_act = __ldg(sa_row), s_b0 = __ldg(sb0), s_b1 = __ldg(sb1);
+      for (int k = 0; k < p.k_iters; ++k) {
+        const float sc0 = s_act * s_b0, sc1 = s_act * s_b1;
+        if (k + 1 < p.k_iters) {       // next block's scales while this one's product is in flight
+          s_act = __ldg(sa_row + k + 1);
+          s_b0 = __ldg(sb0 + k + 1);
+          s_b1 = __ldg(sb1 + k + 1);
+        }
+        if (!ptx::mbar_wait(ptx::smem_u32(&part_full_bar[buf]), buf_phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                               static_cast<uint32_t>(buf * kTileN);
+        uint32_t v[2][32];
+        ptx::tmem_ld_32x32(t_row + col0, v[0]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          ptx::tmem_ld_wait();
+          if (c + 1 < 4) ptx::tmem_ld_32x32(t_row + ((c + 1) < 2 ? col0 + (c + 1) * 32 : col1 + (c - 1) * 32), v[(c + 1) & 1]);
+          const float sc = c < 2 ? sc0 : sc1;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(v[c & 1][j]), sc, acc[c * 32 + j]);
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&part_empty_bar[buf]));
+        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (kEpi == kEpiSiluMul) {
+        // acc[0..63] gate, acc[64..127] up for columns n_blk*128 + half*64 ..
+        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(slot) * p.ld_out +
+                              tc.n_blk * kSlabRows + half * 64;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i0 = q * 8 + 2 * j;
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(silu(acc[i0]) * acc[64 + i0], silu(acc[i0 + 1]) * acc[64 + i0 + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+          reinterpret_cast<uint4*>(yrow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        const int row = p.sorted_rows[slot];
+        if (row >= 0) {
+          const float wt = p.sorted_weights[slot];
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out +
+                                                  tc.n_blk * kTileN + half * 128);
+#pragma unroll
+          for (int q = 0; q < 32; ++q)
+            dst[q] = make_float4(wt * acc[4 * q], wt * acc[4 * q + 1], wt * acc[4 * q + 2], wt * acc[4 * q + 3]);
+        }
+      }
+    }
+    if (!ok && threadIdx.x == 64) atomicExch(p.status, kStatusGemmTimeout | 0x23);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 }  // namespace fmoe

@@ -51,6 +51,8 @@ struct GemmLaunch {
   int ld_out;
   int32_t* status;
   int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
+  bool block_scale;             // fp8 with 1x128 activation groups and 128x128 weight blocks:
+                                // a_scale is [a_rows, K/128], b_scale [E*b_rows/128, K/128]
   int mode;                     // 2 = CTA-pair kernel (cta_group::2), anything else = single-CTA kernel
   uint64_t desc_template_override;  // 0 = the library's descriptor encoding (diagnostics only)
   uint32_t idesc_override;          // 0 = the library's instruction descriptor
