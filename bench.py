@@ -279,6 +279,9 @@ def run_gpu(a, c):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "WARN"      # no version banner: stdout is the one JSON line
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=dev)
     if c["E"] % world or c["T"] % world:
         raise SystemExit("experts and tokens must divide over the ranks")
@@ -298,12 +301,30 @@ def run_gpu(a, c):
             return M.fused_moe(traits, args)
         launches_per_step = M.launches_per_run(traits)
     else:
-        local = ep.make_local_moe(traits, d["w1"], d["w2"], d["s1"], d["s2"])
-        moe = ep.ExpertParallelMoE(c["E"], world, rank, local)
+        # Transport: peer-memory kernels (no host sync) unless FMOE_EP_MODE=nccl or the
+        # peer buffers cannot be set up, in which case NCCL all-to-all collectives are used.
+        ep_transport = "nccl_all_to_all"
+        moe = None
+        if os.environ.get("FMOE_EP_MODE", "peer") != "nccl":
+            try:
+                moe = ep.PeerExpertParallelMoE(c["E"], world, rank, traits, d["w1"], d["w2"], d["s1"], d["s2"],
+                                               tokens_per_rank=T_local, topk=c["K"], hidden=H)
+                ep_transport = "peer_memory"
+            except Exception as exc:  # noqa: BLE001
+                if rank == 0:
+                    print(f"peer-memory expert parallelism unavailable ({exc!r}); using NCCL", file=sys.stderr)
+        ok = torch.tensor([1 if ep_transport == "peer_memory" else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            ep_transport = "nccl_all_to_all"
+            local = ep.make_local_moe(traits, d["w1"], d["w2"], d["s1"], d["s2"])
+            moe = ep.ExpertParallelMoE(c["E"], world, rank, local)
+            launches_per_step = M.launches_per_run(traits) + 2     # + pack and combine kernels
+        else:
+            launches_per_step = moe.launches_per_step
 
         def step():
             return moe.forward(d["x"], d["ids"], d["w"])
-        launches_per_step = M.launches_per_run(traits) + 2     # + pack and combine kernels
 
     def barrier():
         if world > 1:
@@ -353,22 +374,60 @@ def run_gpu(a, c):
         prof.close()
         assert api.check_status(args.workspace) == 0
 
+    # expert-parallel phases (events around plan / pack / dispatch / local operator / return /
+    # combine of a few extra steps, rank 0 only)
+    ep_stage = None
+    if world > 1 and ep_transport == "nccl_all_to_all":
+        barrier()
+        moe.trace = []
+        n_tr = 10
+        for _ in range(n_tr):
+            step()
+        torch.cuda.synchronize()
+        tr, moe.trace = moe.trace, None
+        ep_stage = {}
+        for (n0, e0_), (n1, e1_) in zip(tr[:-1], tr[1:]):
+            if n1 != "start":
+                ep_stage[n1] = ep_stage.get(n1, 0.0) + e0_.elapsed_time(e1_) / n_tr
+
     # end to end: host buffers in, host buffer out, every step
     x_h = d["x"].cpu().pin_memory()
     ids_h = d["ids"].cpu().pin_memory()
     w_h = d["w"].cpu().pin_memory()
     out_h = torch.empty(T_local, H, dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step():
-        d["x"].copy_(x_h, non_blocking=True)
-        d["ids"].copy_(ids_h, non_blocking=True)
-        d["w"].copy_(w_h, non_blocking=True)
-        out = step()
-        out_h.copy_(out, non_blocking=True)
+    # every step copies its inputs in from pinned host memory and its result back out; the
+    # copies of neighbouring steps overlap the compute (therock_b200.api.HostPipeline)
+    depth = 2
+    if world == 1:
+        outs = [torch.empty_like(d["x"]) for _ in range(depth)]
+
+        def pipe_step(x, ids, w, slot):
+            args.a, args.topk_ids, args.topk_weight, args.o = x, ids, w, outs[slot]
+            return M.fused_moe(traits, args, stream=torch.cuda.current_stream())
+    else:
+        def pipe_step(x, ids, w, slot):
+            return moe.forward(x, ids, w)
+    pipe = api.HostPipeline(pipe_step, T_local, H, c["K"], dev, depth=depth)
     n_e2e = max(3, min(a.steps, 100))
-    for _ in range(3):
-        e2e_step()
-    ms_e2e, _, _ = timed(e2e_step, n_e2e)
+
+    def e2e_run(n):
+        for _ in range(n):
+            pipe.submit(x_h, ids_h, w_h, out_h)
+    e2e_run(3)
+    pipe.drain()
+    barrier()
+    e0 = pipe.mark()
+    e2e_run(n_e2e)
+    e1 = pipe.mark()
+    pipe.drain()
+    barrier()
+    ms_e2e_t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_e2e_t, op=dist.ReduceOp.MAX)
+    ms_e2e = float(ms_e2e_t.item())
+    if world == 1:
+        args.a, args.topk_ids, args.topk_weight, args.o = d["x"], d["ids"], d["w"], outs[0]
     if sampler:
         sampler.stop()
 
@@ -392,6 +451,10 @@ def run_gpu(a, c):
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / n_e2e, "steps": n_e2e},
             "gpu_launches": launches_per_step * a.steps, "clocks": clocks}
+    if world > 1:
+        line["config"]["ep_transport"] = ep_transport
+    if ep_stage is not None:
+        line["ep_stage_ms"] = ep_stage
     if stage is not None:
         runs = max(stage["runs"], 1)
         per = {k: stage[k] / runs for k in api.STAGES}

@@ -43,6 +43,7 @@ struct fused_moe_args {
   int intermediate_size = 0;   // per expert, I (W1 has 2I rows)
   int num_experts = 0;
   int topk = 0;
+  const int32_t* num_tokens_dev_ptr = nullptr;  // optional device-side token count (<= num_tokens)
 };
 
 struct stream_config {
@@ -75,6 +76,7 @@ inline void to_c(const fused_moe_args& a, fmoe_args_c* c) {
   c->out = a.o_ptr; c->workspace = a.ws_ptr; c->workspace_bytes = a.ws_bytes;
   c->T = a.num_tokens; c->H = a.hidden_size; c->I = a.intermediate_size;
   c->E = a.num_experts; c->K = a.topk;
+  c->num_tokens_dev = a.num_tokens_dev_ptr;
 }
 }  // namespace fmoe_detail
 

@@ -79,6 +79,10 @@ typedef struct fmoe_args_c {
   uint64_t workspace_bytes;
   int32_t T, H, I, E, K;
   int32_t reserved[3];
+  const int32_t* num_tokens_dev; /* optional device int32: only the first min(T, *num_tokens_dev)
+                                    tokens are processed (T still sizes the workspace); used when
+                                    the batch size is only known on the device, e.g. on the
+                                    receiving side of an expert-parallel dispatch.  NULL = T. */
 } fmoe_args_c;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -183,6 +187,50 @@ FMOE_API int fmoe_gather_rows(const void* src, int32_t n_src, int32_t cols, cons
  * came back through the all-to-all.  No counterpart in the single-GPU reference. */
 FMOE_API int fmoe_combine_rows(const void* rows, const int32_t* index, int32_t T, int32_t K,
                                int32_t H, void* out, void* stream);
+
+/* ---- Expert parallelism over peer memory (one process per GPU; no counterpart in the
+ * single-GPU reference operator).  Every rank holds one buffer of identical layout that all
+ * ranks of the node can address (peer_base[r] = address of rank r's buffer in this process,
+ * a device array of G entries).  All calls are asynchronous on `stream`; none synchronises
+ * with the host. */
+typedef struct fmoe_ep_layout_c {
+  uint64_t flags;    /* int32[G]: barrier epochs written by the peers */
+  uint64_t matrix;   /* int32[G*G]: matrix[s*G+d] = rows rank s sends to rank d this step */
+  uint64_t rows;     /* bf16 [recv_cap, H]: received token rows */
+  uint64_t ids;      /* int32[recv_cap]: local expert id of each received row */
+  uint64_t weights;  /* float[recv_cap]: routing weight of each received row */
+  uint64_t src;      /* int32[recv_cap][2]: (source rank, source send slot) */
+  uint64_t back;     /* bf16 [send_cap, H]: expert outputs returned to this rank */
+  int64_t recv_cap;  /* rows the receive arrays hold (>= all routed pairs of the step) */
+  int64_t send_cap;  /* rows of `back` (>= T*K of this rank) */
+} fmoe_ep_layout_c;
+
+/* Groups this rank's T*K routed pairs by the rank that owns the expert (stable):
+ * order[i] = flat pair index of send slot i, inv_index[pair] = its slot (-1 if dropped),
+ * cum[G+1] = cumulative rows per destination.  scratch_tokens: int32[T*K]. */
+FMOE_API int fmoe_ep_plan(const int32_t* topk_ids, int32_t T, int32_t K, int32_t experts_per_rank,
+                          int32_t G, int32_t* order, int32_t* inv_index, int32_t* cum,
+                          int32_t* scratch_tokens, void* stream);
+/* Writes this rank's row of the count matrix into every rank's buffer. */
+FMOE_API int fmoe_ep_publish(const int32_t* cum, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,
+                             int32_t me, int32_t G, void* stream);
+/* All ranks meet: each writes `epoch` (strictly increasing across calls) into every peer's
+ * flag word and waits, for a bounded time, until all peers wrote theirs; on expiry the
+ * status word receives 0x300 | rank and the kernel returns. */
+FMOE_API int fmoe_ep_barrier(const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
+                             int32_t G, int32_t epoch, int32_t* status, void* stream);
+/* Sends every routed token row, with its local expert id, weight and return address, into
+ * the owner rank's receive arrays; stores this rank's own received-row count in n_recv_dev.
+ * Needs the count matrix complete (publish + barrier). */
+FMOE_API int fmoe_ep_dispatch(const void* x, const int32_t* topk_ids, const float* topk_weight,
+                              int32_t T, int32_t K, int32_t H, int32_t experts_per_rank,
+                              const int32_t* order, const int32_t* cum, const uint64_t* peer_base,
+                              const fmoe_ep_layout_c* lay, int32_t me, int32_t G, int32_t* n_recv_dev,
+                              void* stream);
+/* Sends the expert outputs of the received rows back to the send slot they came from. */
+FMOE_API int fmoe_ep_return(const void* out_rows, int32_t H, const int32_t* n_recv_dev,
+                            const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
+                            int32_t G, void* stream);
 
 /* Number of kernels one fmoe_run launches for these traits (for launch accounting). */
 FMOE_API int fmoe_launches_per_run(const fmoe_traits_c* traits);

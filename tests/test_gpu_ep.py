@@ -61,6 +61,58 @@ def test_single_rank_expert_parallel_path(quant):
     assert _close(got, ref, quant)
 
 
+def _peer_worker(rank, world, port, quant, ret):
+    import torch.distributed as dist
+    from therock_b200 import ep
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        T, H, I, E, K = 256, 512, 256, 8, 2
+        d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=23)
+        d["topk_ids"][::13, 0] = -1
+        e_local = E // world
+        lo = rank * e_local
+        if quant == 0:
+            w1, w2, s1, s2 = bf16_dev(d["w1"][lo:lo + e_local], dev), bf16_dev(d["w2"][lo:lo + e_local], dev), None, None
+        else:
+            w1, w2 = to_dev(d["w1"][lo:lo + e_local], device=dev), to_dev(d["w2"][lo:lo + e_local], device=dev)
+            s1, s2 = to_dev(d["w1_scale"][lo:lo + e_local], device=dev), to_dev(d["w2_scale"][lo:lo + e_local], device=dev)
+        t_local = T // world
+        sl = slice(rank * t_local, (rank + 1) * t_local)
+        moe = ep.PeerExpertParallelMoE(E, world, rank, traits_for(quant), w1, w2, s1, s2,
+                                       tokens_per_rank=t_local, topk=K, hidden=H)
+        x, ids, w = bf16_dev(d["x"][sl], dev), to_dev(d["topk_ids"][sl], device=dev), to_dev(d["topk_w"][sl], device=dev)
+        ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
+                          sel=np.arange(sl.start, sl.stop, dtype=np.int32))
+        ok = True
+        for _ in range(3):      # repeated steps reuse the same peer buffers
+            out = moe.forward(x, ids, w)
+            ok = ok and moe.check_status() == 0 and bool(_close(out_bits(out), ref, quant))
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_two_gpu_peer_memory_expert_parallel(quant):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, quant, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert all(ret.get(r) for r in range(2)), dict(ret)
+
+
 def _worker(rank, world, port, quant, ret):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")

@@ -33,13 +33,20 @@ class _Args(ctypes.Structure):
                 ("out", ctypes.c_void_p), ("workspace", ctypes.c_void_p),
                 ("workspace_bytes", ctypes.c_uint64),
                 ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("I", ctypes.c_int32),
-                ("E", ctypes.c_int32), ("K", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+                ("E", ctypes.c_int32), ("K", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3),
+                ("num_tokens_dev", ctypes.c_void_p)]
 
 
 class _Layout(ctypes.Structure):
     _fields_ = [("capacity", ctypes.c_int64)] + [(n, ctypes.c_uint64) for n in (
         "total_bytes", "meta", "sorted_token_ids", "sorted_weights", "sorted_rows",
         "sorted_expert_ids", "mblk_cum", "a_sorted", "a_scale", "y", "y_quant", "y_scale", "slots")]
+
+
+class EpLayout(ctypes.Structure):
+    """Byte offsets inside the per-rank peer-addressable buffer (fmoe_ep_layout_c)."""
+    _fields_ = [(n, ctypes.c_uint64) for n in ("flags", "matrix", "rows", "ids", "weights", "src", "back")] + \
+               [("recv_cap", ctypes.c_int64), ("send_cap", ctypes.c_int64)]
 
 
 _lib: Optional[ctypes.CDLL] = None
@@ -79,6 +86,13 @@ def lib() -> ctypes.CDLL:
                                        ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         l.fmoe_combine_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                         ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+        vp, i32 = ctypes.c_void_p, ctypes.c_int32
+        l.fmoe_ep_plan.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
+        l.fmoe_ep_publish.argtypes = [vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp]
+        l.fmoe_ep_barrier.argtypes = [vp, ctypes.POINTER(EpLayout), i32, i32, i32, vp, vp]
+        l.fmoe_ep_dispatch.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, ctypes.POINTER(EpLayout),
+                                       i32, i32, vp, vp]
+        l.fmoe_ep_return.argtypes = [vp, i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp]
         _lib = l
     return _lib
 
@@ -129,6 +143,7 @@ class FusedMoeArgs:
     g_scale: Optional[torch.Tensor] = None
     d_scale: Optional[torch.Tensor] = None
     workspace: Optional[torch.Tensor] = None   # uint8, >= fused_moe_workspace_size bytes
+    num_tokens_dev: Optional[torch.Tensor] = None  # int32[1] on the device: process only that many tokens
 
     def to_c(self) -> _Args:
         for name in ("a", "g", "d", "topk_ids", "topk_weight"):
@@ -155,6 +170,7 @@ class FusedMoeArgs:
             c.workspace = self.workspace.data_ptr()
             c.workspace_bytes = self.workspace.numel() * self.workspace.element_size()
         c.T, c.H, c.I, c.E, c.K = T, H, I2 // 2, E, self.topk_ids.shape[1]
+        c.num_tokens_dev = self.num_tokens_dev.data_ptr() if self.num_tokens_dev is not None else None
         return c
 
 
@@ -299,3 +315,67 @@ def fused_moe_static_ws(traits: FusedMoeTraits, args: FusedMoeArgs, stream=None)
     t, a = traits.to_c(), args.to_c()
     _check(lib().fmoe_run_static_ws(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream)))
     return args.o
+
+
+class HostPipeline:
+    """Runs an operator step on host-resident batches with the copies hidden behind compute.
+
+    Three streams: host->device copies of batch i+1 and the device->host copy of result i-1
+    overlap the compute of batch i (`depth` device-side input/output slots).  Every batch is
+    still copied in from pinned host memory and its result copied back; only the waiting is
+    removed.  `step(x, topk_ids, topk_weight, slot) -> out` runs on the compute stream; `slot`
+    (0..depth-1) lets the step keep one preallocated output per slot."""
+
+    def __init__(self, step, T: int, H: int, K: int, device, depth: int = 2):
+        self.step, self.depth, self.device = step, depth, device
+        self.h2d, self.compute, self.d2h = (torch.cuda.Stream(device) for _ in range(3))
+        self.x = [torch.empty(T, H, dtype=torch.bfloat16, device=device) for _ in range(depth)]
+        self.ids = [torch.empty(T, K, dtype=torch.int32, device=device) for _ in range(depth)]
+        self.w = [torch.empty(T, K, dtype=torch.float32, device=device) for _ in range(depth)]
+        self.out = [None] * depth
+        self.in_ready = [torch.cuda.Event() for _ in range(depth)]
+        self.in_free = [torch.cuda.Event() for _ in range(depth)]
+        self.out_ready = [torch.cuda.Event() for _ in range(depth)]
+        self.out_free = [torch.cuda.Event() for _ in range(depth)]
+        self.n = 0
+
+    def submit(self, x_host, ids_host, w_host, out_host):
+        s = self.n % self.depth
+        first = self.n < self.depth
+        with torch.cuda.stream(self.h2d):
+            if not first:
+                self.h2d.wait_event(self.in_free[s])        # the compute that read this slot is done
+            self.x[s].copy_(x_host, non_blocking=True)
+            self.ids[s].copy_(ids_host, non_blocking=True)
+            self.w[s].copy_(w_host, non_blocking=True)
+            self.in_ready[s].record(self.h2d)
+        with torch.cuda.stream(self.compute):
+            self.compute.wait_event(self.in_ready[s])
+            if not first:
+                self.compute.wait_event(self.out_free[s])   # the previous result of this slot left
+            out = self.step(self.x[s], self.ids[s], self.w[s], s)
+            self.out[s] = out
+            self.in_free[s].record(self.compute)
+            self.out_ready[s].record(self.compute)
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(self.out_ready[s])
+            out_host.copy_(out, non_blocking=True)
+            self.out_free[s].record(self.d2h)
+        self.n += 1
+
+    def mark(self) -> "torch.cuda.Event":
+        """Event on the compute stream that follows everything submitted so far on all three
+        streams (for timing a batch of submissions on the device)."""
+        ev_a, ev_b = torch.cuda.Event(), torch.cuda.Event()
+        ev_a.record(self.h2d)
+        ev_b.record(self.d2h)
+        self.compute.wait_event(ev_a)
+        self.compute.wait_event(ev_b)
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(self.compute)
+        return ev
+
+    def drain(self):
+        self.d2h.synchronize()
+        self.compute.synchronize()
+        self.h2d.synchronize()

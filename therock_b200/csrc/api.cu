@@ -224,7 +224,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
 
   FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
                                      sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
-                                     mblk_cum, status, stream));
+                                     mblk_cum, status, stream, a.num_tokens_dev));
   FMOE_STAGE(1);
   const bool blk = traits->quant == FMOE_QUANT_BLOCK128;
   const int qmode = !fp8 ? 0 : (blk ? 2 : 1);
@@ -279,7 +279,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     return fail(FMOE_ERR_CUDA, "gemm2 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
   FMOE_STAGE(5);
 
-  FMOE_CUDA(fmoe::launch_combine(slots, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream));
+  FMOE_CUDA(fmoe::launch_combine(slots, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream, a.num_tokens_dev));
   FMOE_STAGE(6);
 #undef FMOE_STAGE
 

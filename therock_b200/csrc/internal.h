@@ -7,12 +7,16 @@
 namespace fmoe {
 
 // moe_sorting.  All outputs are device pointers; sorted_rows, mblk_cum and status_to_clear
-// (a status word the kernel resets to 0) may be null.
+// (a status word the kernel resets to 0) may be null.  num_tokens_dev (optional) is a device
+// int that lowers the token count below T; id_div > 1 buckets by id / id_div (the rank
+// that owns the expert); inv_out[T*K] receives each pair's slot (-1 if dropped).
 cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight, int T, int K,
                                int E, int block_m, int64_t cap, int32_t* sorted_token_ids,
                                float* sorted_weights, int32_t* sorted_rows,
                                int32_t* sorted_expert_ids, int32_t* num_post_pad,
-                               int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream);
+                               int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream,
+                               const int32_t* num_tokens_dev = nullptr, int id_div = 1,
+                               int32_t* inv_out = nullptr);
 
 // Gather rows of a bf16 matrix into sorted order, optionally quantising each row to e4m3.
 //   src [n_src, cols] bf16; row_ids [cap] (entry >= n_src means pad -> zero row) or null
@@ -25,7 +29,8 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
 
 // out[t, :] = bf16( sum_k slots[t*K + k, :] ) over the k whose expert id lies in [0, E).
 cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
-                           int H, void* out, cudaStream_t stream);
+                           int H, void* out, cudaStream_t stream,
+                           const int32_t* num_tokens_dev = nullptr);
 
 // out[t, :] = bf16( sum_k rows[index[t*K + k], :] ), f32 accumulation, index < 0 skipped;
 // rows are bf16 [*, H].

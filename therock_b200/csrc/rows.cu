@@ -118,8 +118,9 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
 
 __global__ void __launch_bounds__(kRowThreads)
 combine_kernel(const float4* __restrict__ slots, const int32_t* __restrict__ topk_ids, int K, int E,
-               int H, uint2* __restrict__ out) {
+               int H, uint2* __restrict__ out, const int32_t* __restrict__ num_tokens_dev) {
   const int t = blockIdx.x;
+  if (num_tokens_dev && t >= *num_tokens_dev) return;   // rows past the device-side count
   const int nvec = H >> 2;
   for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -186,9 +187,9 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
 }
 
 cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
-                           int H, void* out, cudaStream_t stream) {
+                           int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev) {
   combine_kernel<<<T, kRowThreads, 0, stream>>>(reinterpret_cast<const float4*>(slots), topk_ids, K,
-                                                E, H, reinterpret_cast<uint2*>(out));
+                                                E, H, reinterpret_cast<uint2*>(out), num_tokens_dev);
   return cudaGetLastError();
 }
 

@@ -18,16 +18,20 @@ constexpr int kSortWarps = kSortThreads / 32;
 
 __global__ void __launch_bounds__(kSortThreads, 1)
 moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_weight,
-                   int T, int K, int E, int block_m, int cap,
+                   int T_max, const int32_t* __restrict__ num_tokens_dev, int K, int E, int id_div,
+                   int block_m, int cap,
                    int32_t* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights,
                    int32_t* __restrict__ sorted_rows, int32_t* __restrict__ sorted_expert_ids,
                    int32_t* __restrict__ num_post_pad, int32_t* __restrict__ mblk_cum,
-                   int32_t* __restrict__ status_to_clear) {
+                   int32_t* __restrict__ status_to_clear, int32_t* __restrict__ inv_out) {
   extern __shared__ int32_t sm[];
   int32_t* cnt = sm;                      // [kSortWarps][E] counts, later running offsets
   int32_t* blk_cum = sm + kSortWarps * E; // [E + 1] cumulative padded blocks
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the token count may live on the device (expert-parallel receive side); T_max bounds it
+  const int T = num_tokens_dev ? min(T_max, max(0, *num_tokens_dev)) : T_max;
   const int R = T * K;
+  const int id_limit = E * id_div;       // bucket = id / id_div (id_div > 1: bucket by owner rank)
   // chunk length: multiple of 32 so every warp iterates over whole 32-wide groups
   const int chunk = ((R + kSortWarps - 1) / kSortWarps + 31) & ~31;
   const int r_begin = warp * chunk;
@@ -35,7 +39,7 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
 
   for (int i = tid; i < kSortWarps * E; i += kSortThreads) cnt[i] = 0;
   for (int i = tid; i < cap; i += kSortThreads) {
-    sorted_token_ids[i] = T;
+    sorted_token_ids[i] = T_max;
     if (sorted_weights) sorted_weights[i] = 0.0f;
     if (sorted_rows) sorted_rows[i] = -1;
   }
@@ -48,7 +52,7 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
   for (int r0 = r_begin; r0 < r_end; r0 += 32) {
     const int r = r0 + lane;
     int e = (r < r_end) ? topk_ids[r] : -1;
-    if (e < 0 || e >= E) e = -1;
+    e = (e < 0 || e >= id_limit) ? -1 : e / id_div;
     const unsigned mask = __match_any_sync(0xffffffffu, e);
     if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
     __syncwarp();
@@ -98,7 +102,7 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
   for (int r0 = r_begin; r0 < r_end; r0 += 32) {
     const int r = r0 + lane;
     int e = (r < r_end) ? topk_ids[r] : -1;
-    if (e < 0 || e >= E) e = -1;
+    e = (e < 0 || e >= id_limit) ? -1 : e / id_div;
     const unsigned mask = __match_any_sync(0xffffffffu, e);
     if (e >= 0) {
       const int rank = __popc(mask & ((1u << lane) - 1u));
@@ -106,6 +110,9 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
       sorted_token_ids[pos] = r / K;
       if (sorted_weights) sorted_weights[pos] = topk_weight[r];
       if (sorted_rows) sorted_rows[pos] = r;
+      if (inv_out) inv_out[r] = pos;
+    } else if (inv_out && r < r_end) {
+      inv_out[r] = -1;
     }
     __syncwarp();
     if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
@@ -119,7 +126,8 @@ cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight
                                int E, int block_m, int64_t cap, int32_t* sorted_token_ids,
                                float* sorted_weights, int32_t* sorted_rows,
                                int32_t* sorted_expert_ids, int32_t* num_post_pad,
-                               int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream) {
+                               int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream,
+                               const int32_t* num_tokens_dev, int id_div, int32_t* inv_out) {
   const size_t smem = (static_cast<size_t>(kSortWarps) * E + E + 1) * sizeof(int32_t);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(moe_sorting_kernel,
@@ -128,8 +136,9 @@ cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight
     if (e != cudaSuccess) return e;
   }
   moe_sorting_kernel<<<1, kSortThreads, smem, stream>>>(
-      topk_ids, topk_weight, T, K, E, block_m, static_cast<int>(cap), sorted_token_ids,
-      sorted_weights, sorted_rows, sorted_expert_ids, num_post_pad, mblk_cum, status_to_clear);
+      topk_ids, topk_weight, T, num_tokens_dev, K, E, id_div, block_m, static_cast<int>(cap),
+      sorted_token_ids, sorted_weights, sorted_rows, sorted_expert_ids, num_post_pad, mblk_cum,
+      status_to_clear, inv_out);
   return cudaGetLastError();
 }
 

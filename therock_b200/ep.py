@@ -79,11 +79,20 @@ class ExpertParallelMoE:
         self.local_moe = local_moe
         self.gather = gather or _cuda_gather
         self.combine = combine or _cuda_combine
+        self.trace = None          # set to [] to collect (phase, cuda event) marks per forward
+
+    def _mark(self, name):
+        if self.trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.trace.append((name, ev))
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor) -> torch.Tensor:
         T, H = x.shape
         K = topk_ids.shape[1]
+        self._mark("start")
         plan = plan_dispatch(topk_ids, self.e_local, self.world, self.group)
+        self._mark("plan")
         dev = x.device
         order32 = plan.order.to(torch.int32)
         tok = torch.div(order32, K, rounding_mode="floor").to(torch.int32)
@@ -92,18 +101,24 @@ class ExpertParallelMoE:
         flat_ids = topk_ids.reshape(-1)[plan.order]
         send_meta = torch.stack([(flat_ids % self.e_local).to(torch.float32),
                                  topk_weight.reshape(-1)[plan.order]], dim=1).contiguous()
+        self._mark("pack")
         recv_rows = torch.empty(plan.n_recv, H, dtype=x.dtype, device=dev)
         recv_meta = torch.empty(plan.n_recv, 2, dtype=torch.float32, device=dev)
         _a2a(recv_rows, send_rows, plan.recv_counts, plan.send_counts, self.world, self.group)
         _a2a(recv_meta, send_meta, plan.recv_counts, plan.send_counts, self.world, self.group)
+        self._mark("dispatch")
         # local experts: every received row is a token with a single expert
         ids_local = recv_meta[:, 0].to(torch.int32).reshape(-1, 1).contiguous()
         w_local = recv_meta[:, 1].reshape(-1, 1).contiguous()
         part = self.local_moe(recv_rows, ids_local, w_local) if plan.n_recv > 0 else recv_rows
+        self._mark("local_moe")
         # return trip and ordered reduction
         back = torch.empty(plan.n_send, H, dtype=x.dtype, device=dev)
         _a2a(back, part, plan.send_counts, plan.recv_counts, self.world, self.group)
-        return self.combine(back, plan.inv_index, T, K)
+        self._mark("return")
+        out = self.combine(back, plan.inv_index, T, K)
+        self._mark("combine")
+        return out
 
 
 def _cuda_gather(src: torch.Tensor, row_ids: torch.Tensor) -> torch.Tensor:
@@ -141,3 +156,109 @@ def make_local_moe(traits, w1_local, w2_local, w1_scale=None, w2_scale=None):
         return api.fused_moe(traits, args)
 
     return run
+
+
+class PeerExpertParallelMoE:
+    """Expert parallelism over NVLink peer memory with no host synchronisation.
+
+    Every rank owns one peer-addressable buffer (torch symmetric memory, NVLS multicast not
+    used).  A step is a fixed sequence of asynchronous launches on the current stream:
+
+        plan -> publish counts -> barrier -> dispatch (P2P stores of rows + metadata into the
+        owner's receive arrays) -> barrier -> local fused_moe on the received rows (row count
+        read on the device) -> return (P2P stores into the source's slots) -> barrier ->
+        ordered k-sum.
+
+    The barriers are flag kernels with bounded spins; a rank that never arrives shows up in
+    `status` instead of hanging the GPU.
+    """
+
+    def __init__(self, num_experts: int, world: int, rank: int, traits, w1_local, w2_local,
+                 w1_scale=None, w2_scale=None, *, tokens_per_rank: int, topk: int, hidden: int, group=None):
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        from . import api
+        if num_experts % world:
+            raise ValueError("experts must divide evenly over ranks")
+        self.api, self.traits = api, traits
+        self.E, self.world, self.rank = num_experts, world, rank
+        self.e_local = num_experts // world
+        self.T, self.K, self.H = tokens_per_rank, topk, hidden
+        dev = w1_local.device
+        R = tokens_per_rank * topk
+        recv_cap = R * world
+
+        def al(n):
+            return (n + 255) // 256 * 256
+        lay = api.EpLayout()
+        off = 0
+        for name, nbytes in (("flags", world * 4), ("matrix", world * world * 4),
+                             ("rows", recv_cap * hidden * 2), ("ids", recv_cap * 4), ("weights", recv_cap * 4),
+                             ("src", recv_cap * 8), ("back", R * hidden * 2)):
+            setattr(lay, name, off)
+            off = al(off + nbytes)
+        lay.recv_cap, lay.send_cap = recv_cap, R
+        self.lay = lay
+        group = group or dist.group.WORLD
+        self.buf = symm.empty(off, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        self.hdl = symm.rendezvous(self.buf, group)
+        self.peer_base = torch.tensor(list(self.hdl.buffer_ptrs), dtype=torch.int64, device=dev)
+        dist.barrier(group=group)
+
+        def view(name, n, dt):
+            o = getattr(lay, name)
+            return self.buf[o:o + n * torch.empty((), dtype=dt).element_size()].view(dt)
+        self.rows = view("rows", recv_cap * hidden, torch.bfloat16).view(recv_cap, hidden)
+        self.ids = view("ids", recv_cap, torch.int32).view(recv_cap, 1)
+        self.wts = view("weights", recv_cap, torch.float32).view(recv_cap, 1)
+        self.back = view("back", R * hidden, torch.bfloat16).view(R, hidden)
+        self.order = torch.empty(R, dtype=torch.int32, device=dev)
+        self.inv = torch.empty(R, dtype=torch.int32, device=dev)
+        self.cum = torch.zeros(world + 1, dtype=torch.int32, device=dev)
+        self.scratch = torch.empty(R, dtype=torch.int32, device=dev)
+        self.n_recv = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out_rows = torch.empty(recv_cap, hidden, dtype=torch.bfloat16, device=dev)
+        self.args = api.FusedMoeArgs(a=self.rows, g=w1_local, d=w2_local, topk_ids=self.ids,
+                                     topk_weight=self.wts, o=self.out_rows, g_scale=w1_scale,
+                                     d_scale=w2_scale, num_tokens_dev=self.n_recv)
+        self.args.workspace = torch.empty(api.fused_moe_workspace_size(traits, self.args), dtype=torch.uint8,
+                                          device=dev)
+        self.epoch = 0
+        self._ctypes = ctypes
+        self.launches_per_step = 8 + api.launches_per_run(traits)
+
+    def _barrier(self, stream):
+        self.epoch += 1
+        self.api._check(self.api.lib().fmoe_ep_barrier(self.peer_base.data_ptr(), self._ctypes.byref(self.lay),
+                                                       self.rank, self.world, self.epoch, self.status.data_ptr(),
+                                                       stream))
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        api, lib, by = self.api, self.api.lib(), self._ctypes.byref
+        T, K, H, G = self.T, self.K, self.H, self.world
+        assert x.shape == (T, H) and topk_ids.shape == (T, K)
+        st = api._stream_ptr(None)
+        pb = self.peer_base.data_ptr()
+        api._check(lib.fmoe_ep_plan(topk_ids.data_ptr(), T, K, self.e_local, G, self.order.data_ptr(),
+                                    self.inv.data_ptr(), self.cum.data_ptr(), self.scratch.data_ptr(), st))
+        api._check(lib.fmoe_ep_publish(self.cum.data_ptr(), pb, by(self.lay), self.rank, G, st))
+        self._barrier(st)
+        api._check(lib.fmoe_ep_dispatch(x.data_ptr(), topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, H,
+                                        self.e_local, self.order.data_ptr(), self.cum.data_ptr(), pb,
+                                        by(self.lay), self.rank, G, self.n_recv.data_ptr(), st))
+        self._barrier(st)
+        api.fused_moe(self.traits, self.args)
+        api._check(lib.fmoe_ep_return(self.out_rows.data_ptr(), H, self.n_recv.data_ptr(), pb, by(self.lay),
+                                      self.rank, G, st))
+        self._barrier(st)
+        return api.combine_rows(self.back, self.inv, T, K, out=out)
+
+    def check_status(self) -> int:
+        torch.cuda.synchronize()
+        return int(self.status.item()) | self.api.check_status(self.args.workspace)
