@@ -52,12 +52,12 @@ def quantise_weight(wf, quant):
     if quant == 1:
         s = wf.abs().amax(dim=1) / 448.0
         s = torch.where(s > 0, s, torch.ones_like(s))
-        return (wf / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8), s
+        return (wf * (1.0 / s)[:, None]).to(torch.float8_e4m3fn).view(torch.uint8), s
     rows, cols = wf.shape
     blocks = wf.view(rows // 128, 128, cols // 128, 128)
     s = blocks.abs().amax(dim=(1, 3)) / 448.0
     s = torch.where(s > 0, s, torch.ones_like(s))
-    q = (blocks / s[:, None, :, None]).to(torch.float8_e4m3fn).view(torch.uint8).view(rows, cols)
+    q = (blocks * (1.0 / s)[:, None, :, None]).to(torch.float8_e4m3fn).view(torch.uint8).view(rows, cols)
     return q, s.contiguous()
 
 
@@ -280,7 +280,8 @@ def run_gpu(a, c):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
-            os.environ["NCCL_DEBUG"] = "WARN"      # no version banner: stdout is the one JSON line
+            os.environ["NCCL_DEBUG"] = "WARN"
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries only the JSON line
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=dev)
     if c["E"] % world or c["T"] % world:

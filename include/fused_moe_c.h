@@ -105,6 +105,14 @@ FMOE_API int fmoe_sort(const int32_t* topk_ids, const float* topk_weight, int32_
                        float* sorted_weights, int32_t* sorted_expert_ids,
                        int32_t* num_tokens_post_pad, void* stream);
 
+/* Router: logits [T, E] f32 -> topk_ids [T, K] int32, topk_weight [T, K] f32 on the device.
+ * mode 0 = softmax over the experts, 1 = sigmoid; the K best scores are kept (ties to the
+ * lower expert index) and divided by their sum.  E <= 1024, K <= 32.  This is the input
+ * preparation the ck_tile example drivers do on the host before calling fused_moe; here it
+ * is a kernel so logits -> fused_moe needs no host step. */
+FMOE_API int fmoe_route(const float* logits, int32_t T, int32_t E, int32_t K, int32_t mode,
+                        int32_t* topk_ids, float* topk_weight, void* stream);
+
 /* Byte offsets of the regions fmoe_run keeps in the workspace.  After a run has completed
  * the regions hold that run's intermediates, which lets a caller (or a test) inspect every
  * stage: meta[0] = num_tokens_post_pad, meta[1] = device status word. */

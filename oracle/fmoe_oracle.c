@@ -25,6 +25,7 @@
  *               id T and weight 0; ids outside [0,E) are dropped.
  *   bf16 path : gate/up = x . W1^T accumulated in f32; y = silu(gate)*up in f32, rounded
  *               to bf16; o = y . W2^T in f32; out = bf16( sum_k w_k * o_k ), k ascending.
+ *   quantise  : s = absmax/448 (1 if all zero), r = 1/s in f32, q = e4m3(v * r).
  *   fp8 paths : operands quantised (activations dynamically, weights given quantised),
  *               integer-exact products accumulated in f32, scales applied after the
  *               accumulation (per token x per channel) or per 128-deep K block
@@ -118,7 +119,8 @@ ORC_API void orc_e4m3_to_f32(const uint8_t* in, float* out, int64_t n) {
 }
 
 /* Quantise rows of an f32 matrix to e4m3 with one scale per `group` consecutive columns:
- * scale = absmax/448 (1.0 when the group is all zero), q = e4m3(v / scale).
+ * scale = absmax/448 (1.0 when the group is all zero), q = e4m3(v * (1/scale)), the
+ * reciprocal rounded once to f32.
  * group == cols gives the per-token (or per-output-channel) mode, group == 128 the 1x128
  * mode.  scales has rows * (cols/group) entries. */
 ORC_API void orc_quant_rows_e4m3(const float* in, int64_t rows, int64_t cols, int64_t group,
@@ -134,9 +136,10 @@ ORC_API void orc_quant_rows_e4m3(const float* in, int64_t rows, int64_t cols, in
         if (a > amax) amax = a;
       }
       float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+      float inv = 1.0f / s;
       scales[r * ng + g] = s;
       uint8_t* o = q + r * cols + g * group;
-      for (int64_t c = 0; c < group; ++c) o[c] = f32_to_e4m3(p[c] / s);
+      for (int64_t c = 0; c < group; ++c) o[c] = f32_to_e4m3(p[c] * inv);
     }
   }
 }
@@ -155,11 +158,12 @@ ORC_API void orc_quant_blocks_e4m3(const float* in, int64_t rows, int64_t cols,
         if (a > amax) amax = a;
       }
     float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+    float inv = 1.0f / s;
     scales[b] = s;
     for (int64_t r = 0; r < 128; ++r)
       for (int64_t c = 0; c < 128; ++c) {
         int64_t i = (br * 128 + r) * cols + bc * 128 + c;
-        q[i] = f32_to_e4m3(in[i] / s);
+        q[i] = f32_to_e4m3(in[i] * inv);
       }
   }
 }
@@ -327,9 +331,10 @@ static void expert_forward(int quant, int H, int I, const float* xin, const floa
         if (a > amax) amax = a;
       }
       float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+      float inv = 1.0f / s;
       ys[g] = s;
       for (int c = 0; c < group; ++c)
-        yq[g * group + c] = g_e4m3_lut[f32_to_e4m3(y[g * group + c] / s)];
+        yq[g * group + c] = g_e4m3_lut[f32_to_e4m3(y[g * group + c] * inv)];
     }
   }
   /* gemm2 */

@@ -259,7 +259,8 @@ def np_quant(a: np.ndarray, group: int):
     g = a.reshape(rows, cols // group, group).astype(np.float32)
     amax = np.abs(g).max(axis=2)
     s = np.where(amax > 0, amax / np.float32(448.0), np.float32(1.0)).astype(np.float32)
-    q = np_f32_to_e4m3((g / s[:, :, None]).astype(np.float32))
+    inv = (np.float32(1.0) / s).astype(np.float32)
+    q = np_f32_to_e4m3((g * inv[:, :, None]).astype(np.float32))
     return q.reshape(rows, cols), s
 
 

@@ -228,3 +228,41 @@ def test_deepseek_shape_block_scaled_reduced():
     d = O.make_inputs(512, 1024, 256, 256, 8, 2, "sigmoid", seed=3)
     got, _ = run_gpu(d)
     check(d, got, run_oracle(d))
+
+
+# ------------------------------------------------------------------------------ router
+
+@pytest.mark.parametrize("T,E,K,mode", [(128, 8, 2, "softmax"), (4096, 8, 2, "softmax"), (8192, 256, 8, "sigmoid"),
+                                        (33, 300, 5, "softmax"), (7, 17, 17, "sigmoid"), (1, 1, 1, "softmax")])
+def test_router_matches_oracle(T, E, K, mode):
+    logits = O.normal((T, E), 5, 4)
+    if T > 4:
+        logits[3, :] = 0.5                      # full tie: the K lowest indices win
+        logits[2, E - 1] = logits[2, 0]
+    ref_ids, ref_w = O.route(logits, K, mode)
+    ids, w = M.route(to_dev(logits), K, mode)
+    torch.cuda.synchronize()
+    ids, w = ids.cpu().numpy(), w.cpu().numpy()
+    same = ids == ref_ids
+    if not same.all():
+        # a different pick is only acceptable between scores that are equal to rounding
+        s = logits if mode == "sigmoid" else logits - logits.max(axis=1, keepdims=True)
+        t_idx, k_idx = np.nonzero(~same)
+        assert np.abs(s[t_idx, ids[t_idx, k_idx]] - s[t_idx, ref_ids[t_idx, k_idx]]).max() < 1e-5
+        assert (~same).mean() < 1e-3
+    np.testing.assert_allclose(w[same], ref_w[same], rtol=2e-6, atol=1e-7)
+    if T > 4:
+        assert ids[3].tolist() == list(range(K))
+    np.testing.assert_allclose(w.sum(axis=1), 1.0, rtol=1e-5)
+
+
+def test_router_feeds_fused_moe():
+    d = O.make_inputs(**O.CONFIGS["C0"])
+    ids, w = M.route(to_dev(d["logits"]), 2, "softmax")
+    args = args_for(d)
+    args.topk_ids, args.topk_weight = ids, w
+    out = M.fused_moe(traits_for(0), args)
+    torch.cuda.synchronize()
+    d2 = dict(d)
+    d2["topk_ids"], d2["topk_w"] = ids.cpu().numpy(), w.cpu().numpy()
+    check(d2, out_bits(out), run_oracle(d2))

@@ -6,7 +6,7 @@ no Python or CPU fallback: importing the operator without the built library rais
 """
 from .api import (FusedMoeTraits, FusedMoeArgs, fused_moe, fused_moe_workspace_size,  # noqa: F401
                   moe_sorting, sort_capacity, workspace_layout, launches_per_run, lib, LIB_PATH,
-                  FmoeError)
+                  FmoeError, route)
 
 __all__ = ["FusedMoeTraits", "FusedMoeArgs", "fused_moe", "fused_moe_workspace_size", "moe_sorting",
-           "sort_capacity", "workspace_layout", "launches_per_run", "lib", "LIB_PATH", "FmoeError"]
+           "sort_capacity", "workspace_layout", "launches_per_run", "lib", "LIB_PATH", "FmoeError", "route"]

@@ -87,6 +87,7 @@ def lib() -> ctypes.CDLL:
         l.fmoe_combine_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                         ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
         vp, i32 = ctypes.c_void_p, ctypes.c_int32
+        l.fmoe_route.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp]
         l.fmoe_ep_plan.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
         l.fmoe_ep_publish.argtypes = [vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp]
         l.fmoe_ep_barrier.argtypes = [vp, ctypes.POINTER(EpLayout), i32, i32, i32, vp, vp]
@@ -379,3 +380,15 @@ class HostPipeline:
         self.d2h.synchronize()
         self.compute.synchronize()
         self.h2d.synchronize()
+
+
+def route(logits: torch.Tensor, topk: int, mode: str = "softmax", stream=None):
+    """Router kernel: logits [T, E] f32 (CUDA) -> (topk_ids int32 [T, K], topk_weight f32 [T, K])."""
+    if not (logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous()):
+        raise FmoeError(-1, "logits must be a contiguous CUDA float32 tensor")
+    T, E = logits.shape
+    ids = torch.empty(T, topk, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, topk, dtype=torch.float32, device=logits.device)
+    _check(lib().fmoe_route(logits.data_ptr(), T, E, topk, 0 if mode == "softmax" else 1, ids.data_ptr(),
+                            w.data_ptr(), _stream_ptr(stream)))
+    return ids, w

@@ -263,7 +263,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   const void* a2 = y;
   if (fp8) {
     FMOE_CUDA(fmoe::launch_gather_rows(y, static_cast<int>(plan.cap), a.I, nullptr, num_post_pad, plan.cap, qmode,
-                                       yq, y_scale, stream));
+                                       yq, y_scale, stream, sorted_rows));
     a2 = yq;
   }
   FMOE_STAGE(4);

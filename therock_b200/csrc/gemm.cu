@@ -136,6 +136,11 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   p.out = g.out;
   p.ld_out = g.ld_out;
   p.status = g.status;
+  {
+    static int dbg = -1;       // FMOE_DEBUG_FLAGS: timing experiments only
+    if (dbg < 0) { const char* e = getenv("FMOE_DEBUG_FLAGS"); dbg = e ? atoi(e) : 0; }
+    p.debug_flags = static_cast<uint32_t>(dbg);
+  }
   p.desc_template = g.desc_template_override ? g.desc_template_override : ptx::sw128_kmajor_desc_template();
   p.idesc = g.idesc_override ? g.idesc_override : ptx::make_idesc(g.fp8 ? 0u : 1u, kBlockM, kTileN);
   if (g.block_scale) {

@@ -55,6 +55,8 @@ struct GemmParams {
   int* status;                  // device status word
   uint64_t desc_template;       // shared-memory matrix descriptor without the address
   uint32_t idesc;               // tcgen05 instruction descriptor
+  uint32_t debug_flags;         // diagnostics only (results are invalid when set): bit 0 = the
+                                // epilogue skips its work, bit 1 = no MMA is issued
 };
 
 struct TileCoord {
@@ -91,6 +93,8 @@ template <int kEpi>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_row, int slot, int n_blk,
                                               const float* bs0, const float* bs1, float a_s) {
   if (kEpi == kEpiSiluMul) {
+    // pad slots carry no token: their rows of y are never used, so they are not stored
+    const bool live = p.sorted_rows[slot] >= 0;
     __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) +
                           static_cast<size_t>(slot) * p.ld_out + n_blk * kSlabRows;
     // Software pipeline over 32-column chunks: the TMEM loads of chunk c+1 are in flight
@@ -128,10 +132,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
         packed[2 * q] = *reinterpret_cast<uint32_t*>(&v0);
         packed[2 * q + 1] = *reinterpret_cast<uint32_t*>(&v1);
       }
-      uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+      if (live) {
+        uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
     }
   } else {
     const int row = p.sorted_rows[slot];
@@ -274,6 +280,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             // advancing K inside the swizzle row = advancing the start address
             const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
             const uint32_t accum = (k | kk) ? 1u : 0u;
+            if (p.debug_flags & 2u) continue;
             if (kFp8) ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, accum);
             else      ptx::umma_f16(d_tmem, da + adv, db + adv, p.idesc, accum);
           }
@@ -309,7 +316,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
+      if (!(p.debug_flags & 1u)) epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&acc_empty_bar[acc]));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -478,6 +485,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
             const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
             const uint32_t accum = (k | kk) ? 1u : 0u;
+            if (p.debug_flags & 2u) continue;
             if (kFp8) ptx::umma_f8_pair(d_tmem, da + adv, db + adv, p.idesc, accum);
             else      ptx::umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, accum);
           }
@@ -517,7 +525,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      if (valid) epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
+      if (valid && !(p.debug_flags & 1u)) epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_u32(&acc_empty_bar[acc]), 0));
@@ -721,7 +729,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
       }
       if (!ok) break;
-      if (kEpi == kEpiSiluMul) {
+      if (kEpi == kEpiSiluMul && p.sorted_rows[slot] >= 0) {
         // acc[0..63] gate, acc[64..127] up for columns n_blk*128 + half*64 ..
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(slot) * p.ld_out +
                               tc.n_blk * kSlabRows + half * 64;
@@ -736,7 +744,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           reinterpret_cast<uint4*>(yrow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
         }
-      } else {
+      } else if (kEpi == kEpiScaledSlots) {
         const int row = p.sorted_rows[slot];
         if (row >= 0) {
           const float wt = p.sorted_weights[slot];

@@ -23,9 +23,10 @@ cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight
 //   for identity; only slots < *num_post_pad are touched.
 //   quant 0: dst bf16 [cap, cols].  quant 1: dst e4m3 [cap, cols] + scales[cap] (one per
 //   row).  quant 2: dst e4m3 + scales [cap, cols/128] (one per 128 columns).
+//   live_ids (optional, [cap]): slots whose entry is negative are skipped entirely.
 cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
-                               float* scales, cudaStream_t stream);
+                               float* scales, cudaStream_t stream, const int32_t* live_ids = nullptr);
 
 // out[t, :] = bf16( sum_k slots[t*K + k, :] ) over the k whose expert id lies in [0, E).
 cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,

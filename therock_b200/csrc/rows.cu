@@ -30,13 +30,13 @@ __device__ __forceinline__ uint32_t e4m3_byte(float x) {
   return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
 }
 
-// quantise 8 floats with one scale into 8 bytes
-__device__ __forceinline__ uint2 quant8(const float (&f)[8], float scale) {
+// quantise 8 floats into 8 bytes: q = e4m3(v * inv_scale), inv_scale = 1/scale rounded once
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float inv_scale) {
   uint32_t lo = 0, hi = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    lo |= e4m3_byte(f[i] / scale) << (8 * i);
-    hi |= e4m3_byte(f[4 + i] / scale) << (8 * i);
+    lo |= e4m3_byte(f[i] * inv_scale) << (8 * i);
+    hi |= e4m3_byte(f[4 + i] * inv_scale) << (8 * i);
   }
   return make_uint2(lo, hi);
 }
@@ -46,9 +46,12 @@ template <int kQuant>
 __global__ void __launch_bounds__(kRowThreads)
 gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
                    const int32_t* __restrict__ row_ids, const int32_t* __restrict__ num_post_pad,
-                   void* __restrict__ dst, float* __restrict__ scales) {
+                   void* __restrict__ dst, float* __restrict__ scales,
+                   const int32_t* __restrict__ live_ids) {
   const int slot = blockIdx.x;
   if (slot >= *num_post_pad) return;
+  // identity mode (quantising the intermediate): slots without a token are skipped outright
+  if (live_ids != nullptr && live_ids[slot] < 0) return;
   const int row = row_ids ? row_ids[slot] : slot;
   const int nvec = cols >> 3;                       // 8 bf16 per 16-byte vector
   const bool pad = row < 0 || row >= n_src;
@@ -63,16 +66,34 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
 
   uint2* d = reinterpret_cast<uint2*>(dst) + static_cast<size_t>(slot) * nvec;
   if (kQuant == 1) {
-    // per-row scale: block-wide absmax, then a second pass (the row is L1/L2 resident)
+    // per-row scale: the row is read once into registers (up to kMaxVec vectors per thread,
+    // i.e. rows of up to 16384 elements), reduced block-wide, then quantised from registers;
+    // longer rows fall back to a second read.
+    constexpr int kMaxVec = 8;
     __shared__ float warp_max[kRowThreads / 32];
     __shared__ float row_scale;
+    const bool in_regs = nvec <= kMaxVec * kRowThreads;
+    uint4 held[kMaxVec];
     float amax = 0.0f;
     if (!pad) {
-      for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
-        float f[8];
-        unpack8(s[i], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      for (int j = 0; j < kMaxVec; ++j) {
+        const int i = threadIdx.x + j * kRowThreads;
+        if (in_regs && i < nvec) {
+          held[j] = s[i];
+          float f[8];
+          unpack8(held[j], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+        }
+      }
+      if (!in_regs) {
+        for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+          float f[8];
+          unpack8(s[i], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+        }
       }
     }
 #pragma unroll
@@ -88,12 +109,25 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
       scales[slot] = sc;
     }
     __syncthreads();
-    const float sc = row_scale;
-    for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
-      if (pad) { d[i] = make_uint2(0, 0); continue; }
-      float f[8];
-      unpack8(s[i], f);
-      d[i] = quant8(f, sc);
+    const float sc = 1.0f / row_scale;
+    if (pad) {
+      for (int i = threadIdx.x; i < nvec; i += kRowThreads) d[i] = make_uint2(0, 0);
+    } else if (in_regs) {
+#pragma unroll
+      for (int j = 0; j < kMaxVec; ++j) {
+        const int i = threadIdx.x + j * kRowThreads;
+        if (i < nvec) {
+          float f[8];
+          unpack8(held[j], f);
+          d[i] = quant8(f, sc);
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+        float f[8];
+        unpack8(s[i], f);
+        d[i] = quant8(f, sc);
+      }
     }
   } else {
     // one scale per 128 columns = 16 vectors = a 16-lane group
@@ -111,7 +145,7 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
       const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
       if (!live) continue;
       if ((i & 15) == 0) scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
-      d[i] = quant8(f, sc);
+      d[i] = quant8(f, 1.0f / sc);
     }
   }
 }
@@ -174,15 +208,15 @@ cudaError_t launch_combine_rows(const void* rows, const int32_t* index, int T, i
 
 cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
-                               float* scales, cudaStream_t stream) {
+                               float* scales, cudaStream_t stream, const int32_t* live_ids) {
   const dim3 grid(static_cast<unsigned>(cap));
   const uint4* s = reinterpret_cast<const uint4*>(src);
   if (quant == 0)
-    gather_rows_kernel<0><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales);
+    gather_rows_kernel<0><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   else if (quant == 1)
-    gather_rows_kernel<1><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales);
+    gather_rows_kernel<1><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   else
-    gather_rows_kernel<2><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales);
+    gather_rows_kernel<2><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   return cudaGetLastError();
 }
 
