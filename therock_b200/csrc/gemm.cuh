@@ -553,8 +553,10 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
 // row 32q+lane and, for the first GEMM, gate columns [64h, 64h+64) and the matching up
 // columns, so SiLU(gate)*up needs no exchange; for the second GEMM it owns output channels
 // [128h, 128h+128), one weight-scale block.
-constexpr int kBlockGemmThreads = 64 + 256;   // producer warp, MMA warp, 8 epilogue warps
+constexpr int kBlockGemmThreads = 384;   // warpgroup 0: producer + MMA (+2 idle warps); warpgroups 1, 2: epilogue
 constexpr int kBlockStages = 4;
+constexpr int kBlockThinRegs = 40;       // registers per thread kept by warpgroup 0
+constexpr int kBlockFatRegs = 216;       // registers per thread taken by the epilogue warpgroups
 
 struct BlockGemmParams {
   GemmParams g;                 // a_scale / b_scale of g are unused here
@@ -608,8 +610,10 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = cum_s[p.num_experts] * p.n_blocks;
 
-  if (warp == 0) {
-    if (lane == 0) {
+  if (warp < 4) {
+    // -------------------------------------------------------------- warpgroup 0: data movement and MMA issue
+    ptx::setmaxnreg_dec<kBlockThinRegs>();
+    if (warp == 0 && lane == 0) {
       ptx::prefetch_tensormap(&tm_a);
       ptx::prefetch_tensormap(&tm_b);
       int stage = 0;
@@ -637,9 +641,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
       }
       if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x21);
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -671,8 +673,10 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x22);
     }
   } else {
+    // -------------------------------------------------------------- warpgroups 1, 2: promotion + epilogue
+    ptx::setmaxnreg_inc<kBlockFatRegs>();
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 4) >> 2;
     int buf = 0;
     uint32_t buf_phase = 0;
     bool ok = true;
@@ -682,7 +686,6 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int slot = tc.m_blk * kBlockM + quad * 32 + lane;
       const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
       const float* sa_row = bp.a_scale + static_cast<size_t>(slot) * kb_n;
-      // weight-scale rows (one per 128 weight rows) this thread needs
       const float* sb0;
       const float* sb1;
       if (kEpi == kEpiSiluMul) {
@@ -692,15 +695,16 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         sb0 = bp.b_scale + static_cast<size_t>(b_row0 / 128 + half) * kb_n;
         sb1 = sb0;
       }
-      float acc[128];
+      uint64_t acc[64];          // 128 f32 running sums, two per register pair
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+      for (int j = 0; j < 64; ++j) acc[j] = 0ull;
       // TMEM columns of this thread's two 64-column runs
       const int col0 = (kEpi == kEpiSiluMul) ? half * 64 : half * 128;
       const int col1 = (kEpi == kEpiSiluMul) ? kSlabRows + half * 64 : half * 128 + 64;
       float s_act = __ldg(sa_row), s_b0 = __ldg(sb0), s_b1 = __ldg(sb1);
       for (int k = 0; k < p.k_iters; ++k) {
         const float sc0 = s_act * s_b0, sc1 = s_act * s_b1;
+        const uint64_t sc0_2 = ptx::pack2(sc0, sc0), sc1_2 = ptx::pack2(sc1, sc1);
         if (k + 1 < p.k_iters) {       // next block's scales while this one's product is in flight
           s_act = __ldg(sa_row + k + 1);
           s_b0 = __ldg(sb0 + k + 1);
@@ -714,23 +718,50 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                static_cast<uint32_t>(buf * kTileN);
         uint32_t v[2][32];
-        ptx::tmem_ld_32x32(t_row + col0, v[0]);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        const bool dbg_no_ld = p.debug_flags & 4u, dbg_no_fma = p.debug_flags & 1u, dbg_scalar = p.debug_flags & 8u;
+        if (!dbg_no_ld) {
+          ptx::tmem_ld_32x32(t_row + col0, v[0]);
+          ptx::tmem_ld_32x32(t_row + col0 + 32, v[1]);
           ptx::tmem_ld_wait();
-          if (c + 1 < 4) ptx::tmem_ld_32x32(t_row + ((c + 1) < 2 ? col0 + (c + 1) * 32 : col1 + (c - 1) * 32), v[(c + 1) & 1]);
-          const float sc = c < 2 ? sc0 : sc1;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(v[c & 1][j]), sc, acc[c * 32 + j]);
         }
+        if (!dbg_no_fma && !dbg_scalar) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ptx::fma2(acc[j], v[0][2 * j], v[0][2 * j + 1], sc0_2);
+        }
+        if (!dbg_no_ld) ptx::tmem_ld_32x32(t_row + col1, v[0]);
+        if (!dbg_no_fma && !dbg_scalar) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ptx::fma2(acc[16 + j], v[1][2 * j], v[1][2 * j + 1], sc0_2);
+        }
+        if (!dbg_no_ld) {
+          ptx::tmem_ld_32x32(t_row + col1 + 32, v[1]);
+          ptx::tmem_ld_wait();
+        }
+        // all four loads have landed: the buffer can be overwritten while the last FMAs run
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&part_empty_bar[buf]));
+        if (!dbg_no_fma && !dbg_scalar) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ptx::fma2(acc[32 + j], v[0][2 * j], v[0][2 * j + 1], sc1_2);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ptx::fma2(acc[48 + j], v[1][2 * j], v[1][2 * j + 1], sc1_2);
+        }
+        if (dbg_scalar) {      // timing experiment: scalar FMAs on half of the data
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float lo, hi;
+            ptx::unpack2(acc[j], lo, hi);
+            lo = fmaf(__uint_as_float(v[0][j]), sc0, lo);
+            hi = fmaf(__uint_as_float(v[1][j]), sc1, hi);
+            acc[j] = ptx::pack2(lo, hi);
+          }
+        }
         if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
       }
       if (!ok) break;
       if (kEpi == kEpiSiluMul && p.sorted_rows[slot] >= 0) {
-        // acc[0..63] gate, acc[64..127] up for columns n_blk*128 + half*64 ..
+        // pairs 0..31: gate, 32..63: up, columns n_blk*128 + half*64 ..
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(slot) * p.ld_out +
                               tc.n_blk * kSlabRows + half * 64;
 #pragma unroll
@@ -738,8 +769,10 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const int i0 = q * 8 + 2 * j;
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(silu(acc[i0]) * acc[64 + i0], silu(acc[i0 + 1]) * acc[64 + i0 + 1]);
+            float g0, g1, u0, u1;
+            ptx::unpack2(acc[q * 4 + j], g0, g1);
+            ptx::unpack2(acc[32 + q * 4 + j], u0, u1);
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
             w[j] = *reinterpret_cast<uint32_t*>(&v2);
           }
           reinterpret_cast<uint4*>(yrow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -751,12 +784,16 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out +
                                                   tc.n_blk * kTileN + half * 128);
 #pragma unroll
-          for (int q = 0; q < 32; ++q)
-            dst[q] = make_float4(wt * acc[4 * q], wt * acc[4 * q + 1], wt * acc[4 * q + 2], wt * acc[4 * q + 3]);
+          for (int q = 0; q < 32; ++q) {
+            float a0, a1, a2, a3;
+            ptx::unpack2(acc[2 * q], a0, a1);
+            ptx::unpack2(acc[2 * q + 1], a2, a3);
+            dst[q] = make_float4(wt * a0, wt * a1, wt * a2, wt * a3);
+          }
         }
       }
     }
-    if (!ok && threadIdx.x == 64) atomicExch(p.status, kStatusGemmTimeout | 0x23);
+    if (!ok && threadIdx.x == 128) atomicExch(p.status, kStatusGemmTimeout | 0x23);
   }
 
   ptx::tc_fence_before();

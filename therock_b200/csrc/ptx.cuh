@@ -226,6 +226,31 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, u
       : "memory");
 }
 
+// ----------------------------------------------------------------------------- registers / packed math
+// Warpgroup-wide register reallocation (all four warps of the warpgroup execute it).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+// acc(2 x f32) += a(2 x f32) * s(2 x f32), one instruction for two lanes.
+__device__ __forceinline__ void fma2(uint64_t& acc, uint32_t a_lo, uint32_t a_hi, uint64_t s2) {
+  uint64_t a2;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a2) : "r"(a_lo), "r"(a_hi));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a2), "l"(s2));
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
 // ----------------------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes wide and
 // stored with the 128-byte swizzle (what a TMA box of 128 bytes x rows produces):

@@ -130,22 +130,33 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
       }
     }
   } else {
-    // one scale per 128 columns = 16 vectors = a 16-lane group
+    // one scale per 128 columns = 16 vectors = a 16-lane group.  Up to kGroupVec vectors per
+    // thread are loaded before any is processed so the loads overlap.
+    constexpr int kGroupVec = 4;
     const int ngroups = cols >> 7;
-    for (int base = 0; base < nvec; base += kRowThreads) {    // warp-uniform trip count
-      const int i = base + threadIdx.x;
-      const bool live = i < nvec;                             // nvec is a multiple of 16
-      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (live && !pad) unpack8(s[i], f);
-      float amax = 0.0f;
+    for (int base = 0; base < nvec; base += kRowThreads * kGroupVec) {   // warp-uniform trip count
+      uint4 held[kGroupVec];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      for (int j = 0; j < kGroupVec; ++j) {
+        const int i = base + j * kRowThreads + threadIdx.x;
+        held[j] = (i < nvec && !pad) ? s[i] : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-      const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
-      if (!live) continue;
-      if ((i & 15) == 0) scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
-      d[i] = quant8(f, 1.0f / sc);
+      for (int j = 0; j < kGroupVec; ++j) {
+        const int i = base + j * kRowThreads + threadIdx.x;      // nvec is a multiple of 16
+        float f[8];
+        unpack8(held[j], f);
+        float amax = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
+        if (i < nvec) {
+          if ((i & 15) == 0) scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
+          d[i] = quant8(f, 1.0f / sc);
+        }
+      }
     }
   }
 }
