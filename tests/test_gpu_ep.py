@@ -143,3 +143,30 @@ def test_two_gpu_expert_parallel(quant):
         p.join(300)
         assert p.exitcode == 0
     assert all(ret.get(r) for r in range(2)), dict(ret)
+
+
+def test_barrier_wait_is_bounded_when_a_rank_never_arrives():
+    """Failure detection without a fault: a two-rank barrier in which the second rank never
+    writes its flag.  Both "ranks" are buffers on this one GPU; the kernel must give up after
+    the timeout, report the missing rank in the status word and leave the context usable."""
+    import ctypes
+    from therock_b200 import api
+    dev = "cuda:0"
+    lay = api.EpLayout()
+    lay.flags, lay.matrix = 0, 256
+    mine = torch.zeros(1024, dtype=torch.uint8, device=dev)
+    theirs = torch.zeros(1024, dtype=torch.uint8, device=dev)
+    peer_base = torch.tensor([mine.data_ptr(), theirs.data_ptr()], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 1, status.data_ptr(), 50, st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == (0x300 | 1)                       # rank 1 was never seen
+    assert int(theirs[:8].view(torch.int32)[0].item()) == 1        # our own arrival was published
+    # the context is still healthy and a satisfied barrier passes
+    status.zero_()
+    mine[:8].view(torch.int32)[1] = 2                               # pretend rank 1 arrived at epoch 2
+    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 2, status.data_ptr(), 50, st)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 0

@@ -128,9 +128,10 @@ int fmoe_ep_publish(const int32_t* cum, const uint64_t* peer_base, const fmoe_ep
 }
 
 int fmoe_ep_barrier(const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
-                    int32_t epoch, int32_t* status, void* stream) {
-  if (!peer_base || !lay || !status || G <= 0 || G > fmoe::kMaxRanks) return FMOE_ERR_INVALID_ARG;
-  const long long limit = 8000000000LL;   // about four seconds of SM clock
+                    int32_t epoch, int32_t* status, int32_t timeout_ms, void* stream) {
+  if (!peer_base || !lay || !status || G <= 0 || G > fmoe::kMaxRanks || timeout_ms < 0) return FMOE_ERR_INVALID_ARG;
+  // clock64 ticks at the SM clock (<= ~2 GHz): 2e6 cycles per millisecond is an upper bound
+  const long long limit = timeout_ms > 0 ? 2000000LL * timeout_ms : 8000000000LL;   // default: about four seconds
   fmoe::ep_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(peer_base, lay->flags, me, G, epoch,
                                                                           status, limit);
   return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;

@@ -31,7 +31,8 @@ constexpr int kStageBytes = kABytes + kBBytes;             // 48 KiB
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kSmemMisc = 8192;          // barriers + per-expert block table (<= 1025 ints)
-constexpr int kGemmSmemBytes = kStages * kStageBytes + kSmemMisc + 1024;  // +1024 alignment slack
+constexpr int kEpiStageReserve = 4 * 32 * 36 * 4;   // per-warp staging of the epilogue (see epilogue_tile)
+constexpr int kGemmSmemBytes = kStages * kStageBytes + kSmemMisc + kEpiStageReserve + 1024;  // +1024 alignment slack
 
 enum : int { kEpiSiluMul = 1, kEpiScaledSlots = 2 };
 
@@ -85,20 +86,29 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const int* cum, int E
 // SiLU with the fast exponential and division (a few ulp; far inside the bf16 rounding of y).
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
+// Per-warp staging area for the epilogue's transposed stores: 32 rows x 36 words.
+constexpr int kStageWordsPerRow = 36;
+constexpr int kEpiStageBytesPerWarp = 32 * kStageWordsPerRow * 4;     // 4608
+constexpr int kEpiStageBytes = 4 * kEpiStageBytesPerWarp;             // four epilogue warps
+
 // Fused epilogue of one 128 x 256 accumulator held in TMEM (this thread owns one row).
 //   kEpiSiluMul    : columns 0..127 gate, 128..255 up -> bf16 y[slot, n_blk*128 ..] = SiLU(g)*u
 //   kEpiScaledSlots: 256 output channels -> f32 slots[row, n_blk*256 ..] = w * acc
 // fp8: acc is first multiplied by the row's activation scale and the channel's weight scale.
+// A thread computes 32 consecutive columns of its own row per step.  Storing them directly
+// would make every warp store touch 32 rows with 16 bytes each; instead the warp transposes
+// the 32 x 32 block through its private shared-memory area (`stage`, conflict-free 16-byte
+// accesses) and writes whole row segments: 128-byte (f32) or 64-byte (bf16) contiguous runs.
 template <int kEpi>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_row, int slot, int n_blk,
-                                              const float* bs0, const float* bs1, float a_s) {
+                                              const float* bs0, const float* bs1, float a_s,
+                                              uint32_t* stage) {
+  const int lane = threadIdx.x & 31;
+  const int row = p.sorted_rows[slot];               // flat (token, k) index, < 0 for a pad slot
   if (kEpi == kEpiSiluMul) {
     // pad slots carry no token: their rows of y are never used, so they are not stored
-    const bool live = p.sorted_rows[slot] >= 0;
-    __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) +
-                          static_cast<size_t>(slot) * p.ld_out + n_blk * kSlabRows;
-    // Software pipeline over 32-column chunks: the TMEM loads of chunk c+1 are in flight
-    // while chunk c is scaled, activated and stored.
+    __nv_bfloat16* ybase = reinterpret_cast<__nv_bfloat16*>(p.out) + n_blk * kSlabRows;
+    const int slot0 = slot - lane;                   // first sorted slot of this warp
     uint32_t g[2][32], u[2][32];
     ptx::tmem_ld_32x32(t_row, g[0]);
     ptx::tmem_ld_32x32(t_row + kSlabRows, u[0]);
@@ -132,18 +142,27 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
         packed[2 * q] = *reinterpret_cast<uint32_t*>(&v0);
         packed[2 * q + 1] = *reinterpret_cast<uint32_t*>(&v1);
       }
-      if (live) {
-        uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+      // own row -> staging (16 words of bf16 pairs, row pitch 20 words)
+      __syncwarp();
+      uint4* srow = reinterpret_cast<uint4*>(stage + lane * 20);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      for (int q = 0; q < 4; ++q)
+        srow[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      __syncwarp();
+      // 4 lanes per row, 8 rows per store instruction: 64 contiguous bytes per row
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int r = it * 8 + (lane >> 2);
+        const int seg = lane & 3;
+        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
+        const int live_r = __shfl_sync(0xffffffffu, row, r);
+        if (live_r >= 0)
+          *reinterpret_cast<uint4*>(ybase + static_cast<size_t>(slot0 + r) * p.ld_out + c * 32 + seg * 8) = val;
       }
     }
   } else {
-    const int row = p.sorted_rows[slot];
     const float w = p.sorted_weights[slot];
-    float* orow = reinterpret_cast<float*>(p.out) +
-                  static_cast<size_t>(row < 0 ? 0 : row) * p.ld_out + n_blk * kTileN;
+    float* obase = reinterpret_cast<float*>(p.out) + n_blk * kTileN;
     uint32_t v[2][32];
     ptx::tmem_ld_32x32(t_row, v[0]);
 #pragma unroll
@@ -151,21 +170,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
       const int cur = c & 1;
       ptx::tmem_ld_wait();
       if (c + 1 < kTileN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, v[cur ^ 1]);
-      if (row >= 0) {
-        float4* dst = reinterpret_cast<float4*>(orow + c * 32);
+      __syncwarp();
+      float4* srow = reinterpret_cast<float4*>(stage + lane * kStageWordsPerRow);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float f[4];
+      for (int q = 0; q < 8; ++q) {
+        float f[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) f[j] = __uint_as_float(v[cur][4 * q + j]);
-          if (p.b_scale != nullptr) {
-            // second GEMM: the tile's 256 columns are 256 consecutive output channels
-            const float4 sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
-            f[0] = (f[0] * a_s) * sc.x; f[1] = (f[1] * a_s) * sc.y;
-            f[2] = (f[2] * a_s) * sc.z; f[3] = (f[3] * a_s) * sc.w;
-          }
-          dst[q] = make_float4(w * f[0], w * f[1], w * f[2], w * f[3]);
+        for (int j = 0; j < 4; ++j) f[j] = __uint_as_float(v[cur][4 * q + j]);
+        if (p.b_scale != nullptr) {
+          // second GEMM: the tile's 256 columns are 256 consecutive output channels
+          const float4 sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+          f[0] = (f[0] * a_s) * sc.x; f[1] = (f[1] * a_s) * sc.y;
+          f[2] = (f[2] * a_s) * sc.z; f[3] = (f[3] * a_s) * sc.w;
         }
+        srow[q] = make_float4(w * f[0], w * f[1], w * f[2], w * f[3]);
+      }
+      __syncwarp();
+      // 8 lanes per row, 4 rows per store instruction: 128 contiguous bytes per row
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const int seg = lane & 7;
+        const float4 val = *reinterpret_cast<const float4*>(stage + r * kStageWordsPerRow + seg * 4);
+        const int row_r = __shfl_sync(0xffffffffu, row, r);
+        if (row_r >= 0)
+          *reinterpret_cast<float4*>(obase + static_cast<size_t>(row_r) * p.ld_out + c * 32 + seg * 4) = val;
       }
     }
   }
@@ -316,7 +345,9 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      if (!(p.debug_flags & 1u)) epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
+      if (!(p.debug_flags & 1u))
+        epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s,
+                            reinterpret_cast<uint32_t*>(misc + kSmemMisc) + quad * (kEpiStageBytesPerWarp / 4));
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&acc_empty_bar[acc]));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -344,7 +375,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kABytes + kSlabRows * kStageKBytes;   // 16 KiB A + 16 KiB B slab
 constexpr int kPairSmemMisc = 9216;                                   // barriers + two expert tables
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairSmemMisc + 1024;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairSmemMisc + kEpiStageReserve + 1024;
 
 struct PairTile {
   int expert, n_blk, m_blk0, m_end;   // m_blk0: first row block of the pair; m_end: expert's end
@@ -525,7 +556,9 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      if (valid && !(p.debug_flags & 1u)) epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s);
+      if (valid && !(p.debug_flags & 1u))
+        epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s,
+                            reinterpret_cast<uint32_t*>(misc + kPairSmemMisc) + quad * (kEpiStageBytesPerWarp / 4));
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_u32(&acc_empty_bar[acc]), 0));

@@ -229,6 +229,7 @@ class PeerExpertParallelMoE:
         self.args.workspace = torch.empty(api.fused_moe_workspace_size(traits, self.args), dtype=torch.uint8,
                                           device=dev)
         self.epoch = 0
+        self.barrier_timeout_ms = 0          # 0 = the library default (about four seconds)
         self._ctypes = ctypes
         self.launches_per_step = 8 + api.launches_per_run(traits)
 
@@ -236,7 +237,7 @@ class PeerExpertParallelMoE:
         self.epoch += 1
         self.api._check(self.api.lib().fmoe_ep_barrier(self.peer_base.data_ptr(), self._ctypes.byref(self.lay),
                                                        self.rank, self.world, self.epoch, self.status.data_ptr(),
-                                                       stream))
+                                                       self.barrier_timeout_ms, stream))
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
