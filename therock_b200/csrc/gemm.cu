@@ -158,15 +158,15 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     const int which = g.epilogue == kEpiSiluMul ? 0 : 1;
     if (!configured[dev][which]) {
       cudaError_t e = which == 0
-          ? cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiSiluMul>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes)
-          : cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiScaledSlots>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+          ? cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiSiluMul>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBlockSmemBytes)
+          : cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiScaledSlots>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBlockSmemBytes);
       if (e != cudaSuccess) return e;
       configured[dev][which] = true;
     }
     if (which == 0)
-      fmoe_grouped_gemm_block_kernel<kEpiSiluMul><<<grid, kBlockGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, bp);
+      fmoe_grouped_gemm_block_kernel<kEpiSiluMul><<<grid, kBlockGemmThreads, kBlockSmemBytes, stream>>>(ta, tb, bp);
     else
-      fmoe_grouped_gemm_block_kernel<kEpiScaledSlots><<<grid, kBlockGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, bp);
+      fmoe_grouped_gemm_block_kernel<kEpiScaledSlots><<<grid, kBlockGemmThreads, kBlockSmemBytes, stream>>>(ta, tb, bp);
     return cudaGetLastError();
   }
   const bool pair = g.mode == 2;

@@ -590,6 +590,7 @@ constexpr int kBlockGemmThreads = 384;   // warpgroup 0: producer + MMA (+2 idle
 constexpr int kBlockStages = 4;
 constexpr int kBlockThinRegs = 40;       // registers per thread kept by warpgroup 0
 constexpr int kBlockFatRegs = 216;       // registers per thread taken by the epilogue warpgroups
+constexpr int kBlockSmemBytes = kBlockStages * kStageBytes + kSmemMisc + 8 * 32 * 20 * 4 + 1024;
 
 struct BlockGemmParams {
   GemmParams g;                 // a_scale / b_scale of g are unused here
@@ -793,35 +794,61 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
       }
       if (!ok) break;
-      if (kEpi == kEpiSiluMul && p.sorted_rows[slot] >= 0) {
+      // Final stores go through a per-warp transpose (32 rows x 16 words at a time) so each
+      // store instruction writes 64-byte row segments instead of 16 bytes to 32 different rows.
+      uint32_t* stage = reinterpret_cast<uint32_t*>(misc + kSmemMisc) + (warp - 4) * (32 * 20);
+      const int row = p.sorted_rows[slot];
+      const int slot0 = slot - lane;
+      if (kEpi == kEpiSiluMul) {
         // pairs 0..31: gate, 32..63: up, columns n_blk*128 + half*64 ..
-        __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(slot) * p.ld_out +
-                              tc.n_blk * kSlabRows + half * 64;
+        __nv_bfloat16* ybase = reinterpret_cast<__nv_bfloat16*>(p.out) + tc.n_blk * kSlabRows + half * 64;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint32_t w[4];
+        for (int ch = 0; ch < 2; ++ch) {            // 32 columns (16 packed words) per chunk
+          uint32_t w[16];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < 16; ++j) {
             float g0, g1, u0, u1;
-            ptx::unpack2(acc[q * 4 + j], g0, g1);
-            ptx::unpack2(acc[32 + q * 4 + j], u0, u1);
+            ptx::unpack2(acc[ch * 16 + j], g0, g1);
+            ptx::unpack2(acc[32 + ch * 16 + j], u0, u1);
             __nv_bfloat162 v2 = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
             w[j] = *reinterpret_cast<uint32_t*>(&v2);
           }
-          reinterpret_cast<uint4*>(yrow)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            reinterpret_cast<uint4*>(stage + lane * 20)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int r = it * 8 + (lane >> 2);
+            const int seg = lane & 3;
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
+            if (__shfl_sync(0xffffffffu, row, r) >= 0)
+              *reinterpret_cast<uint4*>(ybase + static_cast<size_t>(slot0 + r) * p.ld_out + ch * 32 + seg * 8) = val;
+          }
         }
       } else if (kEpi == kEpiScaledSlots) {
-        const int row = p.sorted_rows[slot];
-        if (row >= 0) {
-          const float wt = p.sorted_weights[slot];
-          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out +
-                                                  tc.n_blk * kTileN + half * 128);
+        const float wt = p.sorted_weights[slot];
+        float* obase = reinterpret_cast<float*>(p.out) + tc.n_blk * kTileN + half * 128;
 #pragma unroll
-          for (int q = 0; q < 32; ++q) {
+        for (int ch = 0; ch < 8; ++ch) {            // 16 columns per chunk
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
             float a0, a1, a2, a3;
-            ptx::unpack2(acc[2 * q], a0, a1);
-            ptx::unpack2(acc[2 * q + 1], a2, a3);
-            dst[q] = make_float4(wt * a0, wt * a1, wt * a2, wt * a3);
+            ptx::unpack2(acc[ch * 8 + 2 * q], a0, a1);
+            ptx::unpack2(acc[ch * 8 + 2 * q + 1], a2, a3);
+            reinterpret_cast<float4*>(stage + lane * 20)[q] = make_float4(wt * a0, wt * a1, wt * a2, wt * a3);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int r = it * 8 + (lane >> 2);
+            const int seg = lane & 3;
+            const float4 val = *reinterpret_cast<const float4*>(stage + r * 20 + seg * 4);
+            const int row_r = __shfl_sync(0xffffffffu, row, r);
+            if (row_r >= 0)
+              *reinterpret_cast<float4*>(obase + static_cast<size_t>(row_r) * p.ld_out + ch * 16 + seg * 4) = val;
           }
         }
       }
