@@ -350,7 +350,24 @@ def run_gpu(a, c):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(max(a.warmup, 3)):
         step()
-    ms_total, t0, t1 = timed(step, a.steps)
+    # Launch-bound steps (decode-sized batches) are replayed from a CUDA graph: the operator
+    # neither synchronises nor allocates, so one capture of the step replaces its launches.
+    use_graph = world == 1 and (a.graph == "on" or (a.graph == "auto" and c["T"] <= 64))
+    timed_step = step
+    if use_graph:
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        cuda_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            step()
+            side.synchronize()
+            with torch.cuda.graph(cuda_graph, stream=side):
+                step()
+        torch.cuda.synchronize()
+        timed_step = cuda_graph.replay
+        for _ in range(3):
+            timed_step()
+    ms_total, t0, t1 = timed(timed_step, a.steps)
     clocks = sampler.summary(t0, t1) if sampler else None
 
     # per-kernel durations over the same number of steps (single GPU: events between kernels)
@@ -452,6 +469,7 @@ def run_gpu(a, c):
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / n_e2e, "steps": n_e2e},
             "gpu_launches": launches_per_step * a.steps, "clocks": clocks}
+    line["config"]["launch"] = "cuda_graph_replay" if use_graph else "stream"
     if world > 1:
         line["config"]["ep_transport"] = ep_transport
     if ep_stage is not None:
@@ -519,6 +537,8 @@ def main():
     ap.add_argument("--config", default="C1", choices=sorted(CONFIGS))
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the token count (small cases for profiler captures)")
+    ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
+                    help="replay the step from a CUDA graph in the timed loop (auto: decode-sized batches)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-resident timed loop: no stage profile, e2e or CPU baseline")
     a = ap.parse_args()

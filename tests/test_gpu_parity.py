@@ -266,3 +266,49 @@ def test_router_feeds_fused_moe():
     d2 = dict(d)
     d2["topk_ids"], d2["topk_w"] = ids.cpu().numpy(), w.cpu().numpy()
     check(d2, out_bits(out), run_oracle(d2))
+
+
+# ------------------------------------------------------------------------------ graph capture / torch op
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_cuda_graph_replay_matches_eager(quant):
+    d = O.make_inputs(64, 512, 512, 8, 2, quant, "softmax", seed=31)
+    args = args_for(d)
+    args.o = torch.empty_like(args.a)
+    args.workspace = torch.empty(M.fused_moe_workspace_size(traits_for(quant), args), dtype=torch.uint8, device="cuda:0")
+    eager = out_bits(M.fused_moe(traits_for(quant), args)).copy()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        M.fused_moe(traits_for(quant), args)            # warm-up on the capture stream
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            M.fused_moe(traits_for(quant), args)
+    for _ in range(3):
+        args.o.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert (out_bits(args.o) == eager).all()
+    assert api.check_status(args.workspace) == 0
+
+
+def test_torch_library_op():
+    import therock_b200.torch_op  # noqa: F401  (registers torch.ops.therock_b200.*)
+    d = O.make_inputs(40, 256, 256, 4, 2, 1, "softmax", seed=32)
+    a = args_for(d)
+    ids, w = torch.ops.therock_b200.route(to_dev(d["logits"]), 2, "softmax")
+    out = torch.ops.therock_b200.fused_moe(a.a, a.g, a.d, ids, w, a.g_scale, a.d_scale, "token_channel")
+    torch.cuda.synchronize()
+    d2 = dict(d)
+    d2["topk_ids"], d2["topk_w"] = ids.cpu().numpy(), w.cpu().numpy()
+    check(d2, out_bits(out), run_oracle(d2))
+    # fake (meta) implementation: shape inference without running the kernels
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        fx = torch.empty(40, 256, dtype=torch.bfloat16, device="cuda")
+        fo = torch.ops.therock_b200.fused_moe(fx, torch.empty(4, 512, 256, dtype=torch.uint8, device="cuda"),
+                                              torch.empty(4, 256, 256, dtype=torch.uint8, device="cuda"),
+                                              torch.empty(40, 2, dtype=torch.int32, device="cuda"),
+                                              torch.empty(40, 2, device="cuda"), None, None, "token_channel")
+        assert fo.shape == (40, 256) and fo.dtype == torch.bfloat16
