@@ -395,7 +395,7 @@ def run_gpu(a, c):
     # expert-parallel phases (events around plan / pack / dispatch / local operator / return /
     # combine of a few extra steps, rank 0 only)
     ep_stage = None
-    if world > 1 and ep_transport == "nccl_all_to_all":
+    if world > 1:
         barrier()
         moe.trace = []
         n_tr = 10

@@ -25,6 +25,7 @@ struct fused_moe_traits {
   std::string activation = "silu";
   int gate_only = 0;             // 0: gate and up rows packed as [2I, H]
   int block_m = 128;             // sorted M-block
+  int gemm_mode = 0;             // 0 = per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel
 };
 
 struct fused_moe_args {
@@ -44,6 +45,7 @@ struct fused_moe_args {
   int num_experts = 0;
   int topk = 0;
   const int32_t* num_tokens_dev_ptr = nullptr;  // optional device-side token count (<= num_tokens)
+  int expected_tokens = 0;                      // its typical value (kernel choice hint), 0 = num_tokens
 };
 
 struct stream_config {
@@ -66,6 +68,7 @@ inline int to_c(const fused_moe_traits& t, fmoe_traits_c* c) {
   c->activation = FMOE_ACT_SILU;
   c->gate_only = t.gate_only;
   c->block_m = t.block_m;
+  c->gemm_mode = t.gemm_mode;
   return FMOE_OK;
 }
 inline void to_c(const fused_moe_args& a, fmoe_args_c* c) {
@@ -77,6 +80,7 @@ inline void to_c(const fused_moe_args& a, fmoe_args_c* c) {
   c->T = a.num_tokens; c->H = a.hidden_size; c->I = a.intermediate_size;
   c->E = a.num_experts; c->K = a.topk;
   c->num_tokens_dev = a.num_tokens_dev_ptr;
+  c->expected_tokens = a.expected_tokens;
 }
 }  // namespace fmoe_detail
 

@@ -62,7 +62,9 @@ typedef struct fmoe_traits_c {
   int32_t activation;   /* fmoe_activation */
   int32_t gate_only;    /* 0: W1 holds gate rows then up rows (2I); 1 is rejected (unsupported) */
   int32_t block_m;      /* rows per sorted block; 128 */
-  int32_t reserved[3];
+  int32_t gemm_mode;    /* 0 = chosen per GEMM from the expected tile counts, 1 = single-CTA
+                           kernel, 2 = CTA-pair kernel (cta_group::2) */
+  int32_t reserved[2];
 } fmoe_traits_c;
 
 /* Run-time arguments (ck_tile's fused_moe_args role).  All pointers are device pointers. */
@@ -78,7 +80,9 @@ typedef struct fmoe_args_c {
   void* workspace;          /* >= fmoe_get_workspace_size bytes, 256-byte aligned */
   uint64_t workspace_bytes;
   int32_t T, H, I, E, K;
-  int32_t reserved[3];
+  int32_t expected_tokens;  /* 0, or the token count the caller expects when T is only a capacity
+                               (see num_tokens_dev): used to pick the GEMM kernel flavour */
+  int32_t reserved[2];
   const int32_t* num_tokens_dev; /* optional device int32: only the first min(T, *num_tokens_dev)
                                     tokens are processed (T still sizes the workspace); used when
                                     the batch size is only known on the device, e.g. on the

@@ -312,3 +312,20 @@ def test_torch_library_op():
                                               torch.empty(40, 2, dtype=torch.int32, device="cuda"),
                                               torch.empty(40, 2, device="cuda"), None, None, "token_channel")
         assert fo.shape == (40, 256) and fo.dtype == torch.bfloat16
+
+
+def test_random_small_configurations():
+    """Seeded sweep over ragged shapes and all three quantisation modes."""
+    rng = np.random.default_rng(2024)
+    for case in range(14):
+        T = int(rng.integers(1, 300))
+        H = int(rng.choice([256, 512, 768]))
+        I = int(rng.choice([128, 256, 384]))
+        E = int(rng.integers(1, 13))
+        K = int(rng.integers(1, min(E, 4) + 1))
+        quant = int(rng.integers(0, 3))
+        d = O.make_inputs(T, H, I, E, K, quant, "softmax" if case % 2 else "sigmoid", seed=100 + case)
+        if T > 5:
+            d["topk_ids"][int(rng.integers(0, T)), 0] = -1
+        got, _ = run_gpu(d)
+        check(d, got, run_oracle(d))

@@ -23,7 +23,7 @@ class FmoeError(RuntimeError):
 class _Traits(ctypes.Structure):
     _fields_ = [("quant", ctypes.c_int32), ("weight_dtype", ctypes.c_int32),
                 ("activation", ctypes.c_int32), ("gate_only", ctypes.c_int32),
-                ("block_m", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+                ("block_m", ctypes.c_int32), ("gemm_mode", ctypes.c_int32), ("reserved", ctypes.c_int32 * 2)]
 
 
 class _Args(ctypes.Structure):
@@ -33,8 +33,8 @@ class _Args(ctypes.Structure):
                 ("out", ctypes.c_void_p), ("workspace", ctypes.c_void_p),
                 ("workspace_bytes", ctypes.c_uint64),
                 ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("I", ctypes.c_int32),
-                ("E", ctypes.c_int32), ("K", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3),
-                ("num_tokens_dev", ctypes.c_void_p)]
+                ("E", ctypes.c_int32), ("K", ctypes.c_int32), ("expected_tokens", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 2), ("num_tokens_dev", ctypes.c_void_p)]
 
 
 class _Layout(ctypes.Structure):
@@ -113,6 +113,7 @@ class FusedMoeTraits:
     activation: str = "silu"
     gate_only: int = 0
     block_m: int = 128
+    gemm_mode: int = 0            # 0 = per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel
 
     def to_c(self) -> _Traits:
         if self.prec_i != "bf16" or self.prec_o != "bf16":
@@ -129,6 +130,7 @@ class FusedMoeTraits:
         t.activation = 0
         t.gate_only = self.gate_only
         t.block_m = self.block_m
+        t.gemm_mode = self.gemm_mode
         return t
 
 
@@ -145,6 +147,7 @@ class FusedMoeArgs:
     d_scale: Optional[torch.Tensor] = None
     workspace: Optional[torch.Tensor] = None   # uint8, >= fused_moe_workspace_size bytes
     num_tokens_dev: Optional[torch.Tensor] = None  # int32[1] on the device: process only that many tokens
+    expected_tokens: int = 0                   # typical value of num_tokens_dev (kernel choice hint)
 
     def to_c(self) -> _Args:
         for name in ("a", "g", "d", "topk_ids", "topk_weight"):
@@ -172,6 +175,7 @@ class FusedMoeArgs:
             c.workspace_bytes = self.workspace.numel() * self.workspace.element_size()
         c.T, c.H, c.I, c.E, c.K = T, H, I2 // 2, E, self.topk_ids.shape[1]
         c.num_tokens_dev = self.num_tokens_dev.data_ptr() if self.num_tokens_dev is not None else None
+        c.expected_tokens = int(self.expected_tokens)
         return c
 
 

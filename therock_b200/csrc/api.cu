@@ -41,6 +41,7 @@ int validate_traits(const fmoe_traits_c* t) {
   if (t->activation != FMOE_ACT_SILU) return fail(FMOE_ERR_UNSUPPORTED, "only SiLU activation is built");
   if (t->gate_only != 0) return fail(FMOE_ERR_UNSUPPORTED, "gate_only variant is not built");
   if (t->block_m != fmoe::kBlockM) return fail(FMOE_ERR_UNSUPPORTED, "block_m must be %d", fmoe::kBlockM);
+  if (t->gemm_mode < 0 || t->gemm_mode > 2) return fail(FMOE_ERR_INVALID_ARG, "gemm_mode must be 0, 1 or 2");
   return FMOE_OK;
 }
 
@@ -242,14 +243,26 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   g.sorted_weights = sorted_w;
   g.status = status;
   g.max_m_blocks = static_cast<int>(plan.cap / fmoe::kBlockM);
-  // Kernel flavour.  The CTA-pair kernel moves half as much of the weight operand per flop
-  // but pads every expert to an even number of row blocks; with few rows per expert that
-  // padding costs more than the pairing saves in the first GEMM (measured on the Mixtral
-  // shapes: break-even near 1.5k routed rows per expert).
-  const int forced_mode = fmoe::gemm_mode_from_env();
-  const long long rows_per_expert = static_cast<long long>(a.T) * a.K / a.E;
+  // Kernel flavour per GEMM.  The CTA-pair kernel moves a third less of the operands per flop
+  // (about 5 % faster per tile) but pads every expert to an even number of row blocks and
+  // has half as many schedulable units, so whether it wins is a question of wave counts:
+  // estimate the persistent waves of both flavours from the expected number of routed rows.
+  const int forced_mode = traits->gemm_mode ? traits->gemm_mode : fmoe::gemm_mode_from_env();
+  const long long exp_rows = static_cast<long long>(a.expected_tokens > 0 ? a.expected_tokens : a.T) * a.K;
+  const int sms = fmoe::device_sm_count();
+  auto pick_mode = [&](int n_blocks) {
+    if (forced_mode) return forced_mode;
+    // expected row blocks: full blocks plus half a block of padding per expert that is hit
+    const long long hit = exp_rows < a.E ? exp_rows : a.E;
+    long long m_blocks = (exp_rows + 64 * hit + 127) / 128;
+    if (m_blocks < hit) m_blocks = hit;                             // at least one block per expert hit
+    const long long pairs = (m_blocks + hit / 2 + 1) / 2;          // odd experts waste half a pair
+    const long long waves_single = (m_blocks * n_blocks + sms - 1) / sms;
+    const long long waves_pair = (pairs * n_blocks + sms / 2 - 1) / (sms / 2);
+    return (waves_pair * 95 < waves_single * 100) ? 2 : 1;
+  };
   // gemm1: [cap, H] x W1[E, 2I, H]^T -> SiLU(gate) * up -> y [cap, I]
-  g.mode = forced_mode ? forced_mode : (rows_per_expert >= 1536 ? 2 : 1);
+  g.mode = pick_mode(a.I / fmoe::kSlabRows);
   g.epilogue = fmoe::kEpiSiluMul;
   g.a = a_sorted; g.a_rows = plan.cap; g.b = a.w1; g.k_elems = a.H;
   g.b_rows_per_expert = 2 * a.I;
@@ -268,7 +281,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   }
   FMOE_STAGE(4);
   // gemm2: [cap, I] x W2[E, H, I]^T * topk_weight -> slots [T*K, H]
-  g.mode = forced_mode ? forced_mode : (rows_per_expert >= 256 ? 2 : 1);
+  g.mode = pick_mode(a.H / fmoe::kTileN);
   g.epilogue = fmoe::kEpiScaledSlots;
   g.a = a2; g.b = a.w2; g.k_elems = a.I;
   g.b_rows_per_expert = a.H;

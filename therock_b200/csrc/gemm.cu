@@ -108,8 +108,7 @@ int gemm_mode_from_env() {
   return mode;
 }
 
-namespace {
-}  // namespace
+int device_sm_count() { return sm_count(); }
 
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
   CUtensorMap ta, tb;

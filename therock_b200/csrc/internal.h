@@ -69,5 +69,7 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
 
 // 0 = no override, 1 / 2 = FMOE_GEMM_MODE forces the single-CTA / CTA-pair kernel.
 int gemm_mode_from_env();
+// SM count of the current device (cached).
+int device_sm_count();
 
 }  // namespace fmoe

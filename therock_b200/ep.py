@@ -225,11 +225,12 @@ class PeerExpertParallelMoE:
         self.out_rows = torch.empty(recv_cap, hidden, dtype=torch.bfloat16, device=dev)
         self.args = api.FusedMoeArgs(a=self.rows, g=w1_local, d=w2_local, topk_ids=self.ids,
                                      topk_weight=self.wts, o=self.out_rows, g_scale=w1_scale,
-                                     d_scale=w2_scale, num_tokens_dev=self.n_recv)
+                                     d_scale=w2_scale, num_tokens_dev=self.n_recv, expected_tokens=R)
         self.args.workspace = torch.empty(api.fused_moe_workspace_size(traits, self.args), dtype=torch.uint8,
                                           device=dev)
         self.epoch = 0
         self.barrier_timeout_ms = 0          # 0 = the library default (about four seconds)
+        self.trace = None                    # set to [] to collect (phase, cuda event) marks
         self._ctypes = ctypes
         self.launches_per_step = 8 + api.launches_per_run(traits)
 
@@ -246,19 +247,35 @@ class PeerExpertParallelMoE:
         assert x.shape == (T, H) and topk_ids.shape == (T, K)
         st = api._stream_ptr(None)
         pb = self.peer_base.data_ptr()
+        self._mark("start")
         api._check(lib.fmoe_ep_plan(topk_ids.data_ptr(), T, K, self.e_local, G, self.order.data_ptr(),
                                     self.inv.data_ptr(), self.cum.data_ptr(), self.scratch.data_ptr(), st))
         api._check(lib.fmoe_ep_publish(self.cum.data_ptr(), pb, by(self.lay), self.rank, G, st))
+        self._mark("plan")
         self._barrier(st)
+        self._mark("barrier1")
         api._check(lib.fmoe_ep_dispatch(x.data_ptr(), topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, H,
                                         self.e_local, self.order.data_ptr(), self.cum.data_ptr(), pb,
                                         by(self.lay), self.rank, G, self.n_recv.data_ptr(), st))
+        self._mark("dispatch")
         self._barrier(st)
+        self._mark("barrier2")
         api.fused_moe(self.traits, self.args)
+        self._mark("local_moe")
         api._check(lib.fmoe_ep_return(self.out_rows.data_ptr(), H, self.n_recv.data_ptr(), pb, by(self.lay),
                                       self.rank, G, st))
+        self._mark("return")
         self._barrier(st)
-        return api.combine_rows(self.back, self.inv, T, K, out=out)
+        self._mark("barrier3")
+        res = api.combine_rows(self.back, self.inv, T, K, out=out)
+        self._mark("combine")
+        return res
+
+    def _mark(self, name):
+        if self.trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.trace.append((name, ev))
 
     def check_status(self) -> int:
         torch.cuda.synchronize()
