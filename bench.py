@@ -423,6 +423,22 @@ def run_gpu(a, c):
         def pipe_step(x, ids, w, slot):
             args.a, args.topk_ids, args.topk_weight, args.o = x, ids, w, outs[slot]
             return M.fused_moe(traits, args, stream=torch.cuda.current_stream())
+    elif ep_transport == "peer_memory":
+        # the whole expert-parallel step (13 launches, no host sync) is captured once per
+        # pipeline slot and replayed: the host then issues one graph launch per step
+        ep_out = [torch.empty_like(d["x"]) for _ in range(depth)]
+        ep_graphs = [None] * depth
+
+        def pipe_step(x, ids, w, slot):
+            if ep_graphs[slot] is None:
+                moe.forward(x, ids, w, out=ep_out[slot])          # warm-up outside capture
+                torch.cuda.current_stream().synchronize()
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=torch.cuda.current_stream()):
+                    moe.forward(x, ids, w, out=ep_out[slot])
+                ep_graphs[slot] = g_
+            ep_graphs[slot].replay()
+            return ep_out[slot]
     else:
         def pipe_step(x, ids, w, slot):
             return moe.forward(x, ids, w)

@@ -226,13 +226,16 @@ FMOE_API int fmoe_ep_plan(const int32_t* topk_ids, int32_t T, int32_t K, int32_t
 /* Writes this rank's row of the count matrix into every rank's buffer. */
 FMOE_API int fmoe_ep_publish(const int32_t* cum, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,
                              int32_t me, int32_t G, void* stream);
-/* All ranks meet: each writes `epoch` (strictly increasing across calls) into every peer's
- * flag word and waits, for a bounded time (timeout_ms, 0 = about four seconds), until all
- * peers wrote theirs; on expiry the status word receives 0x300 | rank-not-seen and the kernel
- * returns, so a missing rank never hangs the GPU. */
+/* All ranks meet: each writes the barrier's epoch into every peer's flag word and waits, for
+ * a bounded time (timeout_ms, 0 = about four seconds), until all peers wrote theirs; on expiry
+ * the status word receives 0x300 | rank-not-seen and the kernel returns, so a missing rank never
+ * hangs the GPU.  The epoch must grow by one per barrier on every rank: either pass it from
+ * the host (`epoch`, epoch_counter = NULL) or let the kernel advance a device-side counter
+ * (`epoch_counter`, one int32 per rank, zero-initialised), which keeps the launch identical
+ * from step to step so a step can be captured in a CUDA graph. */
 FMOE_API int fmoe_ep_barrier(const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
-                             int32_t G, int32_t epoch, int32_t* status, int32_t timeout_ms,
-                             void* stream);
+                             int32_t G, int32_t epoch, int32_t* epoch_counter, int32_t* status,
+                             int32_t timeout_ms, void* stream);
 /* Sends every routed token row, with its local expert id, weight and return address, into
  * the owner rank's receive arrays; stores this rank's own received-row count in n_recv_dev.
  * Needs the count matrix complete (publish + barrier). */

@@ -159,7 +159,7 @@ def test_barrier_wait_is_bounded_when_a_rank_never_arrives():
     peer_base = torch.tensor([mine.data_ptr(), theirs.data_ptr()], dtype=torch.int64, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     st = torch.cuda.current_stream().cuda_stream
-    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 1, status.data_ptr(), 50, st)
+    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 1, None, status.data_ptr(), 50, st)
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) == (0x300 | 1)                       # rank 1 was never seen
@@ -167,6 +167,14 @@ def test_barrier_wait_is_bounded_when_a_rank_never_arrives():
     # the context is still healthy and a satisfied barrier passes
     status.zero_()
     mine[:8].view(torch.int32)[1] = 2                               # pretend rank 1 arrived at epoch 2
-    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 2, status.data_ptr(), 50, st)
+    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 2, None, status.data_ptr(), 50, st)
     torch.cuda.synchronize()
     assert rc == 0 and int(status.item()) == 0
+    # device-side epoch counter: the kernel advances it itself (1 -> 2 -> 3)
+    counter = torch.tensor([2], dtype=torch.int32, device=dev)
+    mine[:8].view(torch.int32)[1] = 3
+    rc = api.lib().fmoe_ep_barrier(peer_base.data_ptr(), ctypes.byref(lay), 0, 2, 0, counter.data_ptr(),
+                                   status.data_ptr(), 50, st)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 0 and int(counter.item()) == 3
+    assert int(theirs[:8].view(torch.int32)[0].item()) == 3

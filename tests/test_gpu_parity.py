@@ -329,3 +329,42 @@ def test_random_small_configurations():
             d["topk_ids"][int(rng.integers(0, T)), 0] = -1
         got, _ = run_gpu(d)
         check(d, got, run_oracle(d))
+
+
+# ------------------------------------------------------------------------------ C++ host surface
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_cpp_host_program_through_fused_moe_hpp(quant, tmp_path):
+    """Builds tests/cpp/fused_moe_cpp_host.cpp (fused_moe_traits / fused_moe_args /
+    fused_moe(traits, args, stream) and moe_sorting from include/fused_moe.hpp) with nvcc,
+    links it against libfmoe_b200.so, runs it on one problem and checks its outputs."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "fmoe_cpp_host")
+    libdir = os.path.join(root, "therock_b200")
+    env = {k: v for k, v in os.environ.items() if k not in ("CC", "CXX")}
+    subprocess.run(["nvcc", "-std=c++17", "-O2", "-I", os.path.join(root, "include"), "-o", exe,
+                    os.path.join(root, "tests", "cpp", "fused_moe_cpp_host.cpp"), "-L", libdir,
+                    "-l:libfmoe_b200.so", "-Xlinker", "-rpath", "-Xlinker", libdir], check=True, env=env)
+    T, H, I, E, K = 96, 512, 256, 8, 2
+    d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=41)
+    prob, res = str(tmp_path / "problem.bin"), str(tmp_path / "result.bin")
+    with open(prob, "wb") as f:
+        f.write(np.array([T, H, I, E, K, quant], np.int32).tobytes())
+        for name in ("x", "w1", "w2"):
+            f.write(np.ascontiguousarray(d[name]).tobytes())
+        if quant:
+            f.write(d["w1_scale"].astype(np.float32).tobytes())
+            f.write(d["w2_scale"].astype(np.float32).tobytes())
+        f.write(d["topk_ids"].astype(np.int32).tobytes())
+        f.write(d["topk_w"].astype(np.float32).tobytes())
+    r = subprocess.run([exe, prob, res], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr + r.stdout
+    raw = open(res, "rb").read()
+    cap = O.sort_capacity(T, K, E, 128)
+    npp = int(np.frombuffer(raw[:4], np.int32)[0])
+    sids = np.frombuffer(raw[4:4 + cap * 4], np.int32)
+    out = np.frombuffer(raw[4 + cap * 4:], np.uint16).reshape(T, H)
+    ref_sort = O.moe_sorting(d["topk_ids"], d["topk_w"], E, 128)
+    assert npp == int(ref_sort["num_tokens_post_pad"][0]) and (sids == ref_sort["sorted_token_ids"]).all()
+    check(d, out, run_oracle(d))

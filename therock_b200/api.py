@@ -90,7 +90,7 @@ def lib() -> ctypes.CDLL:
         l.fmoe_route.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp]
         l.fmoe_ep_plan.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
         l.fmoe_ep_publish.argtypes = [vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp]
-        l.fmoe_ep_barrier.argtypes = [vp, ctypes.POINTER(EpLayout), i32, i32, i32, vp, i32, vp]
+        l.fmoe_ep_barrier.argtypes = [vp, ctypes.POINTER(EpLayout), i32, i32, i32, vp, vp, i32, vp]
         l.fmoe_ep_dispatch.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, ctypes.POINTER(EpLayout),
                                        i32, i32, vp, vp]
         l.fmoe_ep_return.argtypes = [vp, i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp]

@@ -37,8 +37,16 @@ __global__ void ep_publish_kernel(const int32_t* __restrict__ cum, const uint64_
 }
 
 __global__ void ep_barrier_kernel(const uint64_t* __restrict__ peer_base, uint64_t flags_off, int me, int G,
-                                  int epoch, int32_t* __restrict__ status, long long limit_cycles) {
+                                  int epoch, int32_t* __restrict__ epoch_counter,
+                                  int32_t* __restrict__ status, long long limit_cycles) {
   const int p = threadIdx.x;
+  if (epoch_counter != nullptr) {
+    // the epoch lives on the device: every launch (or graph replay) of this kernel advances it
+    __shared__ int32_t next;
+    if (threadIdx.x == 0) next = ++(*epoch_counter);
+    __syncthreads();
+    epoch = next;
+  }
   if (p >= G) return;
   __threadfence_system();   // everything this rank wrote before the barrier is visible first
   volatile int32_t* theirs = peer_ptr<int32_t>(peer_base, p, flags_off) + me;
@@ -128,12 +136,12 @@ int fmoe_ep_publish(const int32_t* cum, const uint64_t* peer_base, const fmoe_ep
 }
 
 int fmoe_ep_barrier(const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
-                    int32_t epoch, int32_t* status, int32_t timeout_ms, void* stream) {
+                    int32_t epoch, int32_t* epoch_counter, int32_t* status, int32_t timeout_ms, void* stream) {
   if (!peer_base || !lay || !status || G <= 0 || G > fmoe::kMaxRanks || timeout_ms < 0) return FMOE_ERR_INVALID_ARG;
   // clock64 ticks at the SM clock (<= ~2 GHz): 2e6 cycles per millisecond is an upper bound
   const long long limit = timeout_ms > 0 ? 2000000LL * timeout_ms : 8000000000LL;   // default: about four seconds
   fmoe::ep_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(peer_base, lay->flags, me, G, epoch,
-                                                                          status, limit);
+                                                                          epoch_counter, status, limit);
   return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
 }
 

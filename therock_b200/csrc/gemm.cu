@@ -76,8 +76,8 @@ cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const G
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  fmoe_grouped_gemm_kernel<kFp8, kEpi><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  return launch_pdl(fmoe_grouped_gemm_kernel<kFp8, kEpi>, dim3(grid), dim3(kGemmThreads), kGemmSmemBytes, stream,
+                    ta, tb, p);
 }
 
 template <bool kFp8, int kEpi>
@@ -91,8 +91,8 @@ cudaError_t launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, co
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  fmoe_grouped_gemm_pair_kernel<kFp8, kEpi><<<grid, kGemmThreads, kPairSmemBytes, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  return launch_pdl(fmoe_grouped_gemm_pair_kernel<kFp8, kEpi>, dim3(grid), dim3(kGemmThreads), kPairSmemBytes,
+                    stream, ta, tb, p);
 }
 
 }  // namespace
@@ -109,6 +109,15 @@ int gemm_mode_from_env() {
 }
 
 int device_sm_count() { return sm_count(); }
+
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FMOE_PDL");
+    on = (e && std::strcmp(e, "0") == 0) ? 0 : 1;
+  }
+  return on == 1;
+}
 
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
   CUtensorMap ta, tb;
@@ -163,10 +172,10 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
       configured[dev][which] = true;
     }
     if (which == 0)
-      fmoe_grouped_gemm_block_kernel<kEpiSiluMul><<<grid, kBlockGemmThreads, kBlockSmemBytes, stream>>>(ta, tb, bp);
-    else
-      fmoe_grouped_gemm_block_kernel<kEpiScaledSlots><<<grid, kBlockGemmThreads, kBlockSmemBytes, stream>>>(ta, tb, bp);
-    return cudaGetLastError();
+      return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpiSiluMul>, dim3(grid), dim3(kBlockGemmThreads),
+                        kBlockSmemBytes, stream, ta, tb, bp);
+    return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpiScaledSlots>, dim3(grid), dim3(kBlockGemmThreads),
+                      kBlockSmemBytes, stream, ta, tb, bp);
   }
   const bool pair = g.mode == 2;
   if (pair) {

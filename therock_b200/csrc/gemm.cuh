@@ -222,6 +222,8 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements per stage
   constexpr int kUmmaKBytes = 32;                   // one MMA consumes 32 bytes of K per row
 
+  // Everything the previous kernel produced is read after this point.
+  ptx::pdl_wait();
   // The block table is read on every tile boundary by the producer; keep it on chip so the
   // decode does not sit on the critical path with dependent global loads.
   for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
@@ -355,6 +357,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (!ok && epi_tid == 0) atomicExch(p.status, kStatusGemmTimeout | 3);
   }
 
+  ptx::pdl_release();     // the next kernel may start its prologue while this CTA winds down
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -422,6 +425,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;
   constexpr int kUmmaKBytes = 32;
 
+  ptx::pdl_wait();
   for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -569,6 +573,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   // Neither CTA may leave while its partner can still signal its barriers or read its
   // shared memory through a pair MMA.
+  ptx::pdl_release();
   ptx::tc_fence_before();
   ptx::cluster_sync_all();
   if (warp == 1) {
@@ -620,6 +625,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int lane = threadIdx.x & 31;
   constexpr int kUmmaKBytes = 32;
 
+  ptx::pdl_wait();
   for (int i = threadIdx.x; i <= p.num_experts; i += kBlockGemmThreads) cum_s[i] = p.mblk_cum[i];
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBlockStages; ++s) {
@@ -856,6 +862,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (!ok && threadIdx.x == 128) atomicExch(p.status, kStatusGemmTimeout | 0x23);
   }
 
+  ptx::pdl_release();     // the next kernel may start its prologue while this CTA winds down
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -6,6 +6,26 @@
 
 namespace fmoe {
 
+// Launch `kernel` allowing it to overlap the tail of the previous kernel on the stream
+// (programmatic dependent launch).  The kernel must execute griddepcontrol.wait before it
+// touches its predecessor's output.  FMOE_PDL=0 turns the attribute off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // moe_sorting.  All outputs are device pointers; sorted_rows, mblk_cum and status_to_clear
 // (a status word the kernel resets to 0) may be null.  num_tokens_dev (optional) is a device
 // int that lowers the token count below T; id_div > 1 buckets by id / id_div (the rank

@@ -13,6 +13,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ----------------------------------------------------------------------------- dependent launch
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute
+// may be scheduled while its predecessor on the stream drains.  It must call pdl_wait()
+// before it reads anything the predecessor wrote (a no-op for ordinary launches);
+// pdl_release() lets the successor start being scheduled.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

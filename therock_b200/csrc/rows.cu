@@ -7,6 +7,7 @@
 #include <cuda_fp8.h>
 
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace fmoe {
 namespace {
@@ -48,6 +49,8 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
                    const int32_t* __restrict__ row_ids, const int32_t* __restrict__ num_post_pad,
                    void* __restrict__ dst, float* __restrict__ scales,
                    const int32_t* __restrict__ live_ids) {
+  ptx::pdl_wait();
+  ptx::pdl_release();
   const int slot = blockIdx.x;
   if (slot >= *num_post_pad) return;
   // identity mode (quantising the intermediate): slots without a token are skipped outright
@@ -164,6 +167,8 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
 __global__ void __launch_bounds__(kRowThreads)
 combine_kernel(const float4* __restrict__ slots, const int32_t* __restrict__ topk_ids, int K, int E,
                int H, uint2* __restrict__ out, const int32_t* __restrict__ num_tokens_dev) {
+  ptx::pdl_wait();
+  ptx::pdl_release();
   const int t = blockIdx.x;
   if (num_tokens_dev && t >= *num_tokens_dev) return;   // rows past the device-side count
   const int nvec = H >> 2;
@@ -223,19 +228,17 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
   const dim3 grid(static_cast<unsigned>(cap));
   const uint4* s = reinterpret_cast<const uint4*>(src);
   if (quant == 0)
-    gather_rows_kernel<0><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
+    return launch_pdl(gather_rows_kernel<0>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   else if (quant == 1)
-    gather_rows_kernel<1><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
+    return launch_pdl(gather_rows_kernel<1>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   else
-    gather_rows_kernel<2><<<grid, kRowThreads, 0, stream>>>(s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
-  return cudaGetLastError();
+    return launch_pdl(gather_rows_kernel<2>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
 }
 
 cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev) {
-  combine_kernel<<<T, kRowThreads, 0, stream>>>(reinterpret_cast<const float4*>(slots), topk_ids, K,
-                                                E, H, reinterpret_cast<uint2*>(out), num_tokens_dev);
-  return cudaGetLastError();
+  return launch_pdl(combine_kernel, dim3(T), dim3(kRowThreads), 0, stream, reinterpret_cast<const float4*>(slots),
+                    topk_ids, K, E, H, reinterpret_cast<uint2*>(out), num_tokens_dev);
 }
 
 }  // namespace fmoe

@@ -9,6 +9,7 @@
 // 32-wide group, from the match mask).  All arithmetic is integer: the result is
 // bit-exact by construction.
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace fmoe {
 namespace {
@@ -24,6 +25,8 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
                    int32_t* __restrict__ sorted_rows, int32_t* __restrict__ sorted_expert_ids,
                    int32_t* __restrict__ num_post_pad, int32_t* __restrict__ mblk_cum,
                    int32_t* __restrict__ status_to_clear, int32_t* __restrict__ inv_out) {
+  ptx::pdl_wait();      // inputs may come from the kernel just before this one
+  ptx::pdl_release();
   extern __shared__ int32_t sm[];
   int32_t* cnt = sm;                      // [kSortWarps][E] counts, later running offsets
   int32_t* blk_cum = sm + kSortWarps * E; // [E + 1] cumulative padded blocks
@@ -47,15 +50,26 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
     for (int i = tid; i < cap / block_m; i += kSortThreads) sorted_expert_ids[i] = -1;
   __syncthreads();
 
-  // pass 1: per-(warp, expert) histogram
+  // pass 1: per-(warp, expert) histogram.  Four 32-wide groups are loaded before any is
+  // processed so the global-load latency is paid once per 128 pairs, not once per 32.
+  constexpr int kUnroll = 4;
   int32_t* my_cnt = cnt + warp * E;
-  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
-    const int r = r0 + lane;
-    int e = (r < r_end) ? topk_ids[r] : -1;
-    e = (e < 0 || e >= id_limit) ? -1 : e / id_div;
-    const unsigned mask = __match_any_sync(0xffffffffu, e);
-    if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
-    __syncwarp();
+  for (int r0 = r_begin; r0 < r_end; r0 += 32 * kUnroll) {
+    int ev[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int r = r0 + u * 32 + lane;
+      ev[u] = (r < r_end) ? topk_ids[r] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (r0 + u * 32 >= r_end) break;               // warp-uniform
+      int e = ev[u];
+      e = (e < 0 || e >= id_limit) ? -1 : e / id_div;
+      const unsigned mask = __match_any_sync(0xffffffffu, e);
+      if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
+      __syncwarp();
+    }
   }
   __syncthreads();
 
@@ -98,25 +112,37 @@ moe_sorting_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict
   if (tid == 0 && num_post_pad) num_post_pad[0] = blk_cum[E] * block_m;
   if (tid == 0 && status_to_clear) status_to_clear[0] = 0;
 
-  // pass 2: placement
-  for (int r0 = r_begin; r0 < r_end; r0 += 32) {
-    const int r = r0 + lane;
-    int e = (r < r_end) ? topk_ids[r] : -1;
-    e = (e < 0 || e >= id_limit) ? -1 : e / id_div;
-    const unsigned mask = __match_any_sync(0xffffffffu, e);
-    if (e >= 0) {
-      const int rank = __popc(mask & ((1u << lane) - 1u));
-      const int pos = blk_cum[e] * block_m + my_cnt[e] + rank;
-      sorted_token_ids[pos] = r / K;
-      if (sorted_weights) sorted_weights[pos] = topk_weight[r];
-      if (sorted_rows) sorted_rows[pos] = r;
-      if (inv_out) inv_out[r] = pos;
-    } else if (inv_out && r < r_end) {
-      inv_out[r] = -1;
+  // pass 2: placement (same four-group prefetch, weights included)
+  for (int r0 = r_begin; r0 < r_end; r0 += 32 * kUnroll) {
+    int ev[kUnroll];
+    float wv[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int r = r0 + u * 32 + lane;
+      ev[u] = (r < r_end) ? topk_ids[r] : -1;
+      wv[u] = (r < r_end && sorted_weights) ? topk_weight[r] : 0.0f;
     }
-    __syncwarp();
-    if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
-    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (r0 + u * 32 >= r_end) break;               // warp-uniform
+      const int r = r0 + u * 32 + lane;
+      int e = ev[u];
+      e = (e < 0 || e >= id_limit) ? -1 : e / id_div;
+      const unsigned mask = __match_any_sync(0xffffffffu, e);
+      if (e >= 0) {
+        const int rank = __popc(mask & ((1u << lane) - 1u));
+        const int pos = blk_cum[e] * block_m + my_cnt[e] + rank;
+        sorted_token_ids[pos] = r / K;
+        if (sorted_weights) sorted_weights[pos] = wv[u];
+        if (sorted_rows) sorted_rows[pos] = r;
+        if (inv_out) inv_out[r] = pos;
+      } else if (inv_out && r < r_end) {
+        inv_out[r] = -1;
+      }
+      __syncwarp();
+      if (e >= 0 && lane == (__ffs(mask) - 1)) my_cnt[e] += __popc(mask);
+      __syncwarp();
+    }
   }
 }
 
@@ -135,11 +161,10 @@ cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
   }
-  moe_sorting_kernel<<<1, kSortThreads, smem, stream>>>(
-      topk_ids, topk_weight, T, num_tokens_dev, K, E, id_div, block_m, static_cast<int>(cap),
-      sorted_token_ids, sorted_weights, sorted_rows, sorted_expert_ids, num_post_pad, mblk_cum,
-      status_to_clear, inv_out);
-  return cudaGetLastError();
+  return launch_pdl(moe_sorting_kernel, dim3(1), dim3(kSortThreads), smem, stream, topk_ids, topk_weight, T,
+                    num_tokens_dev, K, E, id_div, block_m, static_cast<int>(cap), sorted_token_ids,
+                    sorted_weights, sorted_rows, sorted_expert_ids, num_post_pad, mblk_cum, status_to_clear,
+                    inv_out);
 }
 
 }  // namespace fmoe

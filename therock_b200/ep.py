@@ -228,17 +228,17 @@ class PeerExpertParallelMoE:
                                      d_scale=w2_scale, num_tokens_dev=self.n_recv, expected_tokens=R)
         self.args.workspace = torch.empty(api.fused_moe_workspace_size(traits, self.args), dtype=torch.uint8,
                                           device=dev)
-        self.epoch = 0
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         self.barrier_timeout_ms = 0          # 0 = the library default (about four seconds)
         self.trace = None                    # set to [] to collect (phase, cuda event) marks
         self._ctypes = ctypes
         self.launches_per_step = 8 + api.launches_per_run(traits)
 
     def _barrier(self, stream):
-        self.epoch += 1
+        # the epoch is a device-side counter, so the launch arguments never change
         self.api._check(self.api.lib().fmoe_ep_barrier(self.peer_base.data_ptr(), self._ctypes.byref(self.lay),
-                                                       self.rank, self.world, self.epoch, self.status.data_ptr(),
-                                                       self.barrier_timeout_ms, stream))
+                                                       self.rank, self.world, 0, self.epoch_dev.data_ptr(),
+                                                       self.status.data_ptr(), self.barrier_timeout_ms, stream))
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
