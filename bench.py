@@ -40,6 +40,9 @@ CONFIGS = {
     "C3": dict(T=16, H=4096, I=14336, E=8, K=2, quant=1, label="mixtral-8x7b-decode-fp8"),
     "C4": dict(T=8192, H=7168, I=2048, E=256, K=8, quant=2, routing="sigmoid",
                label="deepseek-v3-shape-fp8-block128"),
+    # analysis only: the C4 shape with per-token / per-channel scales (plain fp8 kernels)
+    "C4tc": dict(T=8192, H=7168, I=2048, E=256, K=8, quant=1, routing="sigmoid",
+                 label="deepseek-v3-shape-fp8-token-channel"),
 }
 QUANT_NAME = {0: "none", 1: "token_channel", 2: "block128"}
 
@@ -288,8 +291,14 @@ def run_gpu(a, c):
         raise SystemExit("experts and tokens must divide over the ranks")
 
     M.lib()  # fails loudly when the CUDA library has not been built
-    traits = M.FusedMoeTraits(prec_w="bf16" if c["quant"] == 0 else "fp8", quant=QUANT_NAME[c["quant"]])
+    layout = a.weight_layout
+    traits = M.FusedMoeTraits(prec_w="bf16" if c["quant"] == 0 else "fp8", quant=QUANT_NAME[c["quant"]],
+                              weight_layout=layout)
     d = device_inputs(c, dev, rank, world)
+    if layout == "tiled128":          # offline pre-shuffle of the weights (not part of the timed step)
+        from therock_b200 import weights as Wt
+        d["w1_rowmajor"], d["w2_rowmajor"] = d["w1"], d["w2"]
+        d["w1"], d["w2"] = Wt.tile_weights(d["w1"]), Wt.tile_weights(d["w2"])
     T_local, H = d["x"].shape
 
     if world == 1:
@@ -486,6 +495,7 @@ def run_gpu(a, c):
                     "ms_per_step": ms_e2e / n_e2e, "steps": n_e2e},
             "gpu_launches": launches_per_step * a.steps, "clocks": clocks}
     line["config"]["launch"] = "cuda_graph_replay" if use_graph else "stream"
+    line["config"]["weight_layout"] = layout
     if world > 1:
         line["config"]["ep_transport"] = ep_transport
     if ep_stage is not None:
@@ -520,8 +530,8 @@ def run_gpu(a, c):
         from oracle import oracle as O
         O.build()
         hd = dict(x=d["x_full"].view(torch.int16).cpu().numpy().view(np.uint16),
-                  w1=(d["w1"].view(torch.int16) if c["quant"] == 0 else d["w1"]).cpu().numpy(),
-                  w2=(d["w2"].view(torch.int16) if c["quant"] == 0 else d["w2"]).cpu().numpy(),
+                  w1=(d.get("w1_rowmajor", d["w1"]).view(torch.int16) if c["quant"] == 0 else d.get("w1_rowmajor", d["w1"])).cpu().numpy(),
+                  w2=(d.get("w2_rowmajor", d["w2"]).view(torch.int16) if c["quant"] == 0 else d.get("w2_rowmajor", d["w2"])).cpu().numpy(),
                   w1_scale=None if d["s1"] is None else d["s1"].cpu().numpy(),
                   w2_scale=None if d["s2"] is None else d["s2"].cpu().numpy(),
                   topk_ids=d["ids_full"].cpu().numpy(), topk_w=d["w_full"].cpu().numpy(), quant=c["quant"])
@@ -553,6 +563,8 @@ def main():
     ap.add_argument("--config", default="C1", choices=sorted(CONFIGS))
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the token count (small cases for profiler captures)")
+    ap.add_argument("--weight-layout", choices=["row_major", "tiled128"], default="row_major",
+                    help="tiled128: weights pre-shuffled so every 128x128-byte operand tile is contiguous")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                     help="replay the step from a CUDA graph in the timed loop (auto: decode-sized batches)")
     ap.add_argument("--kernel-only", action="store_true",

@@ -26,6 +26,7 @@ struct fused_moe_traits {
   int gate_only = 0;             // 0: gate and up rows packed as [2I, H]
   int block_m = 128;             // sorted M-block
   int gemm_mode = 0;             // 0 = per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel
+  std::string weight_layout = "row_major";   // or "tiled128": weights pre-shuffled into 16 KiB tiles
 };
 
 struct fused_moe_args {
@@ -69,6 +70,9 @@ inline int to_c(const fused_moe_traits& t, fmoe_traits_c* c) {
   c->gate_only = t.gate_only;
   c->block_m = t.block_m;
   c->gemm_mode = t.gemm_mode;
+  if (t.weight_layout == "row_major") c->weight_layout = FMOE_WEIGHTS_ROW_MAJOR;
+  else if (t.weight_layout == "tiled128") c->weight_layout = FMOE_WEIGHTS_TILED128;
+  else return FMOE_ERR_INVALID_ARG;
   return FMOE_OK;
 }
 inline void to_c(const fused_moe_args& a, fmoe_args_c* c) {

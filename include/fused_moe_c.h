@@ -55,6 +55,13 @@ enum fmoe_quant {
 
 enum fmoe_activation { FMOE_ACT_SILU = 0 };
 
+enum fmoe_weight_layout {
+  FMOE_WEIGHTS_ROW_MAJOR = 0, /* [E, rows, K], K contiguous */
+  FMOE_WEIGHTS_TILED128 = 1   /* pre-shuffled: [E, rows/128, K_bytes/128, 128 rows, 128 bytes] -- every
+                                 128-row x 128-byte operand tile is one contiguous 16 KiB block, so the
+                                 weight stream reads DRAM in long bursts (same values, same results) */
+};
+
 /* Compile-time-like selection of the operator variant (ck_tile's fused_moe_traits role). */
 typedef struct fmoe_traits_c {
   int32_t quant;        /* fmoe_quant */
@@ -64,7 +71,8 @@ typedef struct fmoe_traits_c {
   int32_t block_m;      /* rows per sorted block; 128 */
   int32_t gemm_mode;    /* 0 = chosen per GEMM from the expected tile counts, 1 = single-CTA
                            kernel, 2 = CTA-pair kernel (cta_group::2) */
-  int32_t reserved[2];
+  int32_t weight_layout; /* fmoe_weight_layout of w1 and w2 */
+  int32_t reserved[1];
 } fmoe_traits_c;
 
 /* Run-time arguments (ck_tile's fused_moe_args role).  All pointers are device pointers. */

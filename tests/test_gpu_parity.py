@@ -368,3 +368,23 @@ def test_cpp_host_program_through_fused_moe_hpp(quant, tmp_path):
     ref_sort = O.moe_sorting(d["topk_ids"], d["topk_w"], E, 128)
     assert npp == int(ref_sort["num_tokens_post_pad"][0]) and (sids == ref_sort["sorted_token_ids"]).all()
     check(d, out, run_oracle(d))
+
+
+@pytest.mark.parametrize("quant", [0, 1, 2])
+@pytest.mark.parametrize("gemm_mode", [1, 2])
+def test_tiled_weight_layout_gives_identical_results(quant, gemm_mode):
+    from therock_b200 import weights as W
+    d = O.make_inputs(300, 512, 384, 6, 2, quant, "softmax", seed=51)
+    base = args_for(d)
+    tr = traits_for(quant)
+    tr.gemm_mode = gemm_mode
+    ref = out_bits(M.fused_moe(tr, base)).copy()
+    tiled = args_for(d)
+    tiled.g, tiled.d = W.tile_weights(tiled.g), W.tile_weights(tiled.d)
+    tr2 = traits_for(quant)
+    tr2.gemm_mode = gemm_mode
+    tr2.weight_layout = "tiled128"
+    got = out_bits(M.fused_moe(tr2, tiled))
+    torch.cuda.synchronize()
+    assert (got == ref).all()
+    check(d, got, run_oracle(d))

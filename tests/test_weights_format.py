@@ -38,3 +38,16 @@ def test_save_load_roundtrip_and_expert_shard(tmp_path):
         shard = W.load_expert_weights(path, experts=range(2, 4))
         assert torch.equal(shard["w1"].view(torch.uint8), q1[2:4].view(torch.uint8))
         assert shard["w2"].shape[0] == 2
+
+
+def test_tile_untile_roundtrip_and_tile_contiguity():
+    w = torch.arange(2 * 256 * 384, dtype=torch.int32).view(2, 256, 384).to(torch.bfloat16)
+    t = W.tile_weights(w)
+    assert t.shape == w.shape and torch.equal(W.untile_weights(t), w)
+    # tile (expert 1, row block 1, K block 2) is one contiguous run of 128 x 64 elements
+    flat = t.reshape(-1)
+    kb = 384 // 64
+    start = ((1 * 2 + 1) * kb + 2) * 128 * 64
+    assert torch.equal(flat[start:start + 128 * 64].view(128, 64), w[1, 128:256, 128:192])
+    q = torch.randint(0, 255, (3, 128, 256), dtype=torch.uint8)
+    assert torch.equal(W.untile_weights(W.tile_weights(q)), q)

@@ -23,7 +23,8 @@ class FmoeError(RuntimeError):
 class _Traits(ctypes.Structure):
     _fields_ = [("quant", ctypes.c_int32), ("weight_dtype", ctypes.c_int32),
                 ("activation", ctypes.c_int32), ("gate_only", ctypes.c_int32),
-                ("block_m", ctypes.c_int32), ("gemm_mode", ctypes.c_int32), ("reserved", ctypes.c_int32 * 2)]
+                ("block_m", ctypes.c_int32), ("gemm_mode", ctypes.c_int32), ("weight_layout", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 1)]
 
 
 class _Args(ctypes.Structure):
@@ -114,6 +115,7 @@ class FusedMoeTraits:
     gate_only: int = 0
     block_m: int = 128
     gemm_mode: int = 0            # 0 = per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel
+    weight_layout: str = "row_major"   # or "tiled128" (see therock_b200.weights.tile_weights)
 
     def to_c(self) -> _Traits:
         if self.prec_i != "bf16" or self.prec_o != "bf16":
@@ -131,6 +133,9 @@ class FusedMoeTraits:
         t.gate_only = self.gate_only
         t.block_m = self.block_m
         t.gemm_mode = self.gemm_mode
+        if self.weight_layout not in ("row_major", "tiled128"):
+            raise FmoeError(-1, f"unknown weight layout {self.weight_layout!r}")
+        t.weight_layout = 0 if self.weight_layout == "row_major" else 1
         return t
 
 

@@ -42,6 +42,8 @@ int validate_traits(const fmoe_traits_c* t) {
   if (t->gate_only != 0) return fail(FMOE_ERR_UNSUPPORTED, "gate_only variant is not built");
   if (t->block_m != fmoe::kBlockM) return fail(FMOE_ERR_UNSUPPORTED, "block_m must be %d", fmoe::kBlockM);
   if (t->gemm_mode < 0 || t->gemm_mode > 2) return fail(FMOE_ERR_INVALID_ARG, "gemm_mode must be 0, 1 or 2");
+  if (t->weight_layout != FMOE_WEIGHTS_ROW_MAJOR && t->weight_layout != FMOE_WEIGHTS_TILED128)
+    return fail(FMOE_ERR_INVALID_ARG, "unknown weight layout %d", t->weight_layout);
   return FMOE_OK;
 }
 
@@ -54,6 +56,11 @@ int validate_dims(const fmoe_traits_c* t, const fmoe_args_c* a) {
   if (a->I % fmoe::kSlabRows) return fail(FMOE_ERR_UNSUPPORTED, "intermediate size must be a multiple of %d", fmoe::kSlabRows);
   if (a->H % fmoe::kTileN) return fail(FMOE_ERR_UNSUPPORTED, "hidden size must be a multiple of %d", fmoe::kTileN);
   if (static_cast<int64_t>(a->T) * a->K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
+  if (t->weight_layout == FMOE_WEIGHTS_TILED128) {
+    const int es = t->quant == FMOE_QUANT_NONE ? 2 : 1;
+    if ((a->H * es) % 128 || (a->I * es) % 128)
+      return fail(FMOE_ERR_UNSUPPORTED, "tiled weights need K extents that are multiples of 128 bytes");
+  }
   if (t->quant == FMOE_QUANT_BLOCK128 && (a->H % 128 || a->I % 128))
     return fail(FMOE_ERR_UNSUPPORTED, "block128 needs hidden and intermediate sizes that are multiples of 128");
   return FMOE_OK;
@@ -236,6 +243,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   fmoe::GemmLaunch g{};
   int drv = 0;
   g.fp8 = fp8;
+  g.b_tiled = traits->weight_layout == FMOE_WEIGHTS_TILED128;
   g.block_scale = blk;
   g.num_experts = a.E;
   g.mblk_cum = mblk_cum;

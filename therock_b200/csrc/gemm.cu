@@ -122,8 +122,15 @@ bool pdl_enabled() {
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
   CUtensorMap ta, tb;
   CUresult r = make_map(&ta, g.a, g.fp8, g.a_rows, g.k_elems);
-  if (r == CUDA_SUCCESS)
-    r = make_map(&tb, g.b, g.fp8, static_cast<int64_t>(g.num_experts) * g.b_rows_per_expert, g.k_elems);
+  const int esize = g.fp8 ? 1 : 2;
+  const int k_blocks = (g.k_elems * esize + kStageKBytes - 1) / kStageKBytes;
+  if (r == CUDA_SUCCESS) {
+    if (g.b_tiled)   // a [tiles * 128, 128 bytes] matrix: every box is one contiguous 16 KiB tile
+      r = make_map(&tb, g.b, g.fp8, static_cast<int64_t>(g.num_experts) * g.b_rows_per_expert * k_blocks,
+                   kStageKBytes / esize);
+    else
+      r = make_map(&tb, g.b, g.fp8, static_cast<int64_t>(g.num_experts) * g.b_rows_per_expert, g.k_elems);
+  }
   if (r != CUDA_SUCCESS) {
     if (drv_err) *drv_err = static_cast<int>(r);
     return cudaErrorInvalidValue;
@@ -144,6 +151,7 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   p.out = g.out;
   p.ld_out = g.ld_out;
   p.status = g.status;
+  p.b_tiled_kb = g.b_tiled ? k_blocks : 0;
   {
     static int dbg = -1;       // FMOE_DEBUG_FLAGS: timing experiments only
     if (dbg < 0) { const char* e = getenv("FMOE_DEBUG_FLAGS"); dbg = e ? atoi(e) : 0; }

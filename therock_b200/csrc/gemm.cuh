@@ -56,6 +56,8 @@ struct GemmParams {
   int* status;                  // device status word
   uint64_t desc_template;       // shared-memory matrix descriptor without the address
   uint32_t idesc;               // tcgen05 instruction descriptor
+  int b_tiled_kb;               // 0: B is row-major; > 0: B is stored as contiguous 128 x 128-byte
+                                // tiles and this is the number of 128-byte K blocks per row
   uint32_t debug_flags;         // diagnostics only (results are invalid when set): bit 0 = the
                                 // epilogue skips its work, bit 1 = no MMA is issued
 };
@@ -84,6 +86,17 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const int* cum, int E
 }
 
 // SiLU with the fast exponential and division (a few ulp; far inside the bf16 rounding of y).
+// TMA coordinates of the 128-row B slab starting at row `b_row` for K stage `k`.
+__device__ __forceinline__ void b_coords(const GemmParams& p, int b_row, int k, int elems_per_stage, int& x, int& y) {
+  if (p.b_tiled_kb > 0) {
+    x = 0;
+    y = ((b_row >> 7) * p.b_tiled_kb + k) << 7;      // tile index * 128 rows of 128 bytes
+  } else {
+    x = k * elems_per_stage;
+    y = b_row;
+  }
+}
+
 __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 // Per-warp staging area for the epilogue's transposed stores: 32 rows x 36 words.
@@ -274,9 +287,12 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t sb = sa + kABytes;
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
           const int kx = k * kElemsPerStage;
+          int bx, by0, by1;
+          b_coords(p, b_row0, k, kElemsPerStage, bx, by0);
+          b_coords(p, b_row1, k, kElemsPerStage, bx, by1);
           ptx::tma_load_2d(sa, &tm_a, full, kx, a_row);
-          ptx::tma_load_2d(sb, &tm_b, full, kx, b_row0);
-          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, kx, b_row1);
+          ptx::tma_load_2d(sb, &tm_b, full, bx, by0);
+          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, bx, by1);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -485,8 +501,10 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t sa = ptx::smem_u32(smem + stage * kPairStageBytes);
           if (rank == 0) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&full_bar[stage]), 2 * kPairStageBytes);
           const int kx = k * kElemsPerStage;
+          int bx, by;
+          b_coords(p, b_row, k, kElemsPerStage, bx, by);
           ptx::tma_load_2d_pair(sa, &tm_a, full0, kx, a_row);
-          ptx::tma_load_2d_pair(sa + kABytes, &tm_b, full0, kx, b_row);
+          ptx::tma_load_2d_pair(sa + kABytes, &tm_b, full0, bx, by);
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -674,9 +692,12 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t sb = sa + kABytes;
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
           const int kx = k * 128;
+          int bx, by0, by1;
+          b_coords(p, b_row0, k, 128, bx, by0);
+          b_coords(p, b_row1, k, 128, bx, by1);
           ptx::tma_load_2d(sa, &tm_a, full, kx, a_row);
-          ptx::tma_load_2d(sb, &tm_b, full, kx, b_row0);
-          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, kx, b_row1);
+          ptx::tma_load_2d(sb, &tm_b, full, bx, by0);
+          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, bx, by1);
           if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
         }
       }

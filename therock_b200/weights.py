@@ -41,6 +41,29 @@ def quantize_experts(w: torch.Tensor, mode: str):
     raise ValueError(f"unknown quantisation mode {mode!r}")
 
 
+def tile_weights(w: torch.Tensor) -> torch.Tensor:
+    """Pre-shuffle [E, rows, K] weights (bf16 or e4m3 bytes) into the "tiled128" layout:
+    [E, rows/128, K_bytes/128, 128 rows, 128 bytes], i.e. every 128-row x 128-byte operand tile
+    becomes one contiguous 16 KiB block.  Returned with the original shape and dtype (the
+    bytes are what changes)."""
+    E, rows, K = w.shape
+    es = w.element_size()
+    kt = 128 // es                      # elements per 128 bytes
+    if rows % 128 or (K * es) % 128:
+        raise ValueError("tiled128 needs rows and K bytes that are multiples of 128")
+    t = w.view(E, rows // 128, 128, K // kt, kt).permute(0, 1, 3, 2, 4).contiguous()
+    return t.view(E, rows, K)
+
+
+def untile_weights(w: torch.Tensor) -> torch.Tensor:
+    """Inverse of tile_weights."""
+    E, rows, K = w.shape
+    es = w.element_size()
+    kt = 128 // es
+    t = w.view(E, rows // 128, K // kt, 128, kt).permute(0, 1, 3, 2, 4).contiguous()
+    return t.view(E, rows, K)
+
+
 def _np(t: torch.Tensor) -> np.ndarray:
     t = t.detach().cpu().contiguous()
     if t.dtype == torch.bfloat16:
