@@ -512,17 +512,25 @@ def run_gpu(a, c):
             peak_kind = peaks["source"] + " copy bandwidth"
         else:
             achieved = 4.0 * c["T"] * c["K"] * c["H"] * c["I"] / (g1_ms * 1e-3) / 1e12
-            long_loop = ms_total > 1000.0
-            peak = peaks["bf16_sustained"] if long_loop else peaks["bf16_burst"]
-            peak_kind = f"{peaks['source']} cuBLAS bf16, {'sustained' if long_loop else 'burst'}"
+            # Denominator: the sustained cuBLAS figure when this loop ran in the same regime it was
+            # measured in (back-to-back launches under the power cap: sw_power_cap active and the
+            # median SM clock well below the maximum), otherwise the burst figure.
+            capped = bool(clocks and clocks.get("sm_mhz") and "sw_power_cap" in clocks.get("reasons", [])
+                          and clocks["sm_mhz"] < 0.8 * clocks["sm_max_mhz"])
+            sustained_regime = ms_total > 1000.0 or capped
+            mult = 2.0 if c["quant"] != 0 else 1.0
+            peak = (peaks["bf16_sustained"] if sustained_regime else peaks["bf16_burst"]) * mult
+            peak_kind = f"{peaks['source']} cuBLAS bf16, {'sustained' if sustained_regime else 'burst'}"
             if c["quant"] != 0:
-                peak *= 2.0
                 peak_kind += " x2 (no fp8 peak was measured)"
             unit, bound = "TFLOP/s", "tensor"
         line["roofline"] = {"bound": bound, "kernel": "fmoe_grouped_gemm_kernel (gate+up, SiLU*up epilogue)",
                             "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                             "traffic": GEMM1_DRAM_TRAFFIC_BYTES.get(a.config), "peak_kind": peak_kind,
                             "ms_per_launch": g1_ms}
+        if bound == "tensor":
+            line["roofline"]["frac_of_burst"] = achieved / (peaks["bf16_burst"] * mult)
+            line["roofline"]["frac_of_sustained"] = achieved / (peaks["bf16_sustained"] * mult)
         line["stage_ms"] = per
 
     if world == 1:
