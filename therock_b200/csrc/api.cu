@@ -251,6 +251,9 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   g.sorted_weights = sorted_w;
   g.status = status;
   g.max_m_blocks = static_cast<int>(plan.cap / fmoe::kBlockM);
+  // no expert can receive more rows than there are routed pairs: lets decode-sized batches
+  // stage only the rows that can be real
+  g.max_live_rows = static_cast<long long>(a.T) * a.K <= fmoe::kBlockM ? a.T * a.K : 0;
   // Kernel flavour per GEMM.  The CTA-pair kernel moves a third less of the operands per flop
   // (about 5 % faster per tile) but pads every expert to an even number of row blocks and
   // has half as many schedulable units, so whether it wins is a question of wave counts:

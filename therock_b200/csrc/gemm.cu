@@ -31,14 +31,15 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Row-major [rows, k_elems] matrix, box = 128 bytes of K x 128 rows, 128-byte swizzle.
-CUresult make_map(CUtensorMap* tm, const void* base, bool fp8, int64_t rows, int k_elems) {
+// Row-major [rows, k_elems] matrix, box = 128 bytes of K x box_rows rows, 128-byte swizzle.
+CUresult make_map(CUtensorMap* tm, const void* base, bool fp8, int64_t rows, int k_elems,
+                  int box_rows = kSlabRows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return CUDA_ERROR_NOT_FOUND;
   const int esize = fp8 ? 1 : 2;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_elems), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(k_elems) * esize};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kStageKBytes / esize), static_cast<cuuint32_t>(kSlabRows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kStageKBytes / esize), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   return fn(tm, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -65,18 +66,19 @@ int sm_count() {
   return n[dev];
 }
 
-template <bool kFp8, int kEpi>
+template <bool kFp8, int kEpi, int kARows = kBlockM>
 cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                            int grid, cudaStream_t stream) {
   static bool configured[kMaxDevices] = {false};   // per instantiation and device
+  constexpr int kSmem = GemmStageCfg<kARows>::kSmemBytesT;
   const int dev = current_device();
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_kernel<kFp8, kEpi>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_kernel<kFp8, kEpi, kARows>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  return launch_pdl(fmoe_grouped_gemm_kernel<kFp8, kEpi>, dim3(grid), dim3(kGemmThreads), kGemmSmemBytes, stream,
+  return launch_pdl(fmoe_grouped_gemm_kernel<kFp8, kEpi, kARows>, dim3(grid), dim3(kGemmThreads), kSmem, stream,
                     ta, tb, p);
 }
 
@@ -121,7 +123,9 @@ bool pdl_enabled() {
 
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
   CUtensorMap ta, tb;
-  CUresult r = make_map(&ta, g.a, g.fp8, g.a_rows, g.k_elems);
+  // decode-sized batches: only the first kDecodeARows rows of a block can be real
+  const bool few_rows = g.max_live_rows > 0 && g.max_live_rows <= kDecodeARows && !g.block_scale && g.mode != 2;
+  CUresult r = make_map(&ta, g.a, g.fp8, g.a_rows, g.k_elems, few_rows ? kDecodeARows : kSlabRows);
   const int esize = g.fp8 ? 1 : 2;
   const int k_blocks = (g.k_elems * esize + kStageKBytes - 1) / kStageKBytes;
   if (r == CUDA_SUCCESS) {
@@ -202,6 +206,15 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   }
   const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
   const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
+  if (few_rows) {
+    if (g.fp8)
+      return g.epilogue == kEpiSiluMul
+                 ? launch_variant<true, kEpiSiluMul, kDecodeARows>(ta, tb, p, grid, stream)
+                 : launch_variant<true, kEpiScaledSlots, kDecodeARows>(ta, tb, p, grid, stream);
+    return g.epilogue == kEpiSiluMul
+               ? launch_variant<false, kEpiSiluMul, kDecodeARows>(ta, tb, p, grid, stream)
+               : launch_variant<false, kEpiScaledSlots, kDecodeARows>(ta, tb, p, grid, stream);
+  }
   if (g.fp8) {
     return g.epilogue == kEpiSiluMul ? launch_variant<true, kEpiSiluMul>(ta, tb, p, grid, stream)
                                      : launch_variant<true, kEpiScaledSlots>(ta, tb, p, grid, stream);

@@ -213,10 +213,29 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
   }
 }
 
-template <bool kFp8, int kEpi>
+// kARows: rows of the A tile that are actually fetched per K stage.  128 is the general
+// case.  For decode-sized batches (at most kARows routed rows in total, hence per expert) only
+// the first kARows rows of a block are real, so only those are loaded: the stage shrinks to
+// kARows*128 + 32 KiB bytes, one more stage fits, and more weight bytes are in flight per SM.
+// The MMA still reads 128 rows; the rows past kARows alias the start of the B slab, produce
+// values that belong to pad slots only, and are never stored.
+constexpr int kDecodeARows = 32;
+
+template <int kARows> struct GemmStageCfg {
+  static constexpr int kAStageBytes = kARows * kStageKBytes;
+  static constexpr int kStageBytesT = kAStageBytes + kBBytes;
+  static constexpr int kStagesT = kARows == kBlockM ? kStages : 5;
+  static constexpr int kSmemBytesT = kStagesT * kStageBytesT + kSmemMisc + kEpiStageReserve + 1024;
+};
+
+template <bool kFp8, int kEpi, int kARows = kBlockM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                          const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+  using Cfg = GemmStageCfg<kARows>;
+  constexpr int kStages = Cfg::kStagesT;             // shadows the general-case constants
+  constexpr int kStageBytes = Cfg::kStageBytesT;
+  constexpr int kABytes = Cfg::kAStageBytes;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &

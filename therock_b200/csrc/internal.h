@@ -77,6 +77,7 @@ struct GemmLaunch {
   int ld_out;
   int32_t* status;
   int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
+  int max_live_rows;            // upper bound on real rows in any block (0 = unknown, i.e. 128)
   bool b_tiled;                 // B is stored as contiguous 128-row x 128-byte tiles (see fmoe_weight_layout)
   bool block_scale;             // fp8 with 1x128 activation groups and 128x128 weight blocks:
                                 // a_scale is [a_rows, K/128], b_scale [E*b_rows/128, K/128]
