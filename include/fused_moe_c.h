@@ -143,6 +143,7 @@ typedef struct fmoe_ws_layout_c {
   uint64_t y_quant;           /* e4m3 [capacity, I] (fp8 variants) */
   uint64_t y_scale;           /* float[capacity] (fp8 variants) */
   uint64_t slots;             /* float [T*K, H]: weighted expert outputs before the combine */
+  uint64_t sort_scratch;      /* int32[128*E]: per-CTA histograms of the multi-CTA moe_sorting */
 } fmoe_ws_layout_c;
 
 FMOE_API int fmoe_get_workspace_layout(const fmoe_traits_c* traits, const fmoe_args_c* args,

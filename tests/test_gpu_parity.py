@@ -388,3 +388,29 @@ def test_tiled_weight_layout_gives_identical_results(quant, gemm_mode):
     torch.cuda.synchronize()
     assert (got == ref).all()
     check(d, got, run_oracle(d))
+
+
+@pytest.mark.parametrize("T,K,E", [(8192, 8, 256), (5000, 2, 8), (4096, 2, 8), (20000, 3, 1000), (8192, 1, 1)])
+def test_multi_cta_sorting_inside_fused_moe_is_bit_exact(T, K, E):
+    """fmoe_run uses the multi-CTA moe_sorting for >= 8192 pairs: same bits as the oracle."""
+    ids, w = O.route(O.normal((T, E), 7, 4), K, "softmax")
+    ids[::9, 0] = -1
+    H, I = 256, 128
+    d = dict(x=O.f32_to_bf16(O.normal((T, H), 7, 1)), w1=O.f32_to_bf16(O.normal((E, 2 * I, H), 7, 2, 0.02)),
+             w2=O.f32_to_bf16(O.normal((E, H, I), 7, 3, 0.02)), topk_ids=ids, topk_w=w, quant=0, w1_scale=None,
+             w2_scale=None)
+    args = args_for(d)
+    M.fused_moe(traits_for(0), args)
+    torch.cuda.synchronize()
+    lay = M.workspace_layout(traits_for(0), args)
+    ref = O.moe_sorting(ids, w, E, 128)
+    ws, cap = args.workspace, lay["capacity"]
+
+    def region(name, n):
+        return ws[lay[name]:lay[name] + 4 * n].view(torch.int32).cpu().numpy()
+    assert (region("sorted_token_ids", cap) == ref["sorted_token_ids"]).all()
+    assert (region("sorted_rows", cap) == ref["sorted_rows"]).all()
+    assert (region("sorted_weights", cap) == ref["sorted_weights"].view(np.int32)).all()
+    assert (region("sorted_expert_ids", cap // 128) == ref["sorted_expert_ids"]).all()
+    assert (region("mblk_cum", E + 1) == ref["mblk_cum"]).all()
+    assert int(region("meta", 2)[0]) == int(ref["num_tokens_post_pad"][0])

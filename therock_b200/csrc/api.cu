@@ -87,6 +87,7 @@ int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
   l.y_quant = take(fp8 ? static_cast<uint64_t>(cap) * a->I : 0);
   l.y_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 * (blk ? a->I / 128 : 1) : 0);
   l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * 4);
+  l.sort_scratch = take(fmoe::sort_scratch_words(a->E) * 4);
   l.total_bytes = off;
   return FMOE_OK;
 }
@@ -232,7 +233,8 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
 
   FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
                                      sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
-                                     mblk_cum, status, stream, a.num_tokens_dev));
+                                     mblk_cum, status, stream, a.num_tokens_dev, 1, nullptr,
+                                     reinterpret_cast<int32_t*>(ws + l.sort_scratch)));
   FMOE_STAGE(1);
   const bool blk = traits->quant == FMOE_QUANT_BLOCK128;
   const int qmode = !fp8 ? 0 : (blk ? 2 : 1);

@@ -29,14 +29,17 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 // moe_sorting.  All outputs are device pointers; sorted_rows, mblk_cum and status_to_clear
 // (a status word the kernel resets to 0) may be null.  num_tokens_dev (optional) is a device
 // int that lowers the token count below T; id_div > 1 buckets by id / id_div (the rank
-// that owns the expert); inv_out[T*K] receives each pair's slot (-1 if dropped).
+// that owns the expert); inv_out[T*K] receives each pair's slot (-1 if dropped); scratch
+// (sort_scratch_words(E) ints, with mblk_cum) enables the multi-CTA path for >= 8192 pairs.
 cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight, int T, int K,
                                int E, int block_m, int64_t cap, int32_t* sorted_token_ids,
                                float* sorted_weights, int32_t* sorted_rows,
                                int32_t* sorted_expert_ids, int32_t* num_post_pad,
                                int32_t* mblk_cum, int32_t* status_to_clear, cudaStream_t stream,
                                const int32_t* num_tokens_dev = nullptr, int id_div = 1,
-                               int32_t* inv_out = nullptr);
+                               int32_t* inv_out = nullptr, int32_t* scratch = nullptr);
+// int32 words of `scratch` that lets launch_moe_sorting spread large inputs over several CTAs.
+constexpr size_t sort_scratch_words(int E) { return 2 * 64 * static_cast<size_t>(E); }
 
 // Gather rows of a bf16 matrix into sorted order, optionally quantising each row to e4m3.
 //   src [n_src, cols] bf16; row_ids [cap] (entry >= n_src means pad -> zero row) or null
