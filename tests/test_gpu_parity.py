@@ -414,3 +414,31 @@ def test_multi_cta_sorting_inside_fused_moe_is_bit_exact(T, K, E):
     assert (region("sorted_expert_ids", cap // 128) == ref["sorted_expert_ids"]).all()
     assert (region("mblk_cum", E + 1) == ref["mblk_cum"]).all()
     assert int(region("meta", 2)[0]) == int(ref["num_tokens_post_pad"][0])
+
+
+def test_host_pipeline_overlaps_copies_and_keeps_results():
+    """Host-resident batches through HostPipeline: every batch is copied in, computed and
+    copied back; different batches must not disturb each other although their copies overlap."""
+    d = O.make_inputs(128, 512, 256, 8, 2, 0, "softmax", seed=61)
+    args = args_for(d)
+    traits = traits_for(0)
+    args.workspace = torch.empty(M.fused_moe_workspace_size(traits, args), dtype=torch.uint8, device="cuda:0")
+    outs = [torch.empty_like(args.a) for _ in range(2)]
+
+    def step(x, ids, w, slot):
+        args.a, args.topk_ids, args.topk_weight, args.o = x, ids, w, outs[slot]
+        return M.fused_moe(traits, args)
+    pipe = api.HostPipeline(step, 128, 512, 2, torch.device("cuda:0"), depth=2)
+    n = 6
+    xs = [torch.from_numpy(O.f32_to_bf16(O.normal((128, 512), 70 + i, 1)).view(np.int16)).view(torch.bfloat16).pin_memory()
+          for i in range(n)]
+    ids_h = torch.from_numpy(d["topk_ids"]).pin_memory()
+    w_h = torch.from_numpy(d["topk_w"]).pin_memory()
+    res = [torch.empty(128, 512, dtype=torch.bfloat16).pin_memory() for _ in range(n)]
+    for i in range(n):
+        pipe.submit(xs[i], ids_h, w_h, res[i])
+    pipe.drain()
+    for i in range(n):
+        di = dict(d)
+        di["x"] = xs[i].view(torch.int16).numpy().view(np.uint16)
+        check(di, res[i].view(torch.int16).numpy().view(np.uint16), run_oracle(di))

@@ -12,7 +12,7 @@
 namespace fmoe {
 namespace {
 
-constexpr int kRowThreads = 256;
+constexpr int kRowThreads = 128;
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
   return __uint_as_float(bits16 << 16);
@@ -70,9 +70,9 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
   uint2* d = reinterpret_cast<uint2*>(dst) + static_cast<size_t>(slot) * nvec;
   if (kQuant == 1) {
     // per-row scale: the row is read once into registers (up to kMaxVec vectors per thread,
-    // i.e. rows of up to 16384 elements), reduced block-wide, then quantised from registers;
+    // i.e. rows of up to 16384 elements with 128 threads), reduced block-wide, then quantised from registers;
     // longer rows fall back to a second read.
-    constexpr int kMaxVec = 8;
+    constexpr int kMaxVec = 16;
     __shared__ float warp_max[kRowThreads / 32];
     __shared__ float row_scale;
     const bool in_regs = nvec <= kMaxVec * kRowThreads;
@@ -135,7 +135,7 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
   } else {
     // one scale per 128 columns = 16 vectors = a 16-lane group.  Up to kGroupVec vectors per
     // thread are loaded before any is processed so the loads overlap.
-    constexpr int kGroupVec = 4;
+    constexpr int kGroupVec = 8;
     const int ngroups = cols >> 7;
     for (int base = 0; base < nvec; base += kRowThreads * kGroupVec) {   // warp-uniform trip count
       uint4 held[kGroupVec];
