@@ -67,7 +67,8 @@ typedef struct fmoe_traits_c {
   int32_t quant;        /* fmoe_quant */
   int32_t weight_dtype; /* fmoe_dtype; must agree with quant */
   int32_t activation;   /* fmoe_activation */
-  int32_t gate_only;    /* 0: W1 holds gate rows then up rows (2I); 1 is rejected (unsupported) */
+  int32_t gate_only;    /* 0: W1 holds gate rows then up rows [E,2I,H], y = SiLU(gate)*up;
+                           1: W1 is [E,I,H] and y = SiLU(gate) (I a multiple of 256; not with block128) */
   int32_t block_m;      /* rows per sorted block; 128 */
   int32_t gemm_mode;    /* 0 = chosen per GEMM from the expected tile counts, 1 = single-CTA
                            kernel, 2 = CTA-pair kernel (cta_group::2) */
@@ -78,7 +79,7 @@ typedef struct fmoe_traits_c {
 /* Run-time arguments (ck_tile's fused_moe_args role).  All pointers are device pointers. */
 typedef struct fmoe_args_c {
   const void* x;            /* [T, H] bf16 activations */
-  const void* w1;           /* [E, 2I, H] gate rows then up rows; bf16 or e4m3 */
+  const void* w1;           /* [E, 2I, H] gate rows then up rows ([E, I, H] when gate_only); bf16 or e4m3 */
   const void* w2;           /* [E, H, I]; bf16 or e4m3 */
   const float* w1_scale;    /* quant 1: [E, 2I]; quant 2: [E, 2I/128, H/128]; else NULL */
   const float* w2_scale;    /* quant 1: [E, H];  quant 2: [E, H/128, I/128]; else NULL */

@@ -289,14 +289,14 @@ enum { ORC_Q_NONE = 0, ORC_Q_TOKEN_CHANNEL = 1, ORC_Q_BLOCK128 = 2 };
  *         for the fp8 modes); xs: activation scale(s) for the fp8 modes.
  *   w1/w2 point at the expert's weights (bf16 or e4m3 bytes), s1/s2 at its scales.
  * o[H] receives the un-weighted down-projection in f32. */
-static void expert_forward(int quant, int H, int I, const float* xin, const float* xs,
+static void expert_forward(int quant, int gate_only, int H, int I, const float* xin, const float* xs,
                            const void* w1, const void* w2, const float* s1, const float* s2,
                            float* wrow, float* y, float* yq, float* ys, float* o) {
   const int HB = H / 128, IB = I / 128;
-  /* gemm1 + SiLU*up */
+  /* gemm1 + SiLU*up (gate_only: W1 has I rows and y = SiLU(gate)) */
   for (int n = 0; n < I; ++n) {
-    float gu[2];
-    for (int half = 0; half < 2; ++half) {
+    float gu[2] = {0.0f, 1.0f};
+    for (int half = 0; half < (gate_only ? 1 : 2); ++half) {
       int64_t row = (int64_t)half * I + n;
       if (quant == ORC_Q_NONE) {
         const uint16_t* wr = (const uint16_t*)w1 + row * H;
@@ -316,7 +316,7 @@ static void expert_forward(int quant, int H, int I, const float* xin, const floa
         }
       }
     }
-    y[n] = silu_f32(gu[0]) * gu[1];
+    y[n] = gate_only ? silu_f32(gu[0]) : silu_f32(gu[0]) * gu[1];
   }
   /* intermediate rounding point: y is held as bf16 in every mode */
   for (int n = 0; n < I; ++n) y[n] = bf16_to_f32(f32_to_bf16(y[n]));
@@ -368,12 +368,30 @@ static void expert_forward(int quant, int H, int I, const float* xin, const floa
  *   x [T,H] bf16; topk_ids/topk_w [T,K]; sel = n_sel token indices to evaluate (NULL = all
  *   T tokens in order); out [n_sel or T, H] bf16.
  * Expert ids outside [0,E) contribute nothing. */
+ORC_API int orc_fused_moe_ex(int T, int H, int I, int E, int K, int quant, int gate_only,
+                             const uint16_t* x, const void* w1, const void* w2,
+                             const float* w1_scale, const float* w2_scale,
+                             const int32_t* topk_ids, const float* topk_w,
+                             const int32_t* sel, int n_sel, uint16_t* out, int n_threads);
+
 ORC_API int orc_fused_moe(int T, int H, int I, int E, int K, int quant,
                           const uint16_t* x, const void* w1, const void* w2,
                           const float* w1_scale, const float* w2_scale,
                           const int32_t* topk_ids, const float* topk_w,
                           const int32_t* sel, int n_sel, uint16_t* out, int n_threads) {
+  return orc_fused_moe_ex(T, H, I, E, K, quant, 0, x, w1, w2, w1_scale, w2_scale, topk_ids, topk_w, sel, n_sel,
+                          out, n_threads);
+}
+
+/* gate_only = 1: W1 is [E, I, H] (no up projection) and y = SiLU(x . W1^T); weight scales of
+ * W1 then have I rows per expert ([E, I] or [E, I/128, H/128]). */
+ORC_API int orc_fused_moe_ex(int T, int H, int I, int E, int K, int quant, int gate_only,
+                             const uint16_t* x, const void* w1, const void* w2,
+                             const float* w1_scale, const float* w2_scale,
+                             const int32_t* topk_ids, const float* topk_w,
+                             const int32_t* sel, int n_sel, uint16_t* out, int n_threads) {
   build_lut();
+  const int w1_rows = gate_only ? I : 2 * I;
   if (quant < 0 || quant > 2) return -1;
   if (quant == ORC_Q_BLOCK128 && (H % 128 || I % 128)) return -2;
   int n = sel ? n_sel : T;
@@ -408,18 +426,18 @@ ORC_API int orc_fused_moe(int T, int H, int I, int E, int K, int quant,
         int e = topk_ids[(int64_t)t * K + k];
         if (e < 0 || e >= E) continue;
         float wk = topk_w[(int64_t)t * K + k];
-        const uint8_t* w1e = (const uint8_t*)w1 + (size_t)e * 2 * I * H * wbytes;
+        const uint8_t* w1e = (const uint8_t*)w1 + (size_t)e * w1_rows * H * wbytes;
         const uint8_t* w2e = (const uint8_t*)w2 + (size_t)e * H * I * wbytes;
         const float* s1 = NULL;
         const float* s2 = NULL;
         if (quant == ORC_Q_TOKEN_CHANNEL) {
-          s1 = w1_scale + (size_t)e * 2 * I;
+          s1 = w1_scale + (size_t)e * w1_rows;
           s2 = w2_scale + (size_t)e * H;
         } else if (quant == ORC_Q_BLOCK128) {
-          s1 = w1_scale + (size_t)e * (2 * I / 128) * (H / 128);
+          s1 = w1_scale + (size_t)e * (w1_rows / 128) * (H / 128);
           s2 = w2_scale + (size_t)e * (H / 128) * (I / 128);
         }
-        expert_forward(quant, H, I, xin, xs, w1e, w2e, s1, s2, wrow, y, yq, ys, o);
+        expert_forward(quant, gate_only, H, I, xin, xs, w1e, w2e, s1, s2, wrow, y, yq, ys, o);
         for (int h = 0; h < H; ++h) acc[h] += wk * o[h];
       }
       for (int h = 0; h < H; ++h) out[(int64_t)i * H + h] = f32_to_bf16(acc[h]);

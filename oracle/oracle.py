@@ -188,7 +188,7 @@ def moe_sorting(topk_ids: np.ndarray, topk_w: np.ndarray, E: int, block_m: int):
 
 
 def fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None, w2_scale=None,
-              sel=None, n_threads: int = 0) -> np.ndarray:
+              sel=None, n_threads: int = 0, gate_only: bool = False) -> np.ndarray:
     """x_bf16 [T,H] uint16; w1 [E,2I,H], w2 [E,H,I] (uint16 bf16 bits or uint8 e4m3 bytes).
     Returns out [n_sel or T, H] as bf16 bits (uint16)."""
     x_bf16 = np.ascontiguousarray(x_bf16, dtype=np.uint16)
@@ -199,8 +199,8 @@ def fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None,
     topk_w = np.ascontiguousarray(topk_w, dtype=np.float32)
     T, H = x_bf16.shape
     E, I2, H2 = w1.shape
-    assert H2 == H and w2.shape == (E, H, I2 // 2)
-    I = I2 // 2
+    I = I2 if gate_only else I2 // 2
+    assert H2 == H and w2.shape == (E, H, I)
     K = topk_ids.shape[1]
     if w1_scale is not None:
         w1_scale = np.ascontiguousarray(w1_scale, dtype=np.float32)
@@ -209,9 +209,9 @@ def fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None,
         sel = np.ascontiguousarray(sel, dtype=np.int32)
     n = T if sel is None else len(sel)
     out = np.empty((n, H), dtype=np.uint16)
-    rc = lib().orc_fused_moe(T, H, I, E, K, quant, _p(x_bf16), _p(w1), _p(w2), _p(w1_scale),
-                             _p(w2_scale), _p(topk_ids), _p(topk_w), _p(sel),
-                             0 if sel is None else len(sel), _p(out), n_threads)
+    rc = lib().orc_fused_moe_ex(T, H, I, E, K, quant, 1 if gate_only else 0, _p(x_bf16), _p(w1), _p(w2),
+                                _p(w1_scale), _p(w2_scale), _p(topk_ids), _p(topk_w), _p(sel),
+                                0 if sel is None else len(sel), _p(out), n_threads)
     if rc != 0:
         raise ValueError(f"orc_fused_moe failed: {rc}")
     return out
@@ -300,12 +300,13 @@ def np_moe_sorting(topk_ids: np.ndarray, topk_w: np.ndarray, E: int, block_m: in
                 num_tokens_post_pad=np.array([pos], np.int32), mblk_cum=cum)
 
 
-def np_fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None, w2_scale=None):
+def np_fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None, w2_scale=None,
+                 gate_only: bool = False):
     """Per-expert batched restatement (float32 matmuls).  Same contract as orc_fused_moe;
     summation order inside the dot products differs, so agreement is to f32 round-off."""
     T, H = x_bf16.shape
     E, I2, _ = w1.shape
-    I = I2 // 2
+    I = I2 if gate_only else I2 // 2
     K = topk_ids.shape[1]
     x = bf16_to_f32(x_bf16)
     tab = np_e4m3_table()
@@ -322,12 +323,13 @@ def np_fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=No
             gu = (tab[q] @ tab[w1[e]].T) * s * w1_scale[e][None, :]
         else:
             q, s = np_quant(xe, 128)
-            gu = np.zeros((len(t_idx), 2 * I), np.float32)
+            gu = np.zeros((len(t_idx), I2), np.float32)
             wf = tab[w1[e]]
             for kb in range(H // 128):
                 part = tab[q[:, kb * 128:(kb + 1) * 128]] @ wf[:, kb * 128:(kb + 1) * 128].T
                 gu += part * s[:, kb:kb + 1] * np.repeat(w1_scale[e][:, kb], 128)[None, :]
-        g, u = gu[:, :I], gu[:, I:]
+        g = gu[:, :I]
+        u = np.float32(1) if gate_only else gu[:, I:]
         y = (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u
         y = bf16_to_f32(np_f32_to_bf16(y.astype(np.float32)))   # y is held as bf16 in every mode
         if quant == QUANT_NONE:
@@ -361,10 +363,11 @@ CONFIGS = {
 }
 
 
-def make_inputs(T, H, I, E, K, quant=QUANT_NONE, routing="softmax", seed=0):
+def make_inputs(T, H, I, E, K, quant=QUANT_NONE, routing="softmax", seed=0, gate_only=False):
     """Seeded synthetic inputs: activations N(0,1), weights N(0,0.02), logits N(0,1)."""
     x = f32_to_bf16(normal((T, H), seed, 1))
-    w1f = normal((E, 2 * I, H), seed, 2, 0.02)
+    R1 = I if gate_only else 2 * I
+    w1f = normal((E, R1, H), seed, 2, 0.02)
     w2f = normal((E, H, I), seed, 3, 0.02)
     logits = normal((T, E), seed, 4)
     ids, w = route(logits, K, routing)
@@ -372,13 +375,13 @@ def make_inputs(T, H, I, E, K, quant=QUANT_NONE, routing="softmax", seed=0):
     if quant == QUANT_NONE:
         d["w1"], d["w2"] = f32_to_bf16(w1f), f32_to_bf16(w2f)
     elif quant == QUANT_TOKEN_CHANNEL:
-        q1, s1 = quant_rows_e4m3(w1f.reshape(E * 2 * I, H))
+        q1, s1 = quant_rows_e4m3(w1f.reshape(E * R1, H))
         q2, s2 = quant_rows_e4m3(w2f.reshape(E * H, I))
-        d["w1"], d["w1_scale"] = q1.reshape(E, 2 * I, H), s1.reshape(E, 2 * I)
+        d["w1"], d["w1_scale"] = q1.reshape(E, R1, H), s1.reshape(E, R1)
         d["w2"], d["w2_scale"] = q2.reshape(E, H, I), s2.reshape(E, H)
     else:
-        q1, s1 = quant_blocks_e4m3(w1f.reshape(E * 2 * I, H))
+        q1, s1 = quant_blocks_e4m3(w1f.reshape(E * R1, H))
         q2, s2 = quant_blocks_e4m3(w2f.reshape(E * H, I))
-        d["w1"], d["w1_scale"] = q1.reshape(E, 2 * I, H), s1.reshape(E, 2 * I // 128, H // 128)
+        d["w1"], d["w1_scale"] = q1.reshape(E, R1, H), s1.reshape(E, R1 // 128, H // 128)
         d["w2"], d["w2_scale"] = q2.reshape(E, H, I), s2.reshape(E, H // 128, I // 128)
     return d

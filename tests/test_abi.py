@@ -98,6 +98,19 @@ def test_argument_errors_are_reported_before_any_launch(lib):
     a.H = 512; a.K = 9
     assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -1
     assert lib.fmoe_get_workspace_size(None, ctypes.byref(a), ctypes.byref(n)) == -1
+    # gate-only: intermediate size must tile by 256, and block128 scales are not built for it
+    a.K = 2
+    t.gate_only = 1
+    assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == 0
+    a.I = 384
+    assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -2
+    a.I = 1024
+    t.quant, t.weight_dtype = 2, 1
+    assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -2
+    t.quant, t.weight_dtype, t.gate_only = 0, 0, 0
+    t.weight_layout = 7
+    assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -1
+    t.weight_layout = 0
     assert lib.fmoe_sort(None, None, 1, 1, 1, 128, None, None, None, None, None) == -1
 
 

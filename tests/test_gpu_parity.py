@@ -442,3 +442,19 @@ def test_host_pipeline_overlaps_copies_and_keeps_results():
         di = dict(d)
         di["x"] = xs[i].view(torch.int16).numpy().view(np.uint16)
         check(di, res[i].view(torch.int16).numpy().view(np.uint16), run_oracle(di))
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+@pytest.mark.parametrize("T,H,I,E,K", [(128, 512, 512, 8, 2), (16, 256, 256, 4, 2), (700, 256, 768, 3, 1)])
+def test_gate_only_variant(quant, T, H, I, E, K):
+    """W1 = [E, I, H] without an up projection: y = SiLU(x . W1^T)."""
+    d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=71, gate_only=True)
+    tr = traits_for(quant)
+    tr.gate_only = 1
+    args = args_for(d)
+    out = M.fused_moe(tr, args)
+    torch.cuda.synchronize()
+    assert api.check_status(args.workspace) == 0
+    ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
+                      gate_only=True)
+    check(d, out_bits(out), ref)

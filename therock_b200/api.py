@@ -155,7 +155,7 @@ class FusedMoeArgs:
     num_tokens_dev: Optional[torch.Tensor] = None  # int32[1] on the device: process only that many tokens
     expected_tokens: int = 0                   # typical value of num_tokens_dev (kernel choice hint)
 
-    def to_c(self) -> _Args:
+    def to_c(self, gate_only: bool = False) -> _Args:
         for name in ("a", "g", "d", "topk_ids", "topk_weight"):
             t = getattr(self, name)
             if not (t.is_cuda and t.is_contiguous()):
@@ -166,8 +166,9 @@ class FusedMoeArgs:
             raise FmoeError(-1, "topk_ids must be int32 and topk_weight float32")
         T, H = self.a.shape
         E, I2, H2 = self.g.shape
-        if H2 != H or tuple(self.d.shape) != (E, H, I2 // 2) or I2 % 2:
-            raise FmoeError(-1, "weight shapes do not match [E,2I,H] / [E,H,I]")
+        I = I2 if gate_only else I2 // 2
+        if H2 != H or tuple(self.d.shape) != (E, H, I) or (not gate_only and I2 % 2):
+            raise FmoeError(-1, "weight shapes do not match [E,2I,H] ([E,I,H] when gate_only) / [E,H,I]")
         if self.topk_ids.shape[0] != T or self.topk_weight.shape != self.topk_ids.shape:
             raise FmoeError(-1, "topk tensors must be [T, K]")
         c = _Args()
@@ -179,7 +180,7 @@ class FusedMoeArgs:
         if self.workspace is not None:
             c.workspace = self.workspace.data_ptr()
             c.workspace_bytes = self.workspace.numel() * self.workspace.element_size()
-        c.T, c.H, c.I, c.E, c.K = T, H, I2 // 2, E, self.topk_ids.shape[1]
+        c.T, c.H, c.I, c.E, c.K = T, H, I, E, self.topk_ids.shape[1]
         c.num_tokens_dev = self.num_tokens_dev.data_ptr() if self.num_tokens_dev is not None else None
         c.expected_tokens = int(self.expected_tokens)
         return c
@@ -195,13 +196,13 @@ def launches_per_run(traits: FusedMoeTraits) -> int:
 
 
 def workspace_layout(traits: FusedMoeTraits, args: FusedMoeArgs) -> dict:
-    t, a, l = traits.to_c(), args.to_c(), _Layout()
+    t, a, l = traits.to_c(), args.to_c(bool(traits.gate_only)), _Layout()
     _check(lib().fmoe_get_workspace_layout(ctypes.byref(t), ctypes.byref(a), ctypes.byref(l)))
     return {n: int(getattr(l, n)) for n, _ in _Layout._fields_}
 
 
 def fused_moe_workspace_size(traits: FusedMoeTraits, args: FusedMoeArgs) -> int:
-    t, a, n = traits.to_c(), args.to_c(), ctypes.c_uint64(0)
+    t, a, n = traits.to_c(), args.to_c(bool(traits.gate_only)), ctypes.c_uint64(0)
     _check(lib().fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)))
     return int(n.value)
 
@@ -222,7 +223,7 @@ def fused_moe(traits: FusedMoeTraits, args: FusedMoeArgs, stream=None, time_kern
     if args.workspace is None:
         args.workspace = torch.empty(fused_moe_workspace_size(traits, args), dtype=torch.uint8,
                                      device=args.a.device)
-    t, a = traits.to_c(), args.to_c()
+    t, a = traits.to_c(), args.to_c(bool(traits.gate_only))
     ms = ctypes.c_float(0.0)
     _check(lib().fmoe_run(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream),
                           ctypes.byref(ms) if time_kernel else None))
@@ -265,7 +266,7 @@ class StageProfile:
         _check(lib().fmoe_profile_create(max_runs, ctypes.byref(self._h)))
 
     def run(self, traits: FusedMoeTraits, args: FusedMoeArgs, stream=None):
-        t, a = traits.to_c(), args.to_c()
+        t, a = traits.to_c(), args.to_c(bool(traits.gate_only))
         _check(lib().fmoe_run_profiled(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream), self._h))
         return args.o
 
@@ -323,7 +324,7 @@ def fused_moe_static_ws(traits: FusedMoeTraits, args: FusedMoeArgs, stream=None)
     one device share that array: keep them on one stream."""
     if args.o is None:
         raise FmoeError(-1, "the output tensor must be provided (this entry point allocates nothing)")
-    t, a = traits.to_c(), args.to_c()
+    t, a = traits.to_c(), args.to_c(bool(traits.gate_only))
     _check(lib().fmoe_run_static_ws(ctypes.byref(t), ctypes.byref(a), _stream_ptr(stream)))
     return args.o
 

@@ -39,7 +39,9 @@ int validate_traits(const fmoe_traits_c* t) {
   if (t->weight_dtype != want)
     return fail(FMOE_ERR_INVALID_ARG, "weight_dtype %d does not match quant mode %d", t->weight_dtype, t->quant);
   if (t->activation != FMOE_ACT_SILU) return fail(FMOE_ERR_UNSUPPORTED, "only SiLU activation is built");
-  if (t->gate_only != 0) return fail(FMOE_ERR_UNSUPPORTED, "gate_only variant is not built");
+  if (t->gate_only != 0 && t->gate_only != 1) return fail(FMOE_ERR_INVALID_ARG, "gate_only must be 0 or 1");
+  if (t->gate_only && t->quant == FMOE_QUANT_BLOCK128)
+    return fail(FMOE_ERR_UNSUPPORTED, "gate_only with block128 scales is not built");
   if (t->block_m != fmoe::kBlockM) return fail(FMOE_ERR_UNSUPPORTED, "block_m must be %d", fmoe::kBlockM);
   if (t->gemm_mode < 0 || t->gemm_mode > 2) return fail(FMOE_ERR_INVALID_ARG, "gemm_mode must be 0, 1 or 2");
   if (t->weight_layout != FMOE_WEIGHTS_ROW_MAJOR && t->weight_layout != FMOE_WEIGHTS_TILED128)
@@ -54,6 +56,8 @@ int validate_dims(const fmoe_traits_c* t, const fmoe_args_c* a) {
   if (a->K > a->E) return fail(FMOE_ERR_INVALID_ARG, "topk %d exceeds experts %d", a->K, a->E);
   if (a->E > 1024) return fail(FMOE_ERR_UNSUPPORTED, "at most 1024 experts");
   if (a->I % fmoe::kSlabRows) return fail(FMOE_ERR_UNSUPPORTED, "intermediate size must be a multiple of %d", fmoe::kSlabRows);
+  if (t->gate_only && a->I % fmoe::kTileN)
+    return fail(FMOE_ERR_UNSUPPORTED, "gate_only needs an intermediate size that is a multiple of %d", fmoe::kTileN);
   if (a->H % fmoe::kTileN) return fail(FMOE_ERR_UNSUPPORTED, "hidden size must be a multiple of %d", fmoe::kTileN);
   if (static_cast<int64_t>(a->T) * a->K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
   if (t->weight_layout == FMOE_WEIGHTS_TILED128) {
@@ -275,11 +279,19 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     return (waves_pair * 95 < waves_single * 100) ? 2 : 1;
   };
   // gemm1: [cap, H] x W1[E, 2I, H]^T -> SiLU(gate) * up -> y [cap, I]
-  g.mode = pick_mode(a.I / fmoe::kSlabRows);
-  g.epilogue = fmoe::kEpiSiluMul;
+  if (traits->gate_only) {
+    // W1 is [E, I, H]: a tile is 256 consecutive gate rows, y = SiLU(gate)
+    g.mode = pick_mode(a.I / fmoe::kTileN);
+    g.epilogue = fmoe::kEpiSilu;
+    g.b_rows_per_expert = a.I;
+    g.n_blocks = a.I / fmoe::kTileN; g.n_stride = fmoe::kTileN; g.second_slab_offset = fmoe::kSlabRows;
+  } else {
+    g.mode = pick_mode(a.I / fmoe::kSlabRows);
+    g.epilogue = fmoe::kEpiSiluMul;
+    g.b_rows_per_expert = 2 * a.I;
+    g.n_blocks = a.I / fmoe::kSlabRows; g.n_stride = fmoe::kSlabRows; g.second_slab_offset = a.I;
+  }
   g.a = a_sorted; g.a_rows = plan.cap; g.b = a.w1; g.k_elems = a.H;
-  g.b_rows_per_expert = 2 * a.I;
-  g.n_blocks = a.I / fmoe::kSlabRows; g.n_stride = fmoe::kSlabRows; g.second_slab_offset = a.I;
   g.a_scale = a_scale; g.b_scale = fp8 ? a.w1_scale : nullptr;
   g.out = y; g.ld_out = a.I;
   if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)

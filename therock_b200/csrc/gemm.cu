@@ -190,6 +190,10 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
                       kBlockSmemBytes, stream, ta, tb, bp);
   }
   const bool pair = g.mode == 2;
+#define FMOE_DISPATCH_EPI(LAUNCH, FP8, ...)                                                        \
+  (g.epilogue == kEpiSiluMul ? LAUNCH<FP8, kEpiSiluMul __VA_ARGS__>(ta, tb, p, grid, stream)       \
+   : g.epilogue == kEpiSilu  ? LAUNCH<FP8, kEpiSilu __VA_ARGS__>(ta, tb, p, grid, stream)          \
+                             : LAUNCH<FP8, kEpiScaledSlots __VA_ARGS__>(ta, tb, p, grid, stream))
   if (pair) {
     if (!g.idesc_override) p.idesc = ptx::make_idesc(g.fp8 ? 0u : 1u, 2 * kBlockM, kTileN);
     // upper bound on pair tiles: every expert may add one half-empty pair
@@ -197,30 +201,17 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     const long long max_tiles = max_pairs * g.n_blocks;
     const int clusters = sm_count() / 2;
     const int grid = 2 * static_cast<int>(max_tiles < clusters ? (max_tiles > 0 ? max_tiles : 1) : clusters);
-    if (g.fp8) {
-      return g.epilogue == kEpiSiluMul ? launch_pair_variant<true, kEpiSiluMul>(ta, tb, p, grid, stream)
-                                       : launch_pair_variant<true, kEpiScaledSlots>(ta, tb, p, grid, stream);
-    }
-    return g.epilogue == kEpiSiluMul ? launch_pair_variant<false, kEpiSiluMul>(ta, tb, p, grid, stream)
-                                     : launch_pair_variant<false, kEpiScaledSlots>(ta, tb, p, grid, stream);
+    return g.fp8 ? FMOE_DISPATCH_EPI(launch_pair_variant, true) : FMOE_DISPATCH_EPI(launch_pair_variant, false);
   }
   const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
   const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
-  if (few_rows) {
-    if (g.fp8)
-      return g.epilogue == kEpiSiluMul
-                 ? launch_variant<true, kEpiSiluMul, kDecodeARows>(ta, tb, p, grid, stream)
-                 : launch_variant<true, kEpiScaledSlots, kDecodeARows>(ta, tb, p, grid, stream);
-    return g.epilogue == kEpiSiluMul
-               ? launch_variant<false, kEpiSiluMul, kDecodeARows>(ta, tb, p, grid, stream)
-               : launch_variant<false, kEpiScaledSlots, kDecodeARows>(ta, tb, p, grid, stream);
-  }
-  if (g.fp8) {
-    return g.epilogue == kEpiSiluMul ? launch_variant<true, kEpiSiluMul>(ta, tb, p, grid, stream)
-                                     : launch_variant<true, kEpiScaledSlots>(ta, tb, p, grid, stream);
-  }
-  return g.epilogue == kEpiSiluMul ? launch_variant<false, kEpiSiluMul>(ta, tb, p, grid, stream)
-                                   : launch_variant<false, kEpiScaledSlots>(ta, tb, p, grid, stream);
+#define FMOE_COMMA_DECODE , kDecodeARows
+  if (few_rows)
+    return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, FMOE_COMMA_DECODE)
+                 : FMOE_DISPATCH_EPI(launch_variant, false, FMOE_COMMA_DECODE);
+  return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true) : FMOE_DISPATCH_EPI(launch_variant, false);
+#undef FMOE_COMMA_DECODE
+#undef FMOE_DISPATCH_EPI
 }
 
 }  // namespace fmoe

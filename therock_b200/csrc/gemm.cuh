@@ -34,7 +34,7 @@ constexpr int kSmemMisc = 8192;          // barriers + per-expert block table (<
 constexpr int kEpiStageReserve = 4 * 32 * 36 * 4;   // per-warp staging of the epilogue (see epilogue_tile)
 constexpr int kGemmSmemBytes = kStages * kStageBytes + kSmemMisc + kEpiStageReserve + 1024;  // +1024 alignment slack
 
-enum : int { kEpiSiluMul = 1, kEpiScaledSlots = 2 };
+enum : int { kEpiSiluMul = 1, kEpiScaledSlots = 2, kEpiSilu = 3 };
 
 // Device status codes written to the workspace status word.
 enum : int { kStatusOk = 0, kStatusGemmTimeout = 0x100 };
@@ -107,6 +107,7 @@ constexpr int kEpiStageBytes = 4 * kEpiStageBytesPerWarp;             // four ep
 // Fused epilogue of one 128 x 256 accumulator held in TMEM (this thread owns one row).
 //   kEpiSiluMul    : columns 0..127 gate, 128..255 up -> bf16 y[slot, n_blk*128 ..] = SiLU(g)*u
 //   kEpiScaledSlots: 256 output channels -> f32 slots[row, n_blk*256 ..] = w * acc
+//   kEpiSilu       : gate-only first GEMM, 256 channels -> bf16 y[slot, n_blk*256 ..] = SiLU(acc)
 // fp8: acc is first multiplied by the row's activation scale and the channel's weight scale.
 // A thread computes 32 consecutive columns of its own row per step.  Storing them directly
 // would make every warp store touch 32 rows with 16 bytes each; instead the warp transposes
@@ -163,6 +164,48 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
         srow[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
       __syncwarp();
       // 4 lanes per row, 8 rows per store instruction: 64 contiguous bytes per row
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int r = it * 8 + (lane >> 2);
+        const int seg = lane & 3;
+        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
+        const int live_r = __shfl_sync(0xffffffffu, row, r);
+        if (live_r >= 0)
+          *reinterpret_cast<uint4*>(ybase + static_cast<size_t>(slot0 + r) * p.ld_out + c * 32 + seg * 8) = val;
+      }
+    }
+  } else if (kEpi == kEpiSilu) {
+    __nv_bfloat16* ybase = reinterpret_cast<__nv_bfloat16*>(p.out) + n_blk * kTileN;
+    const int slot0 = slot - lane;
+    uint32_t v[2][32];
+    ptx::tmem_ld_32x32(t_row, v[0]);
+#pragma unroll
+    for (int c = 0; c < kTileN / 32; ++c) {
+      const int cur = c & 1;
+      ptx::tmem_ld_wait();
+      if (c + 1 < kTileN / 32) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, v[cur ^ 1]);
+      uint32_t packed[16];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float f[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) f[j] = __uint_as_float(v[cur][4 * q + j]);
+        if (p.b_scale != nullptr) {
+          const float4 sc = __ldg(reinterpret_cast<const float4*>(bs0 + c * 32 + 4 * q));
+          f[0] = (f[0] * a_s) * sc.x; f[1] = (f[1] * a_s) * sc.y;
+          f[2] = (f[2] * a_s) * sc.z; f[3] = (f[3] * a_s) * sc.w;
+        }
+        __nv_bfloat162 v0 = __floats2bfloat162_rn(silu(f[0]), silu(f[1]));
+        __nv_bfloat162 v1 = __floats2bfloat162_rn(silu(f[2]), silu(f[3]));
+        packed[2 * q] = *reinterpret_cast<uint32_t*>(&v0);
+        packed[2 * q + 1] = *reinterpret_cast<uint32_t*>(&v1);
+      }
+      __syncwarp();
+      uint4* srow = reinterpret_cast<uint4*>(stage + lane * 20);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        srow[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      __syncwarp();
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int r = it * 8 + (lane >> 2);
