@@ -71,9 +71,9 @@ def route_on_device(logits, K, mode):
     w = (w / w.sum(dim=-1, keepdim=True)).float().contiguous()
     return ids.to(torch.int32).contiguous(), w
 
-# DRAM bytes (read + write) of one gate+up GEMM launch on the benchmark workload, from the
-# ncu capture summarised in profiles/grouped_gemm_bf16_mixtral_prefill.md (None where no
-# capture of that configuration has been taken).
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one gate+up GEMM launch on the
+# benchmark workload, from an ncu capture of this same command (None where no capture of
+# that configuration has been taken).
 GEMM1_DRAM_TRAFFIC_BYTES = {"C1": 2199174144, "C2": None, "C3": None}
 
 

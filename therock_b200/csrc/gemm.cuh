@@ -1,4 +1,5 @@
-// Expert-grouped GEMM for the fused-MoE operator on sm_100a.
+// Expert-grouped GEMMs for the fused-MoE operator on sm_100a: the single-CTA kernel described
+// here, a CTA-pair variant (cta_group::2) and a block-scaled fp8 variant further down.
 //
 // One persistent CTA per SM walks a list of (expert, n-block, m-block) tiles.  Every tile
 // is D[128 x 256] = A[128 x K] * B[256 x K]^T with
