@@ -60,7 +60,9 @@ struct GemmParams {
   int b_tiled_kb;               // 0: B is row-major; > 0: B is stored as contiguous 128 x 128-byte
                                 // tiles and this is the number of 128-byte K blocks per row
   uint32_t debug_flags;         // diagnostics only (results are invalid when set): bit 0 = the
-                                // epilogue skips its work, bit 1 = no MMA is issued
+                                // epilogue skips its work (block-scaled kernel: no promotion
+                                // FMAs), bit 1 = no MMA is issued; block-scaled kernel only:
+                                // bit 2 = no TMEM loads, bit 3 = scalar FMAs, bit 4 = no final stores
 };
 
 struct TileCoord {
@@ -674,8 +676,11 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
 // [128h, 128h+128), one weight-scale block.
 constexpr int kBlockGemmThreads = 384;   // warpgroup 0: producer + MMA (+2 idle warps); warpgroups 1, 2: epilogue
 constexpr int kBlockStages = 4;
+// setmaxnreg only redistributes what the CTA was given at launch (384 threads x 168 registers):
+// the per-role counts must add up to no more than that, or setmaxnreg.inc never returns.
 constexpr int kBlockThinRegs = 40;       // registers per thread kept by warpgroup 0
 constexpr int kBlockFatRegs = 216;       // registers per thread taken by the epilogue warpgroups
+static_assert(128 * kBlockThinRegs + 256 * kBlockFatRegs <= kBlockGemmThreads * 168, "register budget");
 constexpr int kBlockSmemBytes = kBlockStages * kStageBytes + kSmemMisc + 8 * 32 * 20 * 4 + 1024;
 
 struct BlockGemmParams {
@@ -786,7 +791,8 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
           for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
             const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
-            ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, kk ? 1u : 0u);   // fresh partial per stage
+            if (!(p.debug_flags & 2u))
+              ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, kk ? 1u : 0u);   // fresh partial per stage
           }
           ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
           ptx::umma_commit(ptx::smem_u32(&part_full_bar[buf]));
@@ -884,6 +890,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
       }
       if (!ok) break;
+      if (p.debug_flags & 16u) continue;
       // Final stores go through a per-warp transpose (32 rows x 16 words at a time) so each
       // store instruction writes 64-byte row segments instead of 16 bytes to 32 different rows.
       uint32_t* stage = reinterpret_cast<uint32_t*>(misc + kSmemMisc) + (warp - 4) * (32 * 20);
