@@ -174,8 +174,18 @@ def make_host_inputs(c, seed=0):
                 topk_ids=ids, topk_w=w, quant=quant)
 
 
+def host_cores() -> int:
+    """Host threads the CPU arm uses: the cores this process may run on (torchrun exports
+    OMP_NUM_THREADS=1, which would otherwise pin the OpenMP runtime to one thread)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_time_tokens(d, sel, threads=0):
     from oracle import oracle as O
+    threads = threads or host_cores()
     t0 = time.perf_counter()
     O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], d["quant"], d["w1_scale"], d["w2_scale"],
                 sel=sel, n_threads=threads)
@@ -185,7 +195,7 @@ def cpu_time_tokens(d, sel, threads=0):
 def cpu_sample_size(d, c, budget_s: float, n_calls: int) -> int:
     """Tokens per timed call so that n_calls calls take about budget_s."""
     from oracle import oracle as O
-    probe = np.arange(min(O.max_threads(), c["T"]), dtype=np.int32)
+    probe = np.arange(min(host_cores(), c["T"]), dtype=np.int32)
     t = max(cpu_time_tokens(d, probe), 1e-4)
     per_token = t / len(probe)
     n = int(budget_s / max(n_calls, 1) / per_token)
@@ -201,7 +211,7 @@ def run_reference(a, c):
     if rank != 0:
         return
     d = make_host_inputs(c)
-    cores = O.max_threads()
+    cores = host_cores()
     n = cpu_sample_size(d, c, budget_s=90.0, n_calls=a.steps + a.warmup)
     rng = np.random.default_rng(0)
     for _ in range(a.warmup):
@@ -549,7 +559,7 @@ def run_gpu(a, c):
         sel = np.random.default_rng(0).choice(c["T"], n, replace=False).astype(np.int32)
         t = cpu_time_tokens(hd, sel)
         line["cpu_baseline"] = {"value": 6.0 * n * c["K"] * c["H"] * c["I"] / t / 1e12, "unit": "TFLOP/s",
-                                "cores": O.max_threads(), "kind": "port",
+                                "cores": host_cores(), "kind": "port",
                                 "sample": f"{n} of {c['T']} tokens, full weights, one pass ({t:.1f} s)"}
         # parity spot check of the benchmarked run against the same oracle call
         ref = O.fused_moe(hd["x"], hd["w1"], hd["w2"], hd["topk_ids"], hd["topk_w"], c["quant"], hd["w1_scale"],
