@@ -205,11 +205,11 @@ def cpu_sample_size(d, c, budget_s: float, n_calls: int) -> int:
 
 def run_reference(a, c):
     """CPU implementation of the path on the host cores, a bounded token sample per step."""
-    from oracle import oracle as O
-    O.build()
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from oracle import oracle as O
+    O.build()
     d = make_host_inputs(c)
     cores = host_cores()
     n = cpu_sample_size(d, c, budget_s=90.0, n_calls=a.steps + a.warmup)
