@@ -581,6 +581,8 @@ def main():
     ap.add_argument("--config", default="C1", choices=sorted(CONFIGS))
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the token count (small cases for profiler captures)")
+    ap.add_argument("--experts", type=int, default=0,
+                    help="override the expert count (shrinks the weights for profiler captures)")
     ap.add_argument("--weight-layout", choices=["row_major", "tiled128"], default="row_major",
                     help="tiled128: weights pre-shuffled so every 128x128-byte operand tile is contiguous")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
@@ -592,6 +594,9 @@ def main():
     if a.tokens > 0:
         c["T"] = a.tokens
         c["label"] += f"-tokens{a.tokens}"
+    if a.experts > 0:
+        c["E"] = a.experts
+        c["label"] += f"-experts{a.experts}"
     if a.impl == "reference":
         run_reference(a, c)
     else:
