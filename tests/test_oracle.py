@@ -137,6 +137,20 @@ def test_fused_moe_token_subset_and_invalid_ids():
     np.testing.assert_allclose(O.bf16_to_f32(full), O.bf16_to_f32(ref), rtol=2e-2, atol=2e-3)
 
 
+@pytest.mark.parametrize("quant", [0, 1])
+def test_gate_only_oracle_matches_numpy_restatement(quant):
+    # W1 is [E, I, H] and y = SiLU(x W1^T): the C oracle against the independent numpy version
+    d = O.make_inputs(T=36, H=256, I=256, E=5, K=2, quant=quant, seed=3, gate_only=True)
+    assert d["w1"].shape[1] == 256
+    out = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
+                      gate_only=True)
+    ref = O.np_fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"],
+                         d["w2_scale"], gate_only=True)
+    got, want = O.bf16_to_f32(out), O.bf16_to_f32(ref)
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-3)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-3
+
+
 def test_fused_moe_is_linear_in_topk_weight():
     d = O.make_inputs(T=24, H=256, I=128, E=4, K=2, quant=1, seed=2)
     a = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], 1, d["w1_scale"], d["w2_scale"])
