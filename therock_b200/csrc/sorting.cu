@@ -348,14 +348,19 @@ cudaError_t launch_moe_sorting(const int32_t* topk_ids, const float* topk_weight
     int32_t* cnt_cta = scratch;
     int32_t* cta_base = scratch + static_cast<size_t>(kSortMaxCtas) * E;
     const size_t smem_cnt = (static_cast<size_t>(kSortWarps) * E + E) * sizeof(int32_t);
-    static bool configured = false;     // opt in to large dynamic shared memory once (E up to 1024)
-    if (!configured) {
+    // opt in to large dynamic shared memory (E up to 1024) once per device: the attribute
+    // belongs to the device the function is loaded on
+    constexpr int kMaxDevices = 64;
+    static bool configured[kMaxDevices] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
       cudaError_t e1 = cudaFuncSetAttribute(sort_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
       cudaError_t e2 = cudaFuncSetAttribute(sort_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
       if (e1 != cudaSuccess) return e1;
       if (e2 != cudaSuccess) return e2;
+      if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
     }
-    configured = true;
     cudaError_t e = launch_pdl(sort_count_kernel, dim3(n_ctas), dim3(kSortThreads), smem_cnt, stream, topk_ids, T,
                                num_tokens_dev, K, E, id_div, block_m, static_cast<int>(cap), sorted_token_ids,
                                sorted_weights, sorted_rows, sorted_expert_ids, cnt_cta);
