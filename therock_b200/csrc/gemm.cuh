@@ -62,7 +62,8 @@ struct GemmParams {
   uint32_t debug_flags;         // diagnostics only (results are invalid when set): bit 0 = the
                                 // epilogue skips its work (block-scaled kernel: no promotion
                                 // FMAs), bit 1 = no MMA is issued; block-scaled kernel only:
-                                // bit 2 = no TMEM loads, bit 3 = scalar FMAs, bit 4 = no final stores
+                                // bit 2 = no TMEM loads, bit 3 = scalar FMAs, bit 4 = no final stores,
+                                // bit 5 = no TMA loads (the MMAs run on whatever shared memory holds)
 };
 
 struct TileCoord {
@@ -758,6 +759,11 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t full = ptx::smem_u32(&full_bar[stage]);
           const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
           const uint32_t sb = sa + kABytes;
+          if (p.debug_flags & 32u) {     // timing experiment: no operand traffic at all
+            ptx::mbar_arrive(full);
+            if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
           const int kx = k * 128;
           int bx, by0, by1;
