@@ -677,10 +677,11 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
 // [128h, 128h+128), one weight-scale block.
 constexpr int kBlockGemmThreads = 384;   // warpgroup 0: producer + MMA (+2 idle warps); warpgroups 1, 2: epilogue
 constexpr int kBlockStages = 4;
+constexpr int kScaleAhead = 4;           // K blocks between the load of a scale and its use
 // setmaxnreg only redistributes what the CTA was given at launch (384 threads x 168 registers):
 // the per-role counts must add up to no more than that, or setmaxnreg.inc never returns.
 constexpr int kBlockThinRegs = 40;       // registers per thread kept by warpgroup 0
-constexpr int kBlockFatRegs = 216;       // registers per thread taken by the epilogue warpgroups
+constexpr int kBlockFatRegs = 232;       // registers per thread taken by the epilogue warpgroups
 static_assert(128 * kBlockThinRegs + 256 * kBlockFatRegs <= kBlockGemmThreads * 168, "register budget");
 constexpr int kBlockSmemBytes = kBlockStages * kStageBytes + kSmemMisc + 8 * 32 * 20 * 4 + 1024;
 
@@ -837,14 +838,29 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       // TMEM columns of this thread's two 64-column runs
       const int col0 = (kEpi == kEpiSiluMul) ? half * 64 : half * 128;
       const int col1 = (kEpi == kEpiSiluMul) ? kSlabRows + half * 64 : half * 128 + 64;
-      float s_act = __ldg(sa_row), s_b0 = __ldg(sb0), s_b1 = __ldg(sb1);
-      for (int k = 0; k < p.k_iters; ++k) {
-        const float sc0 = s_act * s_b0, sc1 = s_act * s_b1;
+      // Scales are fetched kScaleAhead K blocks before they are used: the per-row loads miss
+      // the small L1 that is left beside 221 KiB of shared memory, and an L2 round trip takes
+      // longer than one stage.
+      float q_act[kScaleAhead], q_b0[kScaleAhead], q_b1[kScaleAhead];
+#pragma unroll
+      for (int u = 0; u < kScaleAhead; ++u) {
+        if (u < p.k_iters) {
+          q_act[u] = __ldg(sa_row + u);
+          q_b0[u] = __ldg(sb0 + u);
+          q_b1[u] = __ldg(sb1 + u);
+        }
+      }
+      for (int k0 = 0; ok && k0 < p.k_iters; k0 += kScaleAhead) {
+#pragma unroll
+      for (int u = 0; u < kScaleAhead; ++u) {
+        const int k = k0 + u;
+        if (k >= p.k_iters) break;
+        const float sc0 = q_act[u] * q_b0[u], sc1 = q_act[u] * q_b1[u];
         const uint64_t sc0_2 = ptx::pack2(sc0, sc0), sc1_2 = ptx::pack2(sc1, sc1);
-        if (k + 1 < p.k_iters) {       // next block's scales while this one's product is in flight
-          s_act = __ldg(sa_row + k + 1);
-          s_b0 = __ldg(sb0 + k + 1);
-          s_b1 = __ldg(sb1 + k + 1);
+        if (k + kScaleAhead < p.k_iters) {
+          q_act[u] = __ldg(sa_row + k + kScaleAhead);
+          q_b0[u] = __ldg(sb0 + k + kScaleAhead);
+          q_b1[u] = __ldg(sb1 + k + kScaleAhead);
         }
         if (!ptx::mbar_wait(ptx::smem_u32(&part_full_bar[buf]), buf_phase, abort_flag)) {
           ok = false;
@@ -894,6 +910,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
         }
         if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+      }
       }
       if (!ok) break;
       if (p.debug_flags & 16u) continue;
