@@ -74,7 +74,7 @@ def route_on_device(logits, K, mode):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one gate+up GEMM launch on the
 # benchmark workload, from an ncu capture of this same command (None where no capture of
 # that configuration has been taken).
-GEMM1_DRAM_TRAFFIC_BYTES = {"C1": 2199174144, "C2": None, "C3": None}
+GEMM1_DRAM_TRAFFIC_BYTES = {"C1": 2199174144, "C2": 1756000000, "C3": 951700000, "C4": 9430000000}
 
 
 def measured_peaks():
@@ -534,9 +534,13 @@ def run_gpu(a, c):
             if c["quant"] != 0:
                 peak_kind += " x2 (no fp8 peak was measured)"
             unit, bound = "TFLOP/s", "tensor"
-        line["roofline"] = {"bound": bound, "kernel": "fmoe_grouped_gemm_kernel (gate+up, SiLU*up epilogue)",
+        kernel = {2: "fmoe_grouped_gemm_block_kernel"}.get(
+            c["quant"], "fmoe_grouped_gemm_pair_kernel" if a.config == "C2" else "fmoe_grouped_gemm_kernel")
+        resized = a.tokens > 0 or a.experts > 0       # the captured traffic belongs to the full-size workload
+        line["roofline"] = {"bound": bound, "kernel": kernel + " (gate+up, SiLU*up epilogue)",
                             "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                            "traffic": GEMM1_DRAM_TRAFFIC_BYTES.get(a.config), "peak_kind": peak_kind,
+                            "traffic": None if resized else GEMM1_DRAM_TRAFFIC_BYTES.get(a.config),
+                            "peak_kind": peak_kind,
                             "ms_per_launch": g1_ms}
         if bound == "tensor":
             line["roofline"]["frac_of_burst"] = achieved / (peaks["bf16_burst"] * mult)
