@@ -41,7 +41,7 @@ def _bits(t):
     return t.view(torch.int16).numpy().view(np.uint16)
 
 
-def _worker(rank, world, port, T, H, I, E, K, quant, drop, ret):
+def _worker(rank, world, port, T, H, I, E, K, quant, drop, ret, dedup=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -65,7 +65,8 @@ def _worker(rank, world, port, T, H, I, E, K, quant, drop, ret):
         x = torch.from_numpy(d["x"][sl].view(np.int16)).view(torch.bfloat16)
         ids = torch.from_numpy(d["topk_ids"][sl].copy())
         wts = torch.from_numpy(d["topk_w"][sl].copy())
-        moe = ep.ExpertParallelMoE(E, world, rank, local_moe, gather=_cpu_gather, combine=_cpu_combine)
+        moe = ep.ExpertParallelMoE(E, world, rank, local_moe, gather=_cpu_gather, combine=_cpu_combine,
+                                   dedup=dedup)
         out = moe.forward(x, ids, wts)
         ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
                           sel=np.arange(sl.start, sl.stop, dtype=np.int32))
@@ -90,6 +91,36 @@ def test_expert_parallel_matches_single_rank_oracle(world, quant, drop):
         p.join(180)
         assert p.exitcode == 0
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+@pytest.mark.parametrize("world,quant,K", [(2, 0, 4), (4, 1, 3)])
+def test_deduplicated_dispatch_matches_single_rank_oracle(world, quant, K):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 64, 256, 128, 8, K, quant, True, ret, True))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_dedup_plan_sends_one_row_per_token_and_rank():
+    ids = torch.tensor([[0, 1, 5], [4, 6, 7], [2, 9, -1], [3, 4, 0]], dtype=torch.int32)   # 8 experts, 2 ranks
+    w = torch.arange(12, dtype=torch.float32).reshape(4, 3) + 1
+    # world = 2 without a process group: only the local arithmetic (the count exchange needs ranks)
+    T, K, world, epr = 4, 3, 2, 4
+    dest = torch.where((ids >= 0) & (ids < 8), ids.long() // epr, torch.full_like(ids.long(), world))
+    hit = torch.zeros(T, world + 1, dtype=torch.bool).scatter_(1, dest, True)[:, :world]
+    assert hit.tolist() == [[True, True], [False, True], [True, False], [True, True]]
+    assert int(hit.sum()) == 6 < int(((ids >= 0) & (ids < 8)).sum())       # 6 rows instead of 10 pairs
+    single = ep.plan_dispatch_dedup(ids, w, experts_per_rank=8, world=1)
+    assert single.n_send == 4 and single.send_counts == [4] and single.index.tolist() == [0, 1, 2, 3]
+    assert single.ids.tolist() == [[0, 1, 5], [4, 6, 7], [2, -1, -1], [3, 4, 0]]
+    assert single.weights[2].tolist() == [7.0, 0.0, 0.0]
 
 
 def test_plan_dispatch_single_rank_is_stable_grouping():

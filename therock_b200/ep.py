@@ -55,6 +55,52 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, gro
                         n_send=n_send, n_recv=int(sum(recv_counts)))
 
 
+@dataclass
+class DedupPlan:
+    """One send row per (token, destination rank) instead of one per (token, expert)."""
+    tok: torch.Tensor            # [n_send] token of each send row, grouped by destination rank
+    ids: torch.Tensor            # [n_send, K] expert ids local to the destination, -1 where the pair goes elsewhere
+    weights: torch.Tensor        # [n_send, K] routing weights at the same positions (0 where unused)
+    send_counts: list
+    recv_counts: list
+    index: torch.Tensor          # [T * world] send row of (token, rank), -1 if the token sends nothing there
+    n_send: int
+    n_recv: int
+
+
+def plan_dispatch_dedup(topk_ids: torch.Tensor, topk_weight: torch.Tensor, experts_per_rank: int, world: int,
+                        group=None) -> DedupPlan:
+    """Groups a token's pairs by owning rank: a token whose K experts live on d distinct ranks
+    sends d rows (each with the K-wide id/weight lists of that rank, k positions kept) instead of K."""
+    T, K = topk_ids.shape
+    dev = topk_ids.device
+    ids = topk_ids.to(torch.int64)
+    n_exp = experts_per_rank * world
+    valid = (ids >= 0) & (ids < n_exp)
+    dest = torch.where(valid, ids // experts_per_rank, torch.full_like(ids, world))          # [T, K]
+    hit = torch.zeros(T, world + 1, dtype=torch.bool, device=dev)
+    hit.scatter_(1, dest, True)
+    hit = hit[:, :world]                                                                     # [T, world]
+    # send rows ordered by (rank, token): column-major walk over `hit`
+    rank_of, tok = torch.nonzero(hit.t(), as_tuple=True)
+    n_send = int(tok.numel())
+    counts = hit.sum(dim=0).to(torch.int64)
+    index = torch.full((T * world,), -1, dtype=torch.int32, device=dev)
+    index[tok * world + rank_of] = torch.arange(n_send, dtype=torch.int32, device=dev)
+    mine = dest[tok] == rank_of.unsqueeze(1)                                                 # [n_send, K]
+    row_ids = torch.where(mine, ids[tok] % experts_per_rank, torch.full_like(ids[tok], -1)).to(torch.int32)
+    row_w = torch.where(mine, topk_weight[tok], torch.zeros_like(topk_weight[tok]))
+    recv_counts_t = torch.empty_like(counts)
+    if world > 1:
+        dist.all_to_all_single(recv_counts_t, counts, group=group)
+    else:
+        recv_counts_t.copy_(counts)
+    recv_counts = recv_counts_t.tolist()
+    return DedupPlan(tok=tok.to(torch.int32), ids=row_ids.contiguous(), weights=row_w.contiguous(),
+                     send_counts=counts.tolist(), recv_counts=recv_counts, index=index, n_send=n_send,
+                     n_recv=int(sum(recv_counts)))
+
+
 def _a2a(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, world: int, group=None):
     if world > 1:
         dist.all_to_all_single(out, inp, out_splits, in_splits, group=group)
@@ -71,10 +117,14 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, num_experts: int, world: int, rank: int, local_moe: Callable,
-                 gather: Optional[Callable] = None, combine: Optional[Callable] = None, group=None):
+                 gather: Optional[Callable] = None, combine: Optional[Callable] = None, group=None,
+                 dedup: bool = False):
         if num_experts % world:
             raise ValueError("experts must divide evenly over ranks")
         self.E, self.world, self.rank, self.group = num_experts, world, rank, group
+        # dedup: one row per (token, destination rank); the owner sums the token's local experts
+        # (k ascending) and returns one partial row, the sender adds the partials in rank order
+        self.dedup = dedup
         self.e_local = num_experts // world
         self.local_moe = local_moe
         self.gather = gather or _cuda_gather
@@ -87,7 +137,35 @@ class ExpertParallelMoE:
             ev.record()
             self.trace.append((name, ev))
 
+    def _forward_dedup(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor) -> torch.Tensor:
+        T, H = x.shape
+        K = topk_ids.shape[1]
+        dev = x.device
+        self._mark("start")
+        plan = plan_dispatch_dedup(topk_ids, topk_weight, self.e_local, self.world, self.group)
+        self._mark("plan")
+        send_rows = self.gather(x, plan.tok)
+        send_meta = torch.cat([plan.ids.to(torch.float32), plan.weights.to(torch.float32)], dim=1).contiguous()
+        self._mark("pack")
+        recv_rows = torch.empty(plan.n_recv, H, dtype=x.dtype, device=dev)
+        recv_meta = torch.empty(plan.n_recv, 2 * K, dtype=torch.float32, device=dev)
+        _a2a(recv_rows, send_rows, plan.recv_counts, plan.send_counts, self.world, self.group)
+        _a2a(recv_meta, send_meta, plan.recv_counts, plan.send_counts, self.world, self.group)
+        self._mark("dispatch")
+        ids_local = recv_meta[:, :K].to(torch.int32).contiguous()       # -1 entries are skipped by the operator
+        w_local = recv_meta[:, K:].contiguous()
+        part = self.local_moe(recv_rows, ids_local, w_local) if plan.n_recv > 0 else recv_rows
+        self._mark("local_moe")
+        back = torch.empty(plan.n_send, H, dtype=x.dtype, device=dev)
+        _a2a(back, part, plan.send_counts, plan.recv_counts, self.world, self.group)
+        self._mark("return")
+        out = self.combine(back, plan.index, T, self.world)             # partial rows added in rank order
+        self._mark("combine")
+        return out
+
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor) -> torch.Tensor:
+        if self.dedup:
+            return self._forward_dedup(x, topk_ids, topk_weight)
         T, H = x.shape
         K = topk_ids.shape[1]
         self._mark("start")
