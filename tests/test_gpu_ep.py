@@ -28,7 +28,7 @@ def _close(got_bits, ref_bits, quant):
         np.linalg.norm(g - r) <= (6e-3 if quant == 0 else 4e-2) * np.linalg.norm(r)
 
 
-def _rank_forward(d, rank, world, device):
+def _rank_forward(d, rank, world, device, dedup=False):
     from therock_b200 import ep
     quant = d["quant"]
     E = d["w1"].shape[0]
@@ -45,7 +45,7 @@ def _rank_forward(d, rank, world, device):
     t_local = T // world
     sl = slice(rank * t_local, (rank + 1) * t_local)
     local = ep.make_local_moe(traits_for(quant), w1, w2, s1, s2)
-    moe = ep.ExpertParallelMoE(E, world, rank, local)
+    moe = ep.ExpertParallelMoE(E, world, rank, local, dedup=dedup)
     out = moe.forward(bf16_dev(d["x"][sl], device), to_dev(d["topk_ids"][sl], device=device),
                       to_dev(d["topk_w"][sl], device=device))
     torch.cuda.synchronize()
@@ -57,6 +57,17 @@ def test_single_rank_expert_parallel_path(quant):
     d = O.make_inputs(200, 512, 256, 8, 2, quant, "softmax", seed=21)
     d["topk_ids"][::9, 1] = -1
     got, _ = _rank_forward(d, 0, 1, "cuda:0")
+    ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"])
+    assert _close(got, ref, quant)
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_single_rank_deduplicated_dispatch(quant):
+    # one row per token with its K-wide id list (invalid ids stay -1): the CUDA gather,
+    # operator and combine kernels behind the de-duplicated plan
+    d = O.make_inputs(200, 512, 256, 8, 3, quant, "softmax", seed=22)
+    d["topk_ids"][::7, 2] = -1
+    got, _ = _rank_forward(d, 0, 1, "cuda:0", dedup=True)
     ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"])
     assert _close(got, ref, quant)
 
