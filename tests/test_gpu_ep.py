@@ -124,14 +124,14 @@ def test_two_gpu_peer_memory_expert_parallel(quant):
     assert all(ret.get(r) for r in range(2)), dict(ret)
 
 
-def _worker(rank, world, port, quant, ret):
+def _worker(rank, world, port, quant, ret, dedup=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        d = O.make_inputs(256, 512, 256, 8, 2, quant, "softmax", seed=22)
-        got, sl = _rank_forward(d, rank, world, f"cuda:{rank}")
+        d = O.make_inputs(256, 512, 256, 8, 4 if dedup else 2, quant, "softmax", seed=22)
+        got, sl = _rank_forward(d, rank, world, f"cuda:{rank}", dedup=dedup)
         ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
                           sel=np.arange(sl.start, sl.stop, dtype=np.int32))
         ret[rank] = bool(_close(got, ref, quant))
@@ -139,15 +139,15 @@ def _worker(rank, world, port, quant, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("quant", [0, 1])
-def test_two_gpu_expert_parallel(quant):
+@pytest.mark.parametrize("quant,dedup", [(0, False), (1, False), (1, True)])
+def test_two_gpu_expert_parallel(quant, dedup):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, quant, ret)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, quant, ret, dedup)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
