@@ -21,12 +21,13 @@ struct fused_moe_traits {
   std::string prec_i = "bf16";   // activation input type: "bf16"
   std::string prec_w = "bf16";   // weight type: "bf16" or "fp8"
   std::string prec_o = "bf16";   // output type: "bf16"
-  std::string quant = "none";    // "none" | "token_channel" | "block128"
+  std::string quant = "none";    // "none" | "token_channel" | "block128" | "block128_ue8m0"
   std::string activation = "silu";
   int gate_only = 0;             // 0: gate and up rows packed as [2I, H]
   int block_m = 128;             // sorted M-block
   int gemm_mode = 0;             // 0 = per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel
   std::string weight_layout = "row_major";   // or "tiled128": weights pre-shuffled into 16 KiB tiles
+  std::string partial_dtype = "f32";         // "f32" | "bf16": weighted expert outputs before the ordered sum
 };
 
 struct fused_moe_args {
@@ -61,6 +62,7 @@ inline int to_c(const fused_moe_traits& t, fmoe_traits_c* c) {
   if (t.quant == "none") c->quant = FMOE_QUANT_NONE;
   else if (t.quant == "token_channel") c->quant = FMOE_QUANT_TOKEN_CHANNEL;
   else if (t.quant == "block128") c->quant = FMOE_QUANT_BLOCK128;
+  else if (t.quant == "block128_ue8m0") c->quant = FMOE_QUANT_BLOCK128_UE8M0;
   else return FMOE_ERR_INVALID_ARG;
   if (t.prec_w == "bf16") c->weight_dtype = FMOE_BF16;
   else if (t.prec_w == "fp8") c->weight_dtype = FMOE_FP8_E4M3;
@@ -72,6 +74,9 @@ inline int to_c(const fused_moe_traits& t, fmoe_traits_c* c) {
   c->gemm_mode = t.gemm_mode;
   if (t.weight_layout == "row_major") c->weight_layout = FMOE_WEIGHTS_ROW_MAJOR;
   else if (t.weight_layout == "tiled128") c->weight_layout = FMOE_WEIGHTS_TILED128;
+  else return FMOE_ERR_INVALID_ARG;
+  if (t.partial_dtype == "f32") c->partial_dtype = FMOE_PARTIAL_F32;
+  else if (t.partial_dtype == "bf16") c->partial_dtype = FMOE_PARTIAL_BF16;
   else return FMOE_ERR_INVALID_ARG;
   return FMOE_OK;
 }

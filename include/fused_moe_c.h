@@ -50,7 +50,29 @@ enum fmoe_dtype { FMOE_BF16 = 0, FMOE_FP8_E4M3 = 1 };
 enum fmoe_quant {
   FMOE_QUANT_NONE = 0,          /* bf16 activations and weights */
   FMOE_QUANT_TOKEN_CHANNEL = 1, /* fp8: dynamic per-token activation scale, per-output-channel weight scale */
-  FMOE_QUANT_BLOCK128 = 2       /* fp8: 1x128 activation groups, 128x128 weight blocks */
+  FMOE_QUANT_BLOCK128 = 2,      /* fp8: 1x128 activation groups, 128x128 weight blocks, f32 scales */
+  FMOE_QUANT_BLOCK128_UE8M0 = 3 /* same granularity with power-of-two scales (the MX "UE8M0" scale format):
+                                   activation scales are 2^ceil(log2(absmax/448)); the weight scales passed
+                                   in must be powers of two.  The scales are applied inside the tensor core
+                                   (tcgen05.mma kind::mxf8f6f4.block_scale), the accumulator never leaves
+                                   tensor memory during the K loop */
+};
+
+/* How the K weighted expert outputs of a token are held before the ordered sum. */
+enum fmoe_partial_dtype {
+  FMOE_PARTIAL_F32 = 0, /* f32: out = bf16( sum_k f32 partial ), one rounding (the default contract) */
+  FMOE_PARTIAL_BF16 = 1 /* each partial is rounded to bf16 first, then summed in f32 in k order and rounded
+                           once more: halves the traffic of the partial rows; this is also what the
+                           expert-parallel path does, where partial rows cross NVLink as bf16 */
+};
+
+/* Kernel flavours of the grouped GEMM, as reported by fmoe_describe_run. */
+enum fmoe_gemm_kernel {
+  FMOE_KERNEL_SINGLE = 1,        /* fmoe_grouped_gemm_kernel: one CTA per 128 x 256 tile */
+  FMOE_KERNEL_PAIR = 2,          /* fmoe_grouped_gemm_pair_kernel: CTA pair, cta_group::2, 256 x 256 tile */
+  FMOE_KERNEL_BLOCK_PROMOTE = 3, /* fmoe_grouped_gemm_block_kernel<.., false>: per-128 partials promoted in registers */
+  FMOE_KERNEL_BLOCK_HW_SCALE = 4,/* fmoe_grouped_gemm_block_kernel<.., true>: block_scale MMA, UE8M0 scales */
+  FMOE_KERNEL_SINGLE_DECODE = 5  /* fmoe_grouped_gemm_kernel staging 32 activation rows (at most 32 routed rows) */
 };
 
 enum fmoe_activation { FMOE_ACT_SILU = 0 };
@@ -73,7 +95,7 @@ typedef struct fmoe_traits_c {
   int32_t gemm_mode;    /* 0 = chosen per GEMM from the expected tile counts, 1 = single-CTA
                            kernel, 2 = CTA-pair kernel (cta_group::2) */
   int32_t weight_layout; /* fmoe_weight_layout of w1 and w2 */
-  int32_t reserved[1];
+  int32_t partial_dtype; /* fmoe_partial_dtype */
 } fmoe_traits_c;
 
 /* Run-time arguments (ck_tile's fused_moe_args role).  All pointers are device pointers. */
@@ -81,8 +103,8 @@ typedef struct fmoe_args_c {
   const void* x;            /* [T, H] bf16 activations */
   const void* w1;           /* [E, 2I, H] gate rows then up rows ([E, I, H] when gate_only); bf16 or e4m3 */
   const void* w2;           /* [E, H, I]; bf16 or e4m3 */
-  const float* w1_scale;    /* quant 1: [E, 2I]; quant 2: [E, 2I/128, H/128]; else NULL */
-  const float* w2_scale;    /* quant 1: [E, H];  quant 2: [E, H/128, I/128]; else NULL */
+  const float* w1_scale;    /* quant 1: [E, 2I]; quant 2, 3: [E, 2I/128, H/128]; else NULL */
+  const float* w2_scale;    /* quant 1: [E, H];  quant 2, 3: [E, H/128, I/128]; else NULL */
   const int32_t* topk_ids;  /* [T, K]; ids outside [0, E) are skipped */
   const float* topk_weight; /* [T, K] */
   void* out;                /* [T, H] bf16 */
@@ -139,11 +161,14 @@ typedef struct fmoe_ws_layout_c {
   uint64_t sorted_expert_ids; /* int32[capacity/block_m] */
   uint64_t mblk_cum;          /* int32[E+1]: cumulative blocks per expert */
   uint64_t a_sorted;          /* [capacity, H] activations in sorted order (bf16 or e4m3) */
-  uint64_t a_scale;           /* float[capacity] (fp8 variants) */
-  uint64_t y;                 /* bf16 [capacity, I]: SiLU(gate)*up */
+  uint64_t a_scale;           /* quant 1: float[capacity]; quant 2: float[capacity, H/128]; quant 3: one UE8M0
+                                 byte per row and 128-wide K group, per (128-row block, four K groups) a
+                                 512-byte image: byte (row%32)*16 + (row/32)*4 + group%4 */
+  uint64_t y;                 /* bf16 [capacity, I]: SiLU(gate)*up (quant 0, 1; the block-scaled modes
+                                 quantise inside the first GEMM and keep no bf16 copy) */
   uint64_t y_quant;           /* e4m3 [capacity, I] (fp8 variants) */
-  uint64_t y_scale;           /* float[capacity] (fp8 variants) */
-  uint64_t slots;             /* float [T*K, H]: weighted expert outputs before the combine */
+  uint64_t y_scale;           /* as a_scale, with I in place of H */
+  uint64_t slots;             /* float or bf16 (traits.partial_dtype) [T*K, H]: weighted expert outputs */
   uint64_t sort_scratch;      /* int32[128*E]: per-CTA histograms of the multi-CTA moe_sorting */
 } fmoe_ws_layout_c;
 
@@ -259,8 +284,21 @@ FMOE_API int fmoe_ep_return(const void* out_rows, int32_t H, const int32_t* n_re
                             const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
                             int32_t G, void* stream);
 
-/* Number of kernels one fmoe_run launches for these traits (for launch accounting). */
-FMOE_API int fmoe_launches_per_run(const fmoe_traits_c* traits);
+/* What one fmoe_run with these traits and dimensions will launch on the current device: the
+ * kernel flavour of each GEMM (the same decision fmoe_run takes) and the number of kernels
+ * (moe_sorting is one launch below 8192 routed pairs and three from there on).  Only the
+ * dimensions of `args` are read.  No counterpart in ck_tile. */
+typedef struct fmoe_run_info_c {
+  int32_t gemm1_kernel;   /* fmoe_gemm_kernel */
+  int32_t gemm2_kernel;   /* fmoe_gemm_kernel */
+  int32_t sort_launches;  /* 1 or 3 */
+  int32_t quant_y_launch; /* 1 when the intermediate is quantised by a kernel of its own */
+  int32_t launches;       /* kernels per fmoe_run */
+  int32_t reserved[3];
+} fmoe_run_info_c;
+FMOE_API int fmoe_describe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, fmoe_run_info_c* info);
+/* Name of a kernel flavour ("fmoe_grouped_gemm_pair_kernel", ...), or "" for an unknown code. */
+FMOE_API const char* fmoe_gemm_kernel_name(int32_t kernel);
 
 #ifdef __cplusplus
 } /* extern "C" */

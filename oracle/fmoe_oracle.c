@@ -26,11 +26,16 @@
  *   bf16 path : gate/up = x . W1^T accumulated in f32; y = silu(gate)*up in f32, rounded
  *               to bf16; o = y . W2^T in f32; out = bf16( sum_k w_k * o_k ), k ascending.
  *   quantise  : s = absmax/448 (1 if all zero), r = 1/s in f32, q = e4m3(v * r).
+ *               Power-of-two variant (mode 3, the MX "UE8M0" scale format): s is the smallest
+ *               power of two >= absmax/448, exponent clamped to [-126, 127].
  *   fp8 paths : operands quantised (activations dynamically, weights given quantised),
  *               integer-exact products accumulated in f32, scales applied after the
  *               accumulation (per token x per channel) or per 128-deep K block
  *               (1x128 activation groups x 128x128 weight blocks).  The intermediate y is
  *               rounded to bf16 (as in the bf16 path) and then quantised dynamically.
+ *   combine   : default: out = bf16( sum_k f32(w_k * o_k) ).  bf16-partial variant (what the
+ *               expert-parallel path and the partial_dtype = bf16 trait compute): every
+ *               w_k * o_k is rounded to bf16 first, the sum of those is f32, rounded once more.
  */
 #include <math.h>
 #include <stdint.h>
@@ -123,8 +128,32 @@ ORC_API void orc_e4m3_to_f32(const uint8_t* in, float* out, int64_t n) {
  * reciprocal rounded once to f32.
  * group == cols gives the per-token (or per-output-channel) mode, group == 128 the 1x128
  * mode.  scales has rows * (cols/group) entries. */
+/* scale of one quantisation group from its absolute maximum; pow2: rounded up to a power of two */
+static inline float scale_from_amax(float amax, int pow2) {
+  if (!(amax > 0.0f)) return 1.0f;
+  float t = amax / 448.0f;
+  if (!pow2) return t;
+  uint32_t u;
+  memcpy(&u, &t, 4);
+  uint32_t e = (u >> 23) + ((u & 0x7fffffu) ? 1u : 0u);
+  if (e < 1u) e = 1u;
+  if (e > 254u) e = 254u;
+  u = e << 23;
+  memcpy(&t, &u, 4);
+  return t;
+}
+
+ORC_API void orc_quant_rows_e4m3_ex(const float* in, int64_t rows, int64_t cols, int64_t group, int pow2,
+                                    uint8_t* q, float* scales);
+
 ORC_API void orc_quant_rows_e4m3(const float* in, int64_t rows, int64_t cols, int64_t group,
                                  uint8_t* q, float* scales) {
+  orc_quant_rows_e4m3_ex(in, rows, cols, group, 0, q, scales);
+}
+
+/* pow2 = 1: power-of-two scales (mode 3) */
+ORC_API void orc_quant_rows_e4m3_ex(const float* in, int64_t rows, int64_t cols, int64_t group, int pow2,
+                                    uint8_t* q, float* scales) {
   int64_t ng = cols / group;
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < rows; ++r) {
@@ -135,7 +164,7 @@ ORC_API void orc_quant_rows_e4m3(const float* in, int64_t rows, int64_t cols, in
         float a = fabsf(p[c]);
         if (a > amax) amax = a;
       }
-      float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+      float s = scale_from_amax(amax, pow2);
       float inv = 1.0f / s;
       scales[r * ng + g] = s;
       uint8_t* o = q + r * cols + g * group;
@@ -145,8 +174,14 @@ ORC_API void orc_quant_rows_e4m3(const float* in, int64_t rows, int64_t cols, in
 }
 
 /* Quantise a weight tensor [rows, cols] with one scale per 128x128 block. */
+ORC_API void orc_quant_blocks_e4m3_ex(const float* in, int64_t rows, int64_t cols, int pow2,
+                                      uint8_t* q, float* scales);
 ORC_API void orc_quant_blocks_e4m3(const float* in, int64_t rows, int64_t cols,
                                    uint8_t* q, float* scales) {
+  orc_quant_blocks_e4m3_ex(in, rows, cols, 0, q, scales);
+}
+ORC_API void orc_quant_blocks_e4m3_ex(const float* in, int64_t rows, int64_t cols, int pow2,
+                                      uint8_t* q, float* scales) {
   int64_t rb = rows / 128, cb = cols / 128;
 #pragma omp parallel for schedule(static)
   for (int64_t b = 0; b < rb * cb; ++b) {
@@ -157,7 +192,7 @@ ORC_API void orc_quant_blocks_e4m3(const float* in, int64_t rows, int64_t cols,
         float a = fabsf(in[(br * 128 + r) * cols + bc * 128 + c]);
         if (a > amax) amax = a;
       }
-    float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+    float s = scale_from_amax(amax, pow2);
     float inv = 1.0f / s;
     scales[b] = s;
     for (int64_t r = 0; r < 128; ++r)
@@ -282,7 +317,7 @@ static inline float dot_f32(const float* a, const float* b, int64_t n) {
 
 static inline float silu_f32(float g) { return g / (1.0f + expf(-g)); }
 
-enum { ORC_Q_NONE = 0, ORC_Q_TOKEN_CHANNEL = 1, ORC_Q_BLOCK128 = 2 };
+enum { ORC_Q_NONE = 0, ORC_Q_TOKEN_CHANNEL = 1, ORC_Q_BLOCK128 = 2, ORC_Q_BLOCK128_POW2 = 3 };
 
 /* One expert applied to one token.
  *   xin : the token's activation row, f32 values (bf16-exact for mode 0, the e4m3 values
@@ -330,7 +365,7 @@ static void expert_forward(int quant, int gate_only, int H, int I, const float* 
         float a = fabsf(y[g * group + c]);
         if (a > amax) amax = a;
       }
-      float s = amax > 0.0f ? amax / 448.0f : 1.0f;
+      float s = scale_from_amax(amax, quant == ORC_Q_BLOCK128_POW2);
       float inv = 1.0f / s;
       ys[g] = s;
       for (int c = 0; c < group; ++c)
@@ -365,14 +400,24 @@ static void expert_forward(int quant, int gate_only, int H, int I, const float* 
  *            token here (x and the intermediate y).
  *   quant 2: w1/w2 e4m3 bytes, w1_scale [E,2I/128,H/128], w2_scale [E,H/128,I/128];
  *            activations quantised per 1x128 group here.
+ *   quant 3: as 2 with power-of-two scales.
  *   x [T,H] bf16; topk_ids/topk_w [T,K]; sel = n_sel token indices to evaluate (NULL = all
  *   T tokens in order); out [n_sel or T, H] bf16.
  * Expert ids outside [0,E) contribute nothing. */
+ORC_API int orc_fused_moe_ex2(int T, int H, int I, int E, int K, int quant, int gate_only, int partial_bf16,
+                              const uint16_t* x, const void* w1, const void* w2,
+                              const float* w1_scale, const float* w2_scale,
+                              const int32_t* topk_ids, const float* topk_w,
+                              const int32_t* sel, int n_sel, uint16_t* out, int n_threads);
+
 ORC_API int orc_fused_moe_ex(int T, int H, int I, int E, int K, int quant, int gate_only,
                              const uint16_t* x, const void* w1, const void* w2,
                              const float* w1_scale, const float* w2_scale,
                              const int32_t* topk_ids, const float* topk_w,
-                             const int32_t* sel, int n_sel, uint16_t* out, int n_threads);
+                             const int32_t* sel, int n_sel, uint16_t* out, int n_threads) {
+  return orc_fused_moe_ex2(T, H, I, E, K, quant, gate_only, 0, x, w1, w2, w1_scale, w2_scale, topk_ids, topk_w, sel,
+                           n_sel, out, n_threads);
+}
 
 ORC_API int orc_fused_moe(int T, int H, int I, int E, int K, int quant,
                           const uint16_t* x, const void* w1, const void* w2,
@@ -384,16 +429,19 @@ ORC_API int orc_fused_moe(int T, int H, int I, int E, int K, int quant,
 }
 
 /* gate_only = 1: W1 is [E, I, H] (no up projection) and y = SiLU(x . W1^T); weight scales of
- * W1 then have I rows per expert ([E, I] or [E, I/128, H/128]). */
-ORC_API int orc_fused_moe_ex(int T, int H, int I, int E, int K, int quant, int gate_only,
-                             const uint16_t* x, const void* w1, const void* w2,
-                             const float* w1_scale, const float* w2_scale,
-                             const int32_t* topk_ids, const float* topk_w,
-                             const int32_t* sel, int n_sel, uint16_t* out, int n_threads) {
+ * W1 then have I rows per expert ([E, I] or [E, I/128, H/128]).
+ * quant 3: as quant 2 with power-of-two activation scales (the weight scales passed in are
+ * expected to be powers of two as well; they are used as given).
+ * partial_bf16 = 1: every weighted expert output w_k * o_k is rounded to bf16 before the sum. */
+ORC_API int orc_fused_moe_ex2(int T, int H, int I, int E, int K, int quant, int gate_only, int partial_bf16,
+                              const uint16_t* x, const void* w1, const void* w2,
+                              const float* w1_scale, const float* w2_scale,
+                              const int32_t* topk_ids, const float* topk_w,
+                              const int32_t* sel, int n_sel, uint16_t* out, int n_threads) {
   build_lut();
   const int w1_rows = gate_only ? I : 2 * I;
-  if (quant < 0 || quant > 2) return -1;
-  if (quant == ORC_Q_BLOCK128 && (H % 128 || I % 128)) return -2;
+  if (quant < 0 || quant > 3) return -1;
+  if (quant >= ORC_Q_BLOCK128 && (H % 128 || I % 128)) return -2;
   int n = sel ? n_sel : T;
   int maxd = H > I ? H : I;
   size_t wbytes = quant == ORC_Q_NONE ? 2 : 1;
@@ -418,7 +466,7 @@ ORC_API int orc_fused_moe_ex(int T, int H, int I, int E, int K, int quant, int g
       for (int k = 0; k < H; ++k) xin[k] = bf16_to_f32(xr[k]);
       if (quant != ORC_Q_NONE) {
         int64_t group = quant == ORC_Q_TOKEN_CHANNEL ? H : 128;
-        orc_quant_rows_e4m3(xin, 1, H, group, q8, xs);
+        orc_quant_rows_e4m3_ex(xin, 1, H, group, quant == ORC_Q_BLOCK128_POW2, q8, xs);
         for (int k = 0; k < H; ++k) xin[k] = g_e4m3_lut[q8[k]];
       }
       for (int h = 0; h < H; ++h) acc[h] = 0.0f;
@@ -433,12 +481,15 @@ ORC_API int orc_fused_moe_ex(int T, int H, int I, int E, int K, int quant, int g
         if (quant == ORC_Q_TOKEN_CHANNEL) {
           s1 = w1_scale + (size_t)e * w1_rows;
           s2 = w2_scale + (size_t)e * H;
-        } else if (quant == ORC_Q_BLOCK128) {
+        } else if (quant >= ORC_Q_BLOCK128) {
           s1 = w1_scale + (size_t)e * (w1_rows / 128) * (H / 128);
           s2 = w2_scale + (size_t)e * (H / 128) * (I / 128);
         }
         expert_forward(quant, gate_only, H, I, xin, xs, w1e, w2e, s1, s2, wrow, y, yq, ys, o);
-        for (int h = 0; h < H; ++h) acc[h] += wk * o[h];
+        if (partial_bf16)
+          for (int h = 0; h < H; ++h) acc[h] += bf16_to_f32(f32_to_bf16(wk * o[h]));
+        else
+          for (int h = 0; h < H; ++h) acc[h] += wk * o[h];
       }
       for (int h = 0; h < H; ++h) out[(int64_t)i * H + h] = f32_to_bf16(acc[h]);
     }

@@ -23,7 +23,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libfmoe_oracle.so")
 _lib = None
 
-QUANT_NONE, QUANT_TOKEN_CHANNEL, QUANT_BLOCK128 = 0, 1, 2
+QUANT_NONE, QUANT_TOKEN_CHANNEL, QUANT_BLOCK128, QUANT_BLOCK128_UE8M0 = 0, 1, 2, 3
 
 
 def build(force: bool = False) -> str:
@@ -130,25 +130,26 @@ def e4m3_to_f32(a: np.ndarray) -> np.ndarray:
     return out
 
 
-def quant_rows_e4m3(a: np.ndarray, group: int | None = None):
-    """[rows, cols] f32 -> (e4m3 bytes [rows, cols], scales [rows, cols/group])."""
+def quant_rows_e4m3(a: np.ndarray, group: int | None = None, pow2: bool = False):
+    """[rows, cols] f32 -> (e4m3 bytes [rows, cols], scales [rows, cols/group]); pow2: scales
+    rounded up to powers of two."""
     a = np.ascontiguousarray(a, dtype=np.float32)
     rows, cols = a.shape
     group = cols if group is None else group
     q = np.empty((rows, cols), dtype=np.uint8)
     s = np.empty((rows, cols // group), dtype=np.float32)
-    lib().orc_quant_rows_e4m3(_p(a), ctypes.c_int64(rows), ctypes.c_int64(cols),
-                              ctypes.c_int64(group), _p(q), _p(s))
+    lib().orc_quant_rows_e4m3_ex(_p(a), ctypes.c_int64(rows), ctypes.c_int64(cols),
+                                 ctypes.c_int64(group), 1 if pow2 else 0, _p(q), _p(s))
     return q, s
 
 
-def quant_blocks_e4m3(a: np.ndarray):
+def quant_blocks_e4m3(a: np.ndarray, pow2: bool = False):
     """[rows, cols] f32 -> (e4m3 bytes, scales [rows/128, cols/128])."""
     a = np.ascontiguousarray(a, dtype=np.float32)
     rows, cols = a.shape
     q = np.empty((rows, cols), dtype=np.uint8)
     s = np.empty((rows // 128, cols // 128), dtype=np.float32)
-    lib().orc_quant_blocks_e4m3(_p(a), ctypes.c_int64(rows), ctypes.c_int64(cols), _p(q), _p(s))
+    lib().orc_quant_blocks_e4m3_ex(_p(a), ctypes.c_int64(rows), ctypes.c_int64(cols), 1 if pow2 else 0, _p(q), _p(s))
     return q, s
 
 
@@ -188,7 +189,7 @@ def moe_sorting(topk_ids: np.ndarray, topk_w: np.ndarray, E: int, block_m: int):
 
 
 def fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None, w2_scale=None,
-              sel=None, n_threads: int = 0, gate_only: bool = False) -> np.ndarray:
+              sel=None, n_threads: int = 0, gate_only: bool = False, partial_bf16: bool = False) -> np.ndarray:
     """x_bf16 [T,H] uint16; w1 [E,2I,H], w2 [E,H,I] (uint16 bf16 bits or uint8 e4m3 bytes).
     Returns out [n_sel or T, H] as bf16 bits (uint16)."""
     x_bf16 = np.ascontiguousarray(x_bf16, dtype=np.uint16)
@@ -209,7 +210,8 @@ def fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None,
         sel = np.ascontiguousarray(sel, dtype=np.int32)
     n = T if sel is None else len(sel)
     out = np.empty((n, H), dtype=np.uint16)
-    rc = lib().orc_fused_moe_ex(T, H, I, E, K, quant, 1 if gate_only else 0, _p(x_bf16), _p(w1), _p(w2),
+    rc = lib().orc_fused_moe_ex2(T, H, I, E, K, quant, 1 if gate_only else 0, 1 if partial_bf16 else 0,
+                                 _p(x_bf16), _p(w1), _p(w2),
                                 _p(w1_scale), _p(w2_scale), _p(topk_ids), _p(topk_w), _p(sel),
                                 0 if sel is None else len(sel), _p(out), n_threads)
     if rc != 0:
@@ -254,11 +256,20 @@ def np_f32_to_e4m3(a: np.ndarray) -> np.ndarray:
     return np.where(sign, code | 0x80, code).astype(np.uint8)
 
 
-def np_quant(a: np.ndarray, group: int):
+def np_pow2_ceil(t: np.ndarray) -> np.ndarray:
+    """Smallest power of two >= t (t > 0, f32), exponent clamped to [-126, 127]."""
+    m, e = np.frexp(t.astype(np.float64))            # t = m * 2^e, m in [0.5, 1)
+    e = np.where(m == 0.5, e - 1, e)
+    return np.ldexp(1.0, np.clip(e, -126, 127)).astype(np.float32)
+
+
+def np_quant(a: np.ndarray, group: int, pow2: bool = False):
     rows, cols = a.shape
     g = a.reshape(rows, cols // group, group).astype(np.float32)
     amax = np.abs(g).max(axis=2)
     s = np.where(amax > 0, amax / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+    if pow2:
+        s = np.where(amax > 0, np_pow2_ceil(s), np.float32(1.0)).astype(np.float32)
     inv = (np.float32(1.0) / s).astype(np.float32)
     q = np_f32_to_e4m3((g * inv[:, :, None]).astype(np.float32))
     return q.reshape(rows, cols), s
@@ -301,7 +312,7 @@ def np_moe_sorting(topk_ids: np.ndarray, topk_w: np.ndarray, E: int, block_m: in
 
 
 def np_fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=None, w2_scale=None,
-                 gate_only: bool = False):
+                 gate_only: bool = False, partial_bf16: bool = False):
     """Per-expert batched restatement (float32 matmuls).  Same contract as orc_fused_moe;
     summation order inside the dot products differs, so agreement is to f32 round-off."""
     T, H = x_bf16.shape
@@ -322,7 +333,7 @@ def np_fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=No
             q, s = np_quant(xe, H)
             gu = (tab[q] @ tab[w1[e]].T) * s * w1_scale[e][None, :]
         else:
-            q, s = np_quant(xe, 128)
+            q, s = np_quant(xe, 128, quant == QUANT_BLOCK128_UE8M0)
             gu = np.zeros((len(t_idx), I2), np.float32)
             wf = tab[w1[e]]
             for kb in range(H // 128):
@@ -338,13 +349,14 @@ def np_fused_moe(x_bf16, w1, w2, topk_ids, topk_w, quant=QUANT_NONE, w1_scale=No
             q, s = np_quant(y, I)
             o = (tab[q] @ tab[w2[e]].T) * s * w2_scale[e][None, :]
         else:
-            q, s = np_quant(y, 128)
+            q, s = np_quant(y, 128, quant == QUANT_BLOCK128_UE8M0)
             o = np.zeros((len(t_idx), H), np.float32)
             wf = tab[w2[e]]
             for kb in range(I // 128):
                 part = tab[q[:, kb * 128:(kb + 1) * 128]] @ wf[:, kb * 128:(kb + 1) * 128].T
                 o += part * s[:, kb:kb + 1] * np.repeat(w2_scale[e][:, kb], 128)[None, :]
-        slots[t_idx, k_idx] = o.astype(np.float32) * topk_w[t_idx, k_idx][:, None]
+        part = o.astype(np.float32) * topk_w[t_idx, k_idx][:, None]
+        slots[t_idx, k_idx] = bf16_to_f32(np_f32_to_bf16(part)) if partial_bf16 else part
     acc = np.zeros((T, H), np.float32)
     for k in range(K):
         acc += slots[:, k]
@@ -380,8 +392,9 @@ def make_inputs(T, H, I, E, K, quant=QUANT_NONE, routing="softmax", seed=0, gate
         d["w1"], d["w1_scale"] = q1.reshape(E, R1, H), s1.reshape(E, R1)
         d["w2"], d["w2_scale"] = q2.reshape(E, H, I), s2.reshape(E, H)
     else:
-        q1, s1 = quant_blocks_e4m3(w1f.reshape(E * R1, H))
-        q2, s2 = quant_blocks_e4m3(w2f.reshape(E * H, I))
+        pow2 = quant == QUANT_BLOCK128_UE8M0
+        q1, s1 = quant_blocks_e4m3(w1f.reshape(E * R1, H), pow2)
+        q2, s2 = quant_blocks_e4m3(w2f.reshape(E * H, I), pow2)
         d["w1"], d["w1_scale"] = q1.reshape(E, R1, H), s1.reshape(E, R1 // 128, H // 128)
         d["w2"], d["w2_scale"] = q2.reshape(E, H, I), s2.reshape(E, H // 128, I // 128)
     return d

@@ -96,6 +96,10 @@ def test_argument_errors_are_reported_before_any_launch(lib):
     a.H = 500
     assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -2
     a.H = 512; a.K = 9
+    # more experts per token than experts is legal: the receiving side of a de-duplicated
+    # expert-parallel dispatch passes K-wide id lists (-1 = elsewhere) to a rank owning fewer experts
+    assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == 0
+    a.K = 0
     assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -1
     assert lib.fmoe_get_workspace_size(None, ctypes.byref(a), ctypes.byref(n)) == -1
     # gate-only: intermediate size must tile by 256, and block128 scales are not built for it
@@ -111,6 +115,14 @@ def test_argument_errors_are_reported_before_any_launch(lib):
     t.weight_layout = 7
     assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -1
     t.weight_layout = 0
+    t.partial_dtype = 5
+    assert lib.fmoe_get_workspace_size(ctypes.byref(t), ctypes.byref(a), ctypes.byref(n)) == -1
+    t.partial_dtype = 0
+    # entry points outside the operator proper report through the same error text
+    assert lib.fmoe_route(None, 1, 1, 1, 0, None, None, None) == -1
+    assert b"fmoe_route" in lib.fmoe_last_error()
+    assert lib.fmoe_ep_plan(None, 1, 1, 1, 1, None, None, None, None, None) == -1
+    assert b"fmoe_ep_plan" in lib.fmoe_last_error()
     assert lib.fmoe_sort(None, None, 1, 1, 1, 128, None, None, None, None, None) == -1
 
 

@@ -5,8 +5,8 @@ include/fused_moe_c.h).  This package only marshals torch tensors into that ABI;
 no Python or CPU fallback: importing the operator without the built library raises.
 """
 from .api import (FusedMoeTraits, FusedMoeArgs, fused_moe, fused_moe_workspace_size,  # noqa: F401
-                  moe_sorting, sort_capacity, workspace_layout, launches_per_run, lib, LIB_PATH,
+                  moe_sorting, sort_capacity, workspace_layout, launches_per_run, describe_run, lib, LIB_PATH,
                   FmoeError, route)
 
 __all__ = ["FusedMoeTraits", "FusedMoeArgs", "fused_moe", "fused_moe_workspace_size", "moe_sorting",
-           "sort_capacity", "workspace_layout", "launches_per_run", "lib", "LIB_PATH", "FmoeError", "route"]
+           "sort_capacity", "workspace_layout", "launches_per_run", "describe_run", "lib", "LIB_PATH", "FmoeError", "route"]

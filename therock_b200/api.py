@@ -11,7 +11,8 @@ import torch
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfmoe_b200.so")
 
-QUANT = {"none": 0, "token_channel": 1, "block128": 2}
+QUANT = {"none": 0, "token_channel": 1, "block128": 2, "block128_ue8m0": 3}
+PARTIAL = {"f32": 0, "bf16": 1}
 
 
 class FmoeError(RuntimeError):
@@ -24,7 +25,13 @@ class _Traits(ctypes.Structure):
     _fields_ = [("quant", ctypes.c_int32), ("weight_dtype", ctypes.c_int32),
                 ("activation", ctypes.c_int32), ("gate_only", ctypes.c_int32),
                 ("block_m", ctypes.c_int32), ("gemm_mode", ctypes.c_int32), ("weight_layout", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 1)]
+                ("partial_dtype", ctypes.c_int32)]
+
+
+class _RunInfo(ctypes.Structure):
+    _fields_ = [("gemm1_kernel", ctypes.c_int32), ("gemm2_kernel", ctypes.c_int32),
+                ("sort_launches", ctypes.c_int32), ("quant_y_launch", ctypes.c_int32),
+                ("launches", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
 
 
 class _Args(ctypes.Structure):
@@ -77,7 +84,9 @@ def lib() -> ctypes.CDLL:
                                ctypes.POINTER(ctypes.c_float)]
         l.fmoe_run_static_ws.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.c_void_p]
         l.fmoe_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
-        l.fmoe_launches_per_run.argtypes = [ctypes.POINTER(_Traits)]
+        l.fmoe_describe_run.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.POINTER(_RunInfo)]
+        l.fmoe_gemm_kernel_name.argtypes = [ctypes.c_int32]
+        l.fmoe_gemm_kernel_name.restype = ctypes.c_char_p
         l.fmoe_profile_create.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]
         l.fmoe_run_profiled.argtypes = [ctypes.POINTER(_Traits), ctypes.POINTER(_Args), ctypes.c_void_p,
                                         ctypes.c_void_p]
@@ -111,12 +120,13 @@ class FusedMoeTraits:
     prec_i: str = "bf16"
     prec_w: str = "bf16"          # "bf16" | "fp8"
     prec_o: str = "bf16"
-    quant: str = "none"           # "none" | "token_channel" | "block128"
+    quant: str = "none"           # "none" | "token_channel" | "block128" | "block128_ue8m0"
     activation: str = "silu"
     gate_only: int = 0
     block_m: int = 128
     gemm_mode: int = 0            # 0 = per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel
     weight_layout: str = "row_major"   # or "tiled128" (see therock_b200.weights.tile_weights)
+    partial_dtype: str = "f32"    # "f32" | "bf16": how the K weighted expert outputs are held before the ordered sum
 
     def to_c(self) -> _Traits:
         if self.prec_i != "bf16" or self.prec_o != "bf16":
@@ -137,6 +147,9 @@ class FusedMoeTraits:
         if self.weight_layout not in ("row_major", "tiled128"):
             raise FmoeError(-1, f"unknown weight layout {self.weight_layout!r}")
         t.weight_layout = 0 if self.weight_layout == "row_major" else 1
+        if self.partial_dtype not in PARTIAL:
+            raise FmoeError(-1, f"unknown partial dtype {self.partial_dtype!r}")
+        t.partial_dtype = PARTIAL[self.partial_dtype]
         return t
 
 
@@ -190,9 +203,19 @@ def sort_capacity(T: int, K: int, E: int, block_m: int = 128) -> int:
     return int(lib().fmoe_sort_capacity(T, K, E, block_m))
 
 
-def launches_per_run(traits: FusedMoeTraits) -> int:
-    t = traits.to_c()
-    return int(lib().fmoe_launches_per_run(ctypes.byref(t)))
+def describe_run(traits: FusedMoeTraits, args: FusedMoeArgs) -> dict:
+    """What fmoe_run will launch for these traits and dimensions on the current device: the
+    kernel flavour of each GEMM (name as compiled) and the number of kernels per run."""
+    t, a, info = traits.to_c(), args.to_c(bool(traits.gate_only)), _RunInfo()
+    _check(lib().fmoe_describe_run(ctypes.byref(t), ctypes.byref(a), ctypes.byref(info)))
+    d = {n: int(getattr(info, n)) for n, _ in _RunInfo._fields_ if n != "reserved"}
+    d["gemm1_kernel_name"] = lib().fmoe_gemm_kernel_name(info.gemm1_kernel).decode()
+    d["gemm2_kernel_name"] = lib().fmoe_gemm_kernel_name(info.gemm2_kernel).decode()
+    return d
+
+
+def launches_per_run(traits: FusedMoeTraits, args: FusedMoeArgs) -> int:
+    return describe_run(traits, args)["launches"]
 
 
 def workspace_layout(traits: FusedMoeTraits, args: FusedMoeArgs) -> dict:

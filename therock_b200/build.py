@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libfmoe_b200.so")
 SOURCES = ["sorting.cu", "rows.cu", "gemm.cu", "api.cu", "ep.cu", "router.cu"]
-HEADERS = ["ptx.cuh", "gemm.cuh", "internal.h", os.path.join("..", "..", "include", "fused_moe_c.h")]
+HEADERS = ["ptx.cuh", "gemm.cuh", "gemm_block.cuh", "scales.cuh", "plan.hpp", "internal.h", os.path.join("..", "..", "include", "fused_moe_c.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

@@ -2,8 +2,8 @@
 // sequence of the fused-MoE operator.  No device memory is allocated here; every buffer
 // belongs to the caller.
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
-#include <cstdarg>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -11,105 +11,61 @@
 #include "../../include/fused_moe_c.h"
 #include "gemm.cuh"
 #include "internal.h"
+#include "plan.hpp"
 
 namespace {
 
-thread_local char g_err[512] = "";
+using fmoe::fail;
+using fmoe::Plan;
+using fmoe::make_plan;
+using fmoe::validate_dims;
+using fmoe::validate_traits;
 
-int fail(int code, const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-  return code;
-}
+// Makes the device that owns `ptr` current for the lifetime of the object and puts the
+// caller's device back afterwards: the entry points leave no trace in the calling thread.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(const void* ptr) {
+    cudaPointerAttributes attr;
+    if (ptr == nullptr || cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+      cudaGetLastError();   // not fatal: stay on the calling thread's device
+      return;
+    }
+    if (attr.type != cudaMemoryTypeDevice) return;
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur == attr.device) return;
+    if (cudaSetDevice(attr.device) != cudaSuccess) {
+      rc_ = fail(FMOE_ERR_CUDA, "cudaSetDevice(%d) failed", attr.device);
+      return;
+    }
+    prev_ = cur;
+  }
+  ~DeviceGuard() {
+    if (prev_ >= 0) cudaSetDevice(prev_);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+  int rc() const { return rc_; }
 
-inline uint64_t align256(uint64_t v) { return (v + 255) & ~static_cast<uint64_t>(255); }
-
-struct Plan {
-  int64_t cap = 0;
-  fmoe_ws_layout_c l{};
+ private:
+  int prev_ = -1;
+  int rc_ = FMOE_OK;
 };
 
-int validate_traits(const fmoe_traits_c* t) {
-  if (!t) return fail(FMOE_ERR_INVALID_ARG, "traits is null");
-  if (t->quant < FMOE_QUANT_NONE || t->quant > FMOE_QUANT_BLOCK128)
-    return fail(FMOE_ERR_INVALID_ARG, "unknown quant mode %d", t->quant);
-  const int want = t->quant == FMOE_QUANT_NONE ? FMOE_BF16 : FMOE_FP8_E4M3;
-  if (t->weight_dtype != want)
-    return fail(FMOE_ERR_INVALID_ARG, "weight_dtype %d does not match quant mode %d", t->weight_dtype, t->quant);
-  if (t->activation != FMOE_ACT_SILU) return fail(FMOE_ERR_UNSUPPORTED, "only SiLU activation is built");
-  if (t->gate_only != 0 && t->gate_only != 1) return fail(FMOE_ERR_INVALID_ARG, "gate_only must be 0 or 1");
-  if (t->gate_only && t->quant == FMOE_QUANT_BLOCK128)
-    return fail(FMOE_ERR_UNSUPPORTED, "gate_only with block128 scales is not built");
-  if (t->block_m != fmoe::kBlockM) return fail(FMOE_ERR_UNSUPPORTED, "block_m must be %d", fmoe::kBlockM);
-  if (t->gemm_mode < 0 || t->gemm_mode > 2) return fail(FMOE_ERR_INVALID_ARG, "gemm_mode must be 0, 1 or 2");
-  if (t->weight_layout != FMOE_WEIGHTS_ROW_MAJOR && t->weight_layout != FMOE_WEIGHTS_TILED128)
-    return fail(FMOE_ERR_INVALID_ARG, "unknown weight layout %d", t->weight_layout);
-  return FMOE_OK;
-}
-
-int validate_dims(const fmoe_traits_c* t, const fmoe_args_c* a) {
-  if (!a) return fail(FMOE_ERR_INVALID_ARG, "args is null");
-  if (a->T < 0 || a->H <= 0 || a->I <= 0 || a->E <= 0 || a->K <= 0)
-    return fail(FMOE_ERR_INVALID_ARG, "dimensions must be positive (T=%d H=%d I=%d E=%d K=%d)", a->T, a->H, a->I, a->E, a->K);
-  if (a->K > a->E) return fail(FMOE_ERR_INVALID_ARG, "topk %d exceeds experts %d", a->K, a->E);
-  if (a->E > 1024) return fail(FMOE_ERR_UNSUPPORTED, "at most 1024 experts");
-  if (a->I % fmoe::kSlabRows) return fail(FMOE_ERR_UNSUPPORTED, "intermediate size must be a multiple of %d", fmoe::kSlabRows);
-  if (t->gate_only && a->I % fmoe::kTileN)
-    return fail(FMOE_ERR_UNSUPPORTED, "gate_only needs an intermediate size that is a multiple of %d", fmoe::kTileN);
-  if (a->H % fmoe::kTileN) return fail(FMOE_ERR_UNSUPPORTED, "hidden size must be a multiple of %d", fmoe::kTileN);
-  if (static_cast<int64_t>(a->T) * a->K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
-  if (t->weight_layout == FMOE_WEIGHTS_TILED128) {
-    const int es = t->quant == FMOE_QUANT_NONE ? 2 : 1;
-    if ((a->H * es) % 128 || (a->I * es) % 128)
-      return fail(FMOE_ERR_UNSUPPORTED, "tiled weights need K extents that are multiples of 128 bytes");
+// A pair of timing events that is destroyed on every exit path.
+struct EventPair {
+  cudaEvent_t a = nullptr, b = nullptr;
+  ~EventPair() {
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
   }
-  if (t->quant == FMOE_QUANT_BLOCK128 && (a->H % 128 || a->I % 128))
-    return fail(FMOE_ERR_UNSUPPORTED, "block128 needs hidden and intermediate sizes that are multiples of 128");
-  return FMOE_OK;
-}
+};
 
-int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
-  const int64_t cap = fmoe_sort_capacity(a->T, a->K, a->E, t->block_m);
-  const bool fp8 = t->quant != FMOE_QUANT_NONE;
-  p->cap = cap;
-  uint64_t off = 0;
-  auto take = [&off](uint64_t bytes) { uint64_t o = off; off = align256(off + bytes); return o; };
-  fmoe_ws_layout_c& l = p->l;
-  l.capacity = cap;
-  l.meta = take(64 * sizeof(int32_t));
-  l.sorted_token_ids = take(cap * 4);
-  l.sorted_weights = take(cap * 4);
-  l.sorted_rows = take(cap * 4);
-  l.sorted_expert_ids = take(cap / t->block_m * 4);
-  l.mblk_cum = take((a->E + 1) * 4);
-  l.a_sorted = take(static_cast<uint64_t>(cap) * a->H * (fp8 ? 1 : 2));
-  const bool blk = t->quant == FMOE_QUANT_BLOCK128;
-  l.a_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 * (blk ? a->H / 128 : 1) : 0);
-  l.y = take(static_cast<uint64_t>(cap) * a->I * 2);
-  l.y_quant = take(fp8 ? static_cast<uint64_t>(cap) * a->I : 0);
-  l.y_scale = take(fp8 ? static_cast<uint64_t>(cap) * 4 * (blk ? a->I / 128 : 1) : 0);
-  l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * 4);
-  l.sort_scratch = take(fmoe::sort_scratch_words(a->E) * 4);
-  l.total_bytes = off;
-  return FMOE_OK;
-}
-
-int set_device_for(const void* ptr) {
-  cudaPointerAttributes attr;
-  if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
-    cudaGetLastError();
-    return FMOE_OK;   // not fatal: keep the calling thread's device
-  }
-  if (attr.type == cudaMemoryTypeDevice) {
-    int cur = -1;
-    cudaGetDevice(&cur);
-    if (cur != attr.device && cudaSetDevice(attr.device) != cudaSuccess)
-      return fail(FMOE_ERR_CUDA, "cudaSetDevice(%d) failed", attr.device);
-  }
-  return FMOE_OK;
-}
+// NVTX range around one stage of the operator (a no-op unless a profiler is attached).
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 
 #define FMOE_CUDA(expr)                                                                    \
   do {                                                                                     \
@@ -124,12 +80,10 @@ extern "C" {
 
 int fmoe_version(void) { return 100; }
 
-const char* fmoe_last_error(void) { return g_err; }
+const char* fmoe_last_error(void) { return fmoe::last_error_buf(); }
 
 int64_t fmoe_sort_capacity(int32_t T, int32_t K, int32_t E, int32_t block_m) {
-  if (block_m <= 0) return 0;
-  const int64_t c = static_cast<int64_t>(T) * K + static_cast<int64_t>(E) * (block_m - 1);
-  return (c + block_m - 1) / block_m * block_m;
+  return fmoe::sort_capacity(T, K, E, block_m);
 }
 
 int fmoe_sort(const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t E,
@@ -140,8 +94,9 @@ int fmoe_sort(const int32_t* topk_ids, const float* topk_weight, int32_t T, int3
   if (T < 0 || K <= 0 || E <= 0 || block_m <= 0) return fail(FMOE_ERR_INVALID_ARG, "bad dimensions");
   if (E > 1024) return fail(FMOE_ERR_UNSUPPORTED, "at most 1024 experts");
   if (static_cast<int64_t>(T) * K > (1 << 24)) return fail(FMOE_ERR_UNSUPPORTED, "T*K too large");
-  int rc = set_device_for(topk_ids);
-  if (rc != FMOE_OK) return rc;
+  DeviceGuard guard(topk_ids);
+  if (guard.rc() != FMOE_OK) return guard.rc();
+  NvtxRange range("fmoe_sort");
   FMOE_CUDA(fmoe::launch_moe_sorting(topk_ids, topk_weight, T, K, E, block_m,
                                      fmoe_sort_capacity(T, K, E, block_m), sorted_token_ids,
                                      sorted_weights, nullptr, sorted_expert_ids, num_tokens_post_pad,
@@ -170,10 +125,25 @@ int fmoe_get_workspace_size(const fmoe_traits_c* traits, const fmoe_args_c* args
   return FMOE_OK;
 }
 
-int fmoe_launches_per_run(const fmoe_traits_c* traits) {
-  if (validate_traits(traits) != FMOE_OK) return FMOE_ERR_INVALID_ARG;
-  // sort, gather(+quant), gemm1, [quant of the intermediate], gemm2, combine
-  return traits->quant == FMOE_QUANT_NONE ? 5 : 6;
+int fmoe_describe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, fmoe_run_info_c* info) {
+  int rc = validate_traits(traits);
+  if (rc == FMOE_OK) rc = validate_dims(traits, args);
+  if (rc != FMOE_OK) return rc;
+  if (!info) return fail(FMOE_ERR_INVALID_ARG, "info is null");
+  *info = fmoe_run_info_c{};
+  const int forced = traits->gemm_mode ? traits->gemm_mode : fmoe::gemm_mode_override();
+  return fmoe::describe_run(traits, args, fmoe::device_sm_count(), forced, info);
+}
+
+const char* fmoe_gemm_kernel_name(int32_t kernel) {
+  switch (kernel) {
+    case FMOE_KERNEL_SINGLE: return "fmoe_grouped_gemm_kernel";
+    case FMOE_KERNEL_PAIR: return "fmoe_grouped_gemm_pair_kernel";
+    case FMOE_KERNEL_BLOCK_PROMOTE: return "fmoe_grouped_gemm_block_kernel<promote>";
+    case FMOE_KERNEL_BLOCK_HW_SCALE: return "fmoe_grouped_gemm_block_kernel<block_scale MMA>";
+    case FMOE_KERNEL_SINGLE_DECODE: return "fmoe_grouped_gemm_kernel<32 activation rows>";
+    default: return "";
+  }
 }
 
 // Stage boundaries at which run_impl records an event when given an event array:
@@ -195,7 +165,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   }
   if (!a.x || !a.w1 || !a.w2 || !a.topk_ids || !a.topk_weight || !a.out)
     return fail(FMOE_ERR_INVALID_ARG, "x, w1, w2, topk_ids, topk_weight and out are required");
-  const bool fp8 = traits->quant != FMOE_QUANT_NONE;
+  const bool fp8 = fmoe::quant_is_fp8(traits->quant);
   if (fp8 && (!a.w1_scale || !a.w2_scale)) return fail(FMOE_ERR_INVALID_ARG, "fp8 variants need w1_scale and w2_scale");
   Plan plan;
   make_plan(traits, args, &plan);
@@ -205,8 +175,9 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
                 (unsigned long long)plan.l.total_bytes);
   if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return fail(FMOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
 
-  rc = set_device_for(a.x);
-  if (rc != FMOE_OK) return rc;
+  DeviceGuard guard(a.x);
+  if (guard.rc() != FMOE_OK) return guard.rc();
+  NvtxRange whole("fmoe_run");
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
@@ -220,113 +191,115 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   int32_t* expert_ids = reinterpret_cast<int32_t*>(ws + l.sorted_expert_ids);
   int32_t* mblk_cum = reinterpret_cast<int32_t*>(ws + l.mblk_cum);
   void* a_sorted = ws + l.a_sorted;
-  float* a_scale = fp8 ? reinterpret_cast<float*>(ws + l.a_scale) : nullptr;
+  void* a_scale = fp8 ? ws + l.a_scale : nullptr;
   void* y = ws + l.y;
   void* yq = ws + l.y_quant;
-  float* y_scale = fp8 ? reinterpret_cast<float*>(ws + l.y_scale) : nullptr;
-  float* slots = reinterpret_cast<float*>(ws + l.slots);
+  void* y_scale = fp8 ? ws + l.y_scale : nullptr;
+  void* slots = ws + l.slots;
 
 #define FMOE_STAGE(i) do { if (stage_ev) FMOE_CUDA(cudaEventRecord(stage_ev[i], stream)); } while (0)
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  EventPair ev;
   FMOE_STAGE(0);
   if (ms_out) {
-    FMOE_CUDA(cudaEventCreate(&ev0));
-    FMOE_CUDA(cudaEventCreate(&ev1));
-    FMOE_CUDA(cudaEventRecord(ev0, stream));
+    FMOE_CUDA(cudaEventCreate(&ev.a));
+    FMOE_CUDA(cudaEventCreate(&ev.b));
+    FMOE_CUDA(cudaEventRecord(ev.a, stream));
   }
 
-  FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
-                                     sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
-                                     mblk_cum, status, stream, a.num_tokens_dev, 1, nullptr,
-                                     reinterpret_cast<int32_t*>(ws + l.sort_scratch)));
+  {
+    NvtxRange r("moe_sorting");
+    FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
+                                       sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
+                                       mblk_cum, status, stream, a.num_tokens_dev, 1, nullptr,
+                                       reinterpret_cast<int32_t*>(ws + l.sort_scratch)));
+  }
   FMOE_STAGE(1);
-  const bool blk = traits->quant == FMOE_QUANT_BLOCK128;
-  const int qmode = !fp8 ? 0 : (blk ? 2 : 1);
-  FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
-                                     a_sorted, a_scale, stream));
+  const bool blk = fmoe::quant_is_block(traits->quant);
+  const bool hw = traits->quant == FMOE_QUANT_BLOCK128_UE8M0;
+  const int qmode = !fp8 ? 0 : (hw ? 3 : (blk ? 2 : 1));
+  {
+    NvtxRange r("gather_quant");
+    FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
+                                       a_sorted, a_scale, stream));
+  }
   FMOE_STAGE(2);
 
   fmoe::GemmLaunch g{};
   int drv = 0;
   g.fp8 = fp8;
   g.b_tiled = traits->weight_layout == FMOE_WEIGHTS_TILED128;
-  g.block_scale = blk;
   g.num_experts = a.E;
   g.mblk_cum = mblk_cum;
   g.sorted_rows = sorted_rows;
   g.sorted_weights = sorted_w;
   g.status = status;
   g.max_m_blocks = static_cast<int>(plan.cap / fmoe::kBlockM);
-  // no expert can receive more rows than there are routed pairs: lets decode-sized batches
-  // stage only the rows that can be real
-  g.max_live_rows = static_cast<long long>(a.T) * a.K <= fmoe::kBlockM ? a.T * a.K : 0;
-  // Kernel flavour per GEMM.  The CTA-pair kernel moves a third less of the operands per flop
-  // (about 5 % faster per tile) but pads every expert to an even number of row blocks and
-  // has half as many schedulable units, so whether it wins is a question of wave counts:
-  // estimate the persistent waves of both flavours from the expected number of routed rows.
-  const int forced_mode = traits->gemm_mode ? traits->gemm_mode : fmoe::gemm_mode_from_env();
-  const long long exp_rows = static_cast<long long>(a.expected_tokens > 0 ? a.expected_tokens : a.T) * a.K;
+  const int forced_mode = traits->gemm_mode ? traits->gemm_mode : fmoe::gemm_mode_override();
   const int sms = fmoe::device_sm_count();
-  auto pick_mode = [&](int n_blocks) {
-    if (forced_mode) return forced_mode;
-    // expected row blocks: full blocks plus half a block of padding per expert that is hit
-    const long long hit = exp_rows < a.E ? exp_rows : a.E;
-    long long m_blocks = (exp_rows + 64 * hit + 127) / 128;
-    if (m_blocks < hit) m_blocks = hit;                             // at least one block per expert hit
-    const long long pairs = (m_blocks + hit / 2 + 1) / 2;          // odd experts waste half a pair
-    const long long waves_single = (m_blocks * n_blocks + sms - 1) / sms;
-    const long long waves_pair = (pairs * n_blocks + sms / 2 - 1) / (sms / 2);
-    return (waves_pair * 95 < waves_single * 100) ? 2 : 1;
-  };
+  const bool fused_quant = blk && fmoe::kFusedBlockQuant;
   // gemm1: [cap, H] x W1[E, 2I, H]^T -> SiLU(gate) * up -> y [cap, I]
   if (traits->gate_only) {
     // W1 is [E, I, H]: a tile is 256 consecutive gate rows, y = SiLU(gate)
-    g.mode = pick_mode(a.I / fmoe::kTileN);
     g.epilogue = fmoe::kEpiSilu;
     g.b_rows_per_expert = a.I;
     g.n_blocks = a.I / fmoe::kTileN; g.n_stride = fmoe::kTileN; g.second_slab_offset = fmoe::kSlabRows;
   } else {
-    g.mode = pick_mode(a.I / fmoe::kSlabRows);
     g.epilogue = fmoe::kEpiSiluMul;
     g.b_rows_per_expert = 2 * a.I;
     g.n_blocks = a.I / fmoe::kSlabRows; g.n_stride = fmoe::kSlabRows; g.second_slab_offset = a.I;
   }
+  g.flavour = fmoe::pick_gemm_flavour(traits, args, g.n_blocks, sms, forced_mode);
   g.a = a_sorted; g.a_rows = plan.cap; g.b = a.w1; g.k_elems = a.H;
   g.a_scale = a_scale; g.b_scale = fp8 ? a.w1_scale : nullptr;
-  g.out = y; g.ld_out = a.I;
-  if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
-    return fail(FMOE_ERR_CUDA, "gemm1 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+  g.out = fused_quant ? yq : y; g.ld_out = a.I;
+  g.out_rows = plan.cap;
+  g.out_scale = fused_quant ? y_scale : nullptr;
+  {
+    NvtxRange r("gemm1_silu_mul");
+    if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
+      return fail(FMOE_ERR_CUDA, "gemm1 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+  }
   FMOE_STAGE(3);
 
   const void* a2 = y;
   if (fp8) {
-    FMOE_CUDA(fmoe::launch_gather_rows(y, static_cast<int>(plan.cap), a.I, nullptr, num_post_pad, plan.cap, qmode,
-                                       yq, y_scale, stream, sorted_rows));
+    if (!fused_quant) {
+      NvtxRange r("quant_intermediate");
+      FMOE_CUDA(fmoe::launch_gather_rows(y, static_cast<int>(plan.cap), a.I, nullptr, num_post_pad, plan.cap, qmode,
+                                         yq, y_scale, stream, sorted_rows));
+    }
     a2 = yq;
   }
   FMOE_STAGE(4);
   // gemm2: [cap, I] x W2[E, H, I]^T * topk_weight -> slots [T*K, H]
-  g.mode = pick_mode(a.H / fmoe::kTileN);
   g.epilogue = fmoe::kEpiScaledSlots;
   g.a = a2; g.b = a.w2; g.k_elems = a.I;
   g.b_rows_per_expert = a.H;
   g.n_blocks = a.H / fmoe::kTileN; g.n_stride = fmoe::kTileN; g.second_slab_offset = fmoe::kSlabRows;
+  g.flavour = fmoe::pick_gemm_flavour(traits, args, g.n_blocks, sms, forced_mode);
   g.a_scale = y_scale; g.b_scale = fp8 ? a.w2_scale : nullptr;
   g.out = slots; g.ld_out = a.H;
-  if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
-    return fail(FMOE_ERR_CUDA, "gemm2 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+  g.out_rows = static_cast<int64_t>(a.T) * a.K;
+  g.out_scale = nullptr;
+  g.out_bf16 = traits->partial_dtype == FMOE_PARTIAL_BF16;
+  {
+    NvtxRange r("gemm2_weighted");
+    if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
+      return fail(FMOE_ERR_CUDA, "gemm2 launch failed (cuda: %s, driver code %d)", cudaGetErrorString(cudaGetLastError()), drv);
+  }
   FMOE_STAGE(5);
 
-  FMOE_CUDA(fmoe::launch_combine(slots, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream, a.num_tokens_dev));
+  {
+    NvtxRange r("combine");
+    FMOE_CUDA(fmoe::launch_combine(slots, g.out_bf16, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream, a.num_tokens_dev));
+  }
   FMOE_STAGE(6);
 #undef FMOE_STAGE
 
   if (ms_out) {
-    FMOE_CUDA(cudaEventRecord(ev1, stream));
-    FMOE_CUDA(cudaEventSynchronize(ev1));
-    FMOE_CUDA(cudaEventElapsedTime(ms_out, ev0, ev1));
-    cudaEventDestroy(ev0);
-    cudaEventDestroy(ev1);
+    FMOE_CUDA(cudaEventRecord(ev.b, stream));
+    FMOE_CUDA(cudaEventSynchronize(ev.b));
+    FMOE_CUDA(cudaEventElapsedTime(ms_out, ev.a, ev.b));
     int32_t st = 0;
     FMOE_CUDA(cudaMemcpy(&st, status, sizeof(st), cudaMemcpyDeviceToHost));
     if (st != 0) return fail(FMOE_ERR_DEVICE_TIMEOUT, "device status word 0x%x: a bounded wait ran out", st);
@@ -350,7 +323,12 @@ int fmoe_profile_create(int32_t max_runs, void** handle) {
   if (!handle || max_runs <= 0) return fail(FMOE_ERR_INVALID_ARG, "handle and a positive run count are required");
   fmoe_profile* p = new fmoe_profile{max_runs, 0, new cudaEvent_t[static_cast<size_t>(max_runs) * kStageEvents]};
   for (int i = 0; i < max_runs * kStageEvents; ++i) {
-    if (cudaEventCreate(&p->ev[i]) != cudaSuccess) return fail(FMOE_ERR_CUDA, "cudaEventCreate failed");
+    if (cudaEventCreate(&p->ev[i]) != cudaSuccess) {
+      for (int j = 0; j < i; ++j) cudaEventDestroy(p->ev[j]);
+      delete[] p->ev;
+      delete p;
+      return fail(FMOE_ERR_CUDA, "cudaEventCreate failed");
+    }
   }
   *handle = p;
   return FMOE_OK;
@@ -420,10 +398,8 @@ int fmoe_run_static_ws(const fmoe_traits_c* traits, const fmoe_args_c* args, voi
                 "this call needs %llu bytes of scratch but the built-in workspace holds %llu; "
                 "use fmoe_run with a caller-provided workspace",
                 (unsigned long long)plan.l.total_bytes, (unsigned long long)FMOE_STATIC_WS_BYTES);
-  if (args->T > 0 && args->x) {
-    rc = set_device_for(args->x);
-    if (rc != FMOE_OK) return rc;
-  }
+  DeviceGuard guard(args->T > 0 ? args->x : nullptr);
+  if (guard.rc() != FMOE_OK) return guard.rc();
   int dev = 0;
   FMOE_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kStaticWsMaxDevices) return fail(FMOE_ERR_UNSUPPORTED, "device index %d out of range", dev);
@@ -456,8 +432,8 @@ int fmoe_gather_rows(const void* src, int32_t n_src, int32_t cols, const int32_t
   if (!src || !row_ids || !dst || !n_rows_dev) return fail(FMOE_ERR_INVALID_ARG, "src, row_ids, n_rows_dev and dst are required");
   if (cols <= 0 || cols % 8) return fail(FMOE_ERR_UNSUPPORTED, "cols must be a positive multiple of 8");
   if (n_rows <= 0) return FMOE_OK;
-  int rc = set_device_for(src);
-  if (rc != FMOE_OK) return rc;
+  DeviceGuard guard(src);
+  if (guard.rc() != FMOE_OK) return guard.rc();
   FMOE_CUDA(fmoe::launch_gather_rows(src, n_src, cols, row_ids, n_rows_dev, n_rows, 0, dst, nullptr,
                                      static_cast<cudaStream_t>(stream)));
   return FMOE_OK;
@@ -468,8 +444,8 @@ int fmoe_combine_rows(const void* rows, const int32_t* index, int32_t T, int32_t
   if (!rows || !index || !out) return fail(FMOE_ERR_INVALID_ARG, "rows, index and out are required");
   if (H <= 0 || H % 8) return fail(FMOE_ERR_UNSUPPORTED, "H must be a positive multiple of 8");
   if (T <= 0) return FMOE_OK;
-  int rc = set_device_for(rows);
-  if (rc != FMOE_OK) return rc;
+  DeviceGuard guard(rows);
+  if (guard.rc() != FMOE_OK) return guard.rc();
   FMOE_CUDA(fmoe::launch_combine_rows(rows, index, T, K, H, out, static_cast<cudaStream_t>(stream)));
   return FMOE_OK;
 }

@@ -15,6 +15,7 @@
 
 #include "../../include/fused_moe_c.h"
 #include "internal.h"
+#include "plan.hpp"
 
 namespace fmoe {
 namespace {
@@ -112,37 +113,47 @@ ep_return_kernel(const uint4* __restrict__ out_rows, int H, const int32_t* __res
 }
 
 }  // namespace
+
+static int launch_status(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FMOE_OK : fail(FMOE_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+}
 }  // namespace fmoe
 
 extern "C" {
 
 int fmoe_ep_plan(const int32_t* topk_ids, int32_t T, int32_t K, int32_t experts_per_rank, int32_t G,
                  int32_t* order, int32_t* inv_index, int32_t* cum, int32_t* scratch_tokens, void* stream) {
-  if (!topk_ids || !order || !inv_index || !cum || !scratch_tokens) return FMOE_ERR_INVALID_ARG;
-  if (T <= 0 || K <= 0 || experts_per_rank <= 0 || G <= 0 || G > fmoe::kMaxRanks) return FMOE_ERR_INVALID_ARG;
+  if (!topk_ids || !order || !inv_index || !cum || !scratch_tokens)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_plan: topk_ids, order, inv_index, cum and scratch_tokens are required");
+  if (T <= 0 || K <= 0 || experts_per_rank <= 0 || G <= 0 || G > fmoe::kMaxRanks)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_plan: bad dimensions (T=%d K=%d experts_per_rank=%d G=%d)", T, K,
+                      experts_per_rank, G);
   // block size 1: no padding, so the cumulative block counts are the cumulative row counts
   cudaError_t e = fmoe::launch_moe_sorting(topk_ids, nullptr, T, K, G, 1, static_cast<int64_t>(T) * K,
                                            scratch_tokens, nullptr, order, nullptr, nullptr, cum, nullptr,
                                            static_cast<cudaStream_t>(stream), nullptr, experts_per_rank,
                                            inv_index);
-  return e == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
+  return e == cudaSuccess ? FMOE_OK : fmoe::fail(FMOE_ERR_CUDA, "fmoe_ep_plan: %s", cudaGetErrorString(e));
 }
 
 int fmoe_ep_publish(const int32_t* cum, const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
                     int32_t G, void* stream) {
-  if (!cum || !peer_base || !lay || G <= 0 || G > fmoe::kMaxRanks) return FMOE_ERR_INVALID_ARG;
+  if (!cum || !peer_base || !lay || G <= 0 || G > fmoe::kMaxRanks || me < 0 || me >= G)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_publish: null pointer or rank %d / world %d out of range", me, G);
   fmoe::ep_publish_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(cum, peer_base, lay->matrix, me, G);
-  return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
+  return fmoe::launch_status("expert-parallel kernel");
 }
 
 int fmoe_ep_barrier(const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
                     int32_t epoch, int32_t* epoch_counter, int32_t* status, int32_t timeout_ms, void* stream) {
-  if (!peer_base || !lay || !status || G <= 0 || G > fmoe::kMaxRanks || timeout_ms < 0) return FMOE_ERR_INVALID_ARG;
+  if (!peer_base || !lay || !status || G <= 0 || G > fmoe::kMaxRanks || me < 0 || me >= G || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_barrier: null pointer, negative timeout, or rank %d / world %d out of range", me, G);
   // clock64 ticks at the SM clock (<= ~2 GHz): 2e6 cycles per millisecond is an upper bound
   const long long limit = timeout_ms > 0 ? 2000000LL * timeout_ms : 8000000000LL;   // default: about four seconds
   fmoe::ep_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(peer_base, lay->flags, me, G, epoch,
                                                                           epoch_counter, status, limit);
-  return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
+  return fmoe::launch_status("expert-parallel kernel");
 }
 
 int fmoe_ep_dispatch(const void* x, const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
@@ -150,22 +161,26 @@ int fmoe_ep_dispatch(const void* x, const int32_t* topk_ids, const float* topk_w
                      const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
                      int32_t* n_recv_dev, void* stream) {
   if (!x || !topk_ids || !topk_weight || !order || !cum || !peer_base || !lay || !n_recv_dev)
-    return FMOE_ERR_INVALID_ARG;
-  if (H <= 0 || H % 8 || T <= 0 || K <= 0) return FMOE_ERR_UNSUPPORTED;
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_dispatch: a required pointer is null");
+  if (G <= 0 || G > fmoe::kMaxRanks || me < 0 || me >= G)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_dispatch: rank %d / world %d out of range", me, G);
+  if (H <= 0 || H % 8 || T <= 0 || K <= 0)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_dispatch: H must be a positive multiple of 8 and T, K positive");
   fmoe::ep_dispatch_kernel<<<T * K, fmoe::kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(x), topk_ids, topk_weight, K, H, experts_per_rank, order, cum, peer_base,
       *lay, me, G, n_recv_dev);
-  return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
+  return fmoe::launch_status("expert-parallel kernel");
 }
 
 int fmoe_ep_return(const void* out_rows, int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base,
                    const fmoe_ep_layout_c* lay, int32_t me, int32_t G, void* stream) {
-  if (!out_rows || !n_recv_dev || !peer_base || !lay || G <= 0 || G > fmoe::kMaxRanks) return FMOE_ERR_INVALID_ARG;
+  if (!out_rows || !n_recv_dev || !peer_base || !lay || G <= 0 || G > fmoe::kMaxRanks || me < 0 || me >= G)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_return: null pointer or rank %d / world %d out of range", me, G);
   if (lay->recv_cap <= 0) return FMOE_OK;
   fmoe::ep_return_kernel<<<static_cast<unsigned>(lay->recv_cap), fmoe::kEpThreads, 0,
                            static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint4*>(out_rows), H,
                                                                  n_recv_dev, peer_base, *lay, me, G);
-  return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
+  return fmoe::launch_status("expert-parallel kernel");
 }
 
 }  // extern "C"

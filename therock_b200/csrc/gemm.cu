@@ -5,7 +5,8 @@
 #include <cstring>
 #include <mutex>
 
-#include "gemm.cuh"
+#include "../../include/fused_moe_c.h"
+#include "gemm_block.cuh"
 #include "internal.h"
 
 namespace fmoe {
@@ -99,15 +100,19 @@ cudaError_t launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, co
 
 }  // namespace
 
-// FMOE_GEMM_MODE=1cta / 2cta forces one kernel flavour for every GEMM (used to compare them);
-// unset, the caller's per-GEMM choice stands.  Returns 0 (no override), 1 or 2.
-int gemm_mode_from_env() {
+// A library built with -DFMOE_TIMING_SWITCHES honours FMOE_GEMM_MODE=1cta / 2cta, which forces one
+// kernel flavour for every GEMM (used to compare them); the product build ignores the variable.
+int gemm_mode_override() {
+#ifdef FMOE_TIMING_SWITCHES
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("FMOE_GEMM_MODE");
     mode = !e ? 0 : (std::strcmp(e, "1cta") == 0 ? 1 : (std::strcmp(e, "2cta") == 0 ? 2 : 0));
   }
   return mode;
+#else
+  return 0;
+#endif
 }
 
 int device_sm_count() { return sm_count(); }
@@ -121,10 +126,27 @@ bool pdl_enabled() {
   return on == 1;
 }
 
+template <int kEpi, bool kHw>
+cudaError_t launch_block_variant(const CUtensorMap& ta, const CUtensorMap& tb, const BlockGemmParams& bp, int grid,
+                                 cudaStream_t stream) {
+  static bool configured[kMaxDevices] = {false};
+  const int dev = current_device();
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpi, kHw>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kBlockSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpi, kHw>, dim3(grid), dim3(kBlockGemmThreads), kBlockSmemBytes,
+                    stream, ta, tb, bp);
+}
+
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
   CUtensorMap ta, tb;
+  const bool block = g.flavour == FMOE_KERNEL_BLOCK_PROMOTE || g.flavour == FMOE_KERNEL_BLOCK_HW_SCALE;
+  const bool pair = g.flavour == FMOE_KERNEL_PAIR;
   // decode-sized batches: only the first kDecodeARows rows of a block can be real
-  const bool few_rows = g.max_live_rows > 0 && g.max_live_rows <= kDecodeARows && !g.block_scale && g.mode != 2;
+  const bool few_rows = g.flavour == FMOE_KERNEL_SINGLE_DECODE;
   CUresult r = make_map(&ta, g.a, g.fp8, g.a_rows, g.k_elems, few_rows ? kDecodeARows : kSlabRows);
   const int esize = g.fp8 ? 1 : 2;
   const int k_blocks = (g.k_elems * esize + kStageKBytes - 1) / kStageKBytes;
@@ -139,31 +161,36 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     if (drv_err) *drv_err = static_cast<int>(r);
     return cudaErrorInvalidValue;
   }
-  GemmParams p;
+  GemmParams p{};
   p.mblk_cum = g.mblk_cum;
   p.num_experts = g.num_experts;
   p.n_blocks = g.n_blocks;
-  const int k_bytes = g.k_elems * (g.fp8 ? 1 : 2);
-  p.k_iters = (k_bytes + kStageKBytes - 1) / kStageKBytes;
+  p.k_iters = k_blocks;
   p.b_rows_per_expert = g.b_rows_per_expert;
   p.n_stride = g.n_stride;
   p.second_slab_offset = g.second_slab_offset;
   p.sorted_rows = g.sorted_rows;
   p.sorted_weights = g.sorted_weights;
-  p.a_scale = g.a_scale;
+  p.a_scale = static_cast<const float*>(g.a_scale);
   p.b_scale = g.b_scale;
   p.out = g.out;
   p.ld_out = g.ld_out;
+  p.out_bf16 = g.out_bf16 ? 1 : 0;
+  p.out_rows = g.out_rows;
   p.status = g.status;
   p.b_tiled_kb = g.b_tiled ? k_blocks : 0;
+#ifdef FMOE_TIMING_SWITCHES
   {
     static int dbg = -1;       // FMOE_DEBUG_FLAGS: timing experiments only
     if (dbg < 0) { const char* e = getenv("FMOE_DEBUG_FLAGS"); dbg = e ? atoi(e) : 0; }
     p.debug_flags = static_cast<uint32_t>(dbg);
   }
-  p.desc_template = g.desc_template_override ? g.desc_template_override : ptx::sw128_kmajor_desc_template();
-  p.idesc = g.idesc_override ? g.idesc_override : ptx::make_idesc(g.fp8 ? 0u : 1u, kBlockM, kTileN);
-  if (g.block_scale) {
+#endif
+  p.desc_template = ptx::sw128_kmajor_desc_template();
+  p.idesc = ptx::make_idesc(g.fp8 ? 0u : 1u, kBlockM, kTileN);
+  const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
+  const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
+  if (block) {
     BlockGemmParams bp;
     bp.g = p;
     bp.g.a_scale = nullptr;
@@ -171,45 +198,34 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     bp.a_scale = g.a_scale;
     bp.b_scale = g.b_scale;
     bp.k_blocks = p.k_iters;
-    const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
-    const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
-    static bool configured[kMaxDevices][2] = {{false}};
-    const int dev = current_device();
-    const int which = g.epilogue == kEpiSiluMul ? 0 : 1;
-    if (!configured[dev][which]) {
-      cudaError_t e = which == 0
-          ? cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiSiluMul>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBlockSmemBytes)
-          : cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpiScaledSlots>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBlockSmemBytes);
-      if (e != cudaSuccess) return e;
-      configured[dev][which] = true;
+    bp.out_scale = g.out_scale;
+    const bool hw = g.flavour == FMOE_KERNEL_BLOCK_HW_SCALE;
+    if (g.epilogue == kEpiSiluMul) {
+      if (g.out_scale == nullptr) return cudaErrorInvalidValue;   // the first GEMM always quantises its output
+      return hw ? launch_block_variant<kEpiSiluMul, true>(ta, tb, bp, grid, stream)
+                : launch_block_variant<kEpiSiluMul, false>(ta, tb, bp, grid, stream);
     }
-    if (which == 0)
-      return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpiSiluMul>, dim3(grid), dim3(kBlockGemmThreads),
-                        kBlockSmemBytes, stream, ta, tb, bp);
-    return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpiScaledSlots>, dim3(grid), dim3(kBlockGemmThreads),
-                      kBlockSmemBytes, stream, ta, tb, bp);
+    return hw ? launch_block_variant<kEpiScaledSlots, true>(ta, tb, bp, grid, stream)
+              : launch_block_variant<kEpiScaledSlots, false>(ta, tb, bp, grid, stream);
   }
-  const bool pair = g.mode == 2;
-#define FMOE_DISPATCH_EPI(LAUNCH, FP8, ...)                                                        \
-  (g.epilogue == kEpiSiluMul ? LAUNCH<FP8, kEpiSiluMul __VA_ARGS__>(ta, tb, p, grid, stream)       \
-   : g.epilogue == kEpiSilu  ? LAUNCH<FP8, kEpiSilu __VA_ARGS__>(ta, tb, p, grid, stream)          \
-                             : LAUNCH<FP8, kEpiScaledSlots __VA_ARGS__>(ta, tb, p, grid, stream))
+#define FMOE_DISPATCH_EPI(LAUNCH, FP8, GRID, ...)                                                  \
+  (g.epilogue == kEpiSiluMul ? LAUNCH<FP8, kEpiSiluMul __VA_ARGS__>(ta, tb, p, GRID, stream)       \
+   : g.epilogue == kEpiSilu  ? LAUNCH<FP8, kEpiSilu __VA_ARGS__>(ta, tb, p, GRID, stream)          \
+                             : LAUNCH<FP8, kEpiScaledSlots __VA_ARGS__>(ta, tb, p, GRID, stream))
   if (pair) {
-    if (!g.idesc_override) p.idesc = ptx::make_idesc(g.fp8 ? 0u : 1u, 2 * kBlockM, kTileN);
+    p.idesc = ptx::make_idesc(g.fp8 ? 0u : 1u, 2 * kBlockM, kTileN);
     // upper bound on pair tiles: every expert may add one half-empty pair
     const long long max_pairs = (static_cast<long long>(g.max_m_blocks) + g.num_experts + 1) / 2;
-    const long long max_tiles = max_pairs * g.n_blocks;
+    const long long max_ptiles = max_pairs * g.n_blocks;
     const int clusters = sm_count() / 2;
-    const int grid = 2 * static_cast<int>(max_tiles < clusters ? (max_tiles > 0 ? max_tiles : 1) : clusters);
-    return g.fp8 ? FMOE_DISPATCH_EPI(launch_pair_variant, true) : FMOE_DISPATCH_EPI(launch_pair_variant, false);
+    const int pgrid = 2 * static_cast<int>(max_ptiles < clusters ? (max_ptiles > 0 ? max_ptiles : 1) : clusters);
+    return g.fp8 ? FMOE_DISPATCH_EPI(launch_pair_variant, true, pgrid) : FMOE_DISPATCH_EPI(launch_pair_variant, false, pgrid);
   }
-  const long long max_tiles = static_cast<long long>(g.max_m_blocks) * g.n_blocks;
-  const int grid = static_cast<int>(max_tiles < sm_count() ? (max_tiles > 0 ? max_tiles : 1) : sm_count());
 #define FMOE_COMMA_DECODE , kDecodeARows
   if (few_rows)
-    return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, FMOE_COMMA_DECODE)
-                 : FMOE_DISPATCH_EPI(launch_variant, false, FMOE_COMMA_DECODE);
-  return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true) : FMOE_DISPATCH_EPI(launch_variant, false);
+    return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, grid, FMOE_COMMA_DECODE)
+                 : FMOE_DISPATCH_EPI(launch_variant, false, grid, FMOE_COMMA_DECODE);
+  return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, grid) : FMOE_DISPATCH_EPI(launch_variant, false, grid);
 #undef FMOE_COMMA_DECODE
 #undef FMOE_DISPATCH_EPI
 }

@@ -1,5 +1,6 @@
 // Expert-grouped GEMMs for the fused-MoE operator on sm_100a: the single-CTA kernel described
-// here, a CTA-pair variant (cta_group::2) and a block-scaled fp8 variant further down.
+// here and a CTA-pair variant (cta_group::2) further down; the block-scaled fp8 kernels are in
+// gemm_block.cuh.
 //
 // One persistent CTA per SM walks a list of (expert, n-block, m-block) tiles.  Every tile
 // is D[128 x 256] = A[128 x K] * B[256 x K]^T with
@@ -52,19 +53,40 @@ struct GemmParams {
   const float* sorted_weights;  // [cap]
   const float* a_scale;         // [cap] per-sorted-row activation scale, or nullptr
   const float* b_scale;         // [E * b_rows_per_expert] per-output-channel scale, or nullptr
-  void* out;                    // kEpiSiluMul: bf16 [cap, ld_out]; kEpiScaledSlots: f32 [T*K, ld_out]
+  void* out;                    // kEpiSiluMul: bf16 [cap, ld_out]; kEpiScaledSlots: f32 or bf16 [T*K, ld_out]
   int ld_out;                   // elements per output row
+  int out_bf16;                 // kEpiScaledSlots: 1 = weighted rows are rounded to bf16
+  int64_t out_rows;             // rows of `out` (bound for the checked build)
   int* status;                  // device status word
   uint64_t desc_template;       // shared-memory matrix descriptor without the address
   uint32_t idesc;               // tcgen05 instruction descriptor
   int b_tiled_kb;               // 0: B is row-major; > 0: B is stored as contiguous 128 x 128-byte
                                 // tiles and this is the number of 128-byte K blocks per row
-  uint32_t debug_flags;         // diagnostics only (results are invalid when set): bit 0 = the
+#ifdef FMOE_TIMING_SWITCHES
+  uint32_t debug_flags;         // timing experiments only (results are invalid when set): bit 0 = the
                                 // epilogue skips its work (block-scaled kernel: no promotion
                                 // FMAs), bit 1 = no MMA is issued; block-scaled kernel only:
-                                // bit 2 = no TMEM loads, bit 3 = scalar FMAs, bit 4 = no final stores,
+                                // bit 2 = no TMEM loads, bit 4 = no final stores,
                                 // bit 5 = no TMA loads (the MMAs run on whatever shared memory holds)
+#endif
 };
+
+// The timing switches exist only in a library built with -DFMOE_TIMING_SWITCHES; in the
+// product build the tests below are constant false and the compiler drops them.
+#ifdef FMOE_TIMING_SWITCHES
+#define FMOE_DBG(p, bits) (((p).debug_flags & (bits)) != 0)
+#else
+#define FMOE_DBG(p, bits) false
+#endif
+
+// Checked build (-DFMOE_BOUNDS_CHECKS): every computed output row is compared with its bound
+// before the store; a violation stores a code in the status word instead of writing.
+enum : int { kStatusBoundsGemm = 0x400, kStatusBoundsRows = 0x500 };
+#ifdef FMOE_BOUNDS_CHECKS
+#define FMOE_ROW_OK(p, r) ((r) < (p).out_rows ? true : (atomicExch((p).status, kStatusBoundsGemm), false))
+#else
+#define FMOE_ROW_OK(p, r) true
+#endif
 
 struct TileCoord {
   int expert, m_blk, n_blk;
@@ -174,7 +196,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
         const int seg = lane & 3;
         const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
         const int live_r = __shfl_sync(0xffffffffu, row, r);
-        if (live_r >= 0)
+        if (live_r >= 0 && FMOE_ROW_OK(p, slot0 + r))
           *reinterpret_cast<uint4*>(ybase + static_cast<size_t>(slot0 + r) * p.ld_out + c * 32 + seg * 8) = val;
       }
     }
@@ -216,7 +238,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
         const int seg = lane & 3;
         const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
         const int live_r = __shfl_sync(0xffffffffu, row, r);
-        if (live_r >= 0)
+        if (live_r >= 0 && FMOE_ROW_OK(p, slot0 + r))
           *reinterpret_cast<uint4*>(ybase + static_cast<size_t>(slot0 + r) * p.ld_out + c * 32 + seg * 8) = val;
       }
     }
@@ -246,15 +268,34 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
         srow[q] = make_float4(w * f[0], w * f[1], w * f[2], w * f[3]);
       }
       __syncwarp();
-      // 8 lanes per row, 4 rows per store instruction: 128 contiguous bytes per row
+      if (p.out_bf16) {
+        // bf16 partial rows: 4 lanes per row, 8 rows per store instruction, 64 bytes per row
+        __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.out) + n_blk * kTileN;
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int r = it * 4 + (lane >> 3);
-        const int seg = lane & 7;
-        const float4 val = *reinterpret_cast<const float4*>(stage + r * kStageWordsPerRow + seg * 4);
-        const int row_r = __shfl_sync(0xffffffffu, row, r);
-        if (row_r >= 0)
-          *reinterpret_cast<float4*>(obase + static_cast<size_t>(row_r) * p.ld_out + c * 32 + seg * 4) = val;
+        for (int it = 0; it < 4; ++it) {
+          const int r = it * 8 + (lane >> 2);
+          const int seg = lane & 3;
+          const float4 v0 = *reinterpret_cast<const float4*>(stage + r * kStageWordsPerRow + seg * 8);
+          const float4 v1 = *reinterpret_cast<const float4*>(stage + r * kStageWordsPerRow + seg * 8 + 4);
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v0.x, v0.y), h1 = __floats2bfloat162_rn(v0.z, v0.w);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v1.x, v1.y), h3 = __floats2bfloat162_rn(v1.z, v1.w);
+          const uint4 val = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                       *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+          const int row_r = __shfl_sync(0xffffffffu, row, r);
+          if (row_r >= 0 && FMOE_ROW_OK(p, row_r))
+            *reinterpret_cast<uint4*>(hbase + static_cast<size_t>(row_r) * p.ld_out + c * 32 + seg * 8) = val;
+        }
+      } else {
+        // 8 lanes per row, 4 rows per store instruction: 128 contiguous bytes per row
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + (lane >> 3);
+          const int seg = lane & 7;
+          const float4 val = *reinterpret_cast<const float4*>(stage + r * kStageWordsPerRow + seg * 4);
+          const int row_r = __shfl_sync(0xffffffffu, row, r);
+          if (row_r >= 0 && FMOE_ROW_OK(p, row_r))
+            *reinterpret_cast<float4*>(obase + static_cast<size_t>(row_r) * p.ld_out + c * 32 + seg * 4) = val;
+        }
       }
     }
   }
@@ -301,12 +342,11 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;   // K elements per stage
   constexpr int kUmmaKBytes = 32;                   // one MMA consumes 32 bytes of K per row
 
-  // Everything the previous kernel produced is read after this point.
-  ptx::pdl_wait();
-  // The block table is read on every tile boundary by the producer; keep it on chip so the
-  // decode does not sit on the critical path with dependent global loads.
-  for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
+  // Set-up that needs nothing from the previous kernel on the stream runs before the
+  // dependency wait, so under programmatic dependent launch it overlaps that kernel's tail.
   if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_a);
+    ptx::prefetch_tensormap(&tm_b);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
@@ -323,6 +363,11 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
     ptx::tmem_relinquish();
   }
+  // Everything the previous kernel produced is read after this point.
+  ptx::pdl_wait();
+  // The block table is read on every tile boundary by the producer; keep it on chip so the
+  // decode does not sit on the critical path with dependent global loads.
+  for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -333,8 +378,6 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      ptx::prefetch_tensormap(&tm_a);
-      ptx::prefetch_tensormap(&tm_b);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -363,6 +406,9 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
       }
       if (!ok) atomicExch(p.status, kStatusGemmTimeout | 1);
+      // every operand of this CTA has been requested: the next kernel on the stream may start
+      // its own set-up while the last tiles are multiplied and stored
+      ptx::pdl_release();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -393,7 +439,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             // advancing K inside the swizzle row = advancing the start address
             const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
             const uint32_t accum = (k | kk) ? 1u : 0u;
-            if (p.debug_flags & 2u) continue;
+            if (FMOE_DBG(p, 2u)) continue;
             if (kFp8) ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, accum);
             else      ptx::umma_f16(d_tmem, da + adv, db + adv, p.idesc, accum);
           }
@@ -429,7 +475,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      if (!(p.debug_flags & 1u))
+      if (!FMOE_DBG(p, 1u))
         epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s,
                             reinterpret_cast<uint32_t*>(misc + kSmemMisc) + quad * (kEpiStageBytesPerWarp / 4));
       ptx::tc_fence_before();
@@ -439,7 +485,6 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (!ok && epi_tid == 0) atomicExch(p.status, kStatusGemmTimeout | 3);
   }
 
-  ptx::pdl_release();     // the next kernel may start its prologue while this CTA winds down
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -507,9 +552,9 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;
   constexpr int kUmmaKBytes = 32;
 
-  ptx::pdl_wait();
-  for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
   if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_a);
+    ptx::prefetch_tensormap(&tm_b);
     for (int s = 0; s < kPairStages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
@@ -526,6 +571,9 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
     ptx::tmem_relinquish_pair();
   }
+  // set-up above needs nothing from the previous kernel; its output is read from here on
+  ptx::pdl_wait();
+  for (int i = threadIdx.x; i <= p.num_experts; i += kGemmThreads) cum_s[i] = p.mblk_cum[i];
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -547,8 +595,6 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both ranks)
     if (lane == 0) {
-      ptx::prefetch_tensormap(&tm_a);
-      ptx::prefetch_tensormap(&tm_b);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -575,6 +621,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
       }
       if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x11);
+      ptx::pdl_release();   // all operands requested: the next kernel may begin its set-up
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (rank 0 only)
@@ -604,7 +651,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
             const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
             const uint32_t accum = (k | kk) ? 1u : 0u;
-            if (p.debug_flags & 2u) continue;
+            if (FMOE_DBG(p, 2u)) continue;
             if (kFp8) ptx::umma_f8_pair(d_tmem, da + adv, db + adv, p.idesc, accum);
             else      ptx::umma_f16_pair(d_tmem, da + adv, db + adv, p.idesc, accum);
           }
@@ -644,7 +691,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * kTileN);
-      if (valid && !(p.debug_flags & 1u))
+      if (valid && !FMOE_DBG(p, 1u))
         epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s,
                             reinterpret_cast<uint32_t*>(misc + kPairSmemMisc) + quad * (kEpiStageBytesPerWarp / 4));
       ptx::tc_fence_before();
@@ -657,349 +704,11 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   // Neither CTA may leave while its partner can still signal its barriers or read its
   // shared memory through a pair MMA.
-  ptx::pdl_release();
   ptx::tc_fence_before();
   ptx::cluster_sync_all();
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
-  }
-}
-
-// ============================================================================= block-scaled fp8
-// 1x128 activation groups x 128x128 weight blocks: the scale changes every 128 elements of
-// K, which is exactly one pipeline stage of e4m3.  The MMAs of one stage therefore write a
-// *partial* product into one of two 256-column TMEM buffers (no accumulation across stages)
-// and eight epilogue warps promote it: acc += partial * (s_act[row, kb] * s_w[nblock, kb]),
-// with the running sums in registers (128 per thread).  Thread (quadrant q, half h) owns
-// row 32q+lane and, for the first GEMM, gate columns [64h, 64h+64) and the matching up
-// columns, so SiLU(gate)*up needs no exchange; for the second GEMM it owns output channels
-// [128h, 128h+128), one weight-scale block.
-constexpr int kBlockGemmThreads = 384;   // warpgroup 0: producer + MMA (+2 idle warps); warpgroups 1, 2: epilogue
-constexpr int kBlockStages = 4;
-constexpr int kScaleAhead = 4;           // K blocks between the load of a scale and its use
-// setmaxnreg only redistributes what the CTA was given at launch (384 threads x 168 registers):
-// the per-role counts must add up to no more than that, or setmaxnreg.inc never returns.
-constexpr int kBlockThinRegs = 40;       // registers per thread kept by warpgroup 0
-constexpr int kBlockFatRegs = 232;       // registers per thread taken by the epilogue warpgroups
-static_assert(128 * kBlockThinRegs + 256 * kBlockFatRegs <= kBlockGemmThreads * 168, "register budget");
-constexpr int kBlockSmemBytes = kBlockStages * kStageBytes + kSmemMisc + 8 * 32 * 20 * 4 + 1024;
-
-struct BlockGemmParams {
-  GemmParams g;                 // a_scale / b_scale of g are unused here
-  const float* a_scale;         // [cap, k_blocks] per sorted row and 128-wide K group
-  const float* b_scale;         // [E * b_rows_per_expert / 128, k_blocks]
-  int k_blocks;                 // K / 128 (== g.k_iters)
-};
-
-template <int kEpi>
-__global__ void __launch_bounds__(kBlockGemmThreads, 1)
-fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
-                               const __grid_constant__ CUtensorMap tm_b, const BlockGemmParams bp) {
-  const GemmParams& p = bp.g;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint8_t* misc = smem + kBlockStages * kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(misc);
-  uint64_t* empty_bar = full_bar + kBlockStages;
-  uint64_t* part_full_bar = empty_bar + kBlockStages;                // [2] partial product ready
-  uint64_t* part_empty_bar = part_full_bar + 2;                      // [2] partial consumed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty_bar + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* cum_s = reinterpret_cast<int*>(misc + 256);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  constexpr int kUmmaKBytes = 32;
-
-  ptx::pdl_wait();
-  for (int i = threadIdx.x; i <= p.num_experts; i += kBlockGemmThreads) cum_s[i] = p.mblk_cum[i];
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kBlockStages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(ptx::smem_u32(&part_full_bar[b]), 1);
-      ptx::mbar_init(ptx::smem_u32(&part_empty_bar[b]), 8);
-    }
-    *abort_flag = 0;
-    ptx::fence_barrier_init();
-    ptx::fence_proxy_async();
-  }
-  if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = cum_s[p.num_experts] * p.n_blocks;
-
-  if (warp < 4) {
-    // -------------------------------------------------------------- warpgroup 0: data movement and MMA issue
-    ptx::setmaxnreg_dec<kBlockThinRegs>();
-    if (warp == 0 && lane == 0) {
-      ptx::prefetch_tensormap(&tm_a);
-      ptx::prefetch_tensormap(&tm_b);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
-        const int a_row = tc.m_blk * kBlockM;
-        const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
-        const int b_row1 = b_row0 + p.second_slab_offset;
-        for (int k = 0; k < p.k_iters; ++k) {
-          if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
-            ok = false;
-            break;
-          }
-          const uint32_t full = ptx::smem_u32(&full_bar[stage]);
-          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
-          const uint32_t sb = sa + kABytes;
-          if (p.debug_flags & 32u) {     // timing experiment: no operand traffic at all
-            ptx::mbar_arrive(full);
-            if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
-            continue;
-          }
-          ptx::mbar_arrive_expect_tx(full, kStageBytes);
-          const int kx = k * 128;
-          int bx, by0, by1;
-          b_coords(p, b_row0, k, 128, bx, by0);
-          b_coords(p, b_row1, k, 128, bx, by1);
-          ptx::tma_load_2d(sa, &tm_a, full, kx, a_row);
-          ptx::tma_load_2d(sb, &tm_b, full, bx, by0);
-          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, bx, by1);
-          if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
-        }
-      }
-      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x21);
-    } else if (warp == 1 && lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int buf = 0;
-      uint32_t buf_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        for (int k = 0; k < p.k_iters; ++k) {
-          if (!ptx::mbar_wait(ptx::smem_u32(&part_empty_bar[buf]), buf_phase ^ 1u, abort_flag) ||
-              !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after();
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kTileN);
-          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
-          const uint64_t da = ptx::make_smem_desc(p.desc_template, sa);
-          const uint64_t db = ptx::make_smem_desc(p.desc_template, sa + kABytes);
-#pragma unroll
-          for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
-            const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
-            if (!(p.debug_flags & 2u))
-              ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, kk ? 1u : 0u);   // fresh partial per stage
-          }
-          ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
-          ptx::umma_commit(ptx::smem_u32(&part_full_bar[buf]));
-          if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
-          if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
-        }
-      }
-      if (!ok) atomicExch(p.status, kStatusGemmTimeout | 0x22);
-    }
-  } else {
-    // -------------------------------------------------------------- warpgroups 1, 2: promotion + epilogue
-    ptx::setmaxnreg_inc<kBlockFatRegs>();
-    const int quad = warp & 3;
-    const int half = (warp - 4) >> 2;
-    int buf = 0;
-    uint32_t buf_phase = 0;
-    bool ok = true;
-    const int kb_n = bp.k_blocks;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
-      const int slot = tc.m_blk * kBlockM + quad * 32 + lane;
-      const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
-      const float* sa_row = bp.a_scale + static_cast<size_t>(slot) * kb_n;
-      const float* sb0;
-      const float* sb1;
-      if (kEpi == kEpiSiluMul) {
-        sb0 = bp.b_scale + static_cast<size_t>(b_row0 / 128) * kb_n;                          // gate slab
-        sb1 = bp.b_scale + static_cast<size_t>((b_row0 + p.second_slab_offset) / 128) * kb_n; // up slab
-      } else {
-        sb0 = bp.b_scale + static_cast<size_t>(b_row0 / 128 + half) * kb_n;
-        sb1 = sb0;
-      }
-      uint64_t acc[64];          // 128 f32 running sums, two per register pair
-#pragma unroll
-      for (int j = 0; j < 64; ++j) acc[j] = 0ull;
-      // TMEM columns of this thread's two 64-column runs
-      const int col0 = (kEpi == kEpiSiluMul) ? half * 64 : half * 128;
-      const int col1 = (kEpi == kEpiSiluMul) ? kSlabRows + half * 64 : half * 128 + 64;
-      // Scales are fetched kScaleAhead K blocks before they are used: the per-row loads miss
-      // the small L1 that is left beside 221 KiB of shared memory, and an L2 round trip takes
-      // longer than one stage.
-      // The row's activation scales come four at a time (one 16-byte load per four stages
-      // instead of four 4-byte loads that each touch 32 sectors per warp) when the rows of
-      // the scale matrix are whole, aligned float4s.
-      static_assert(kScaleAhead == 4, "the vector path loads one float4 per block of stages");
-      const bool vec4 = (kb_n & 3) == 0 && (reinterpret_cast<uintptr_t>(bp.a_scale) & 15) == 0;
-      float q_act[kScaleAhead], n_act[kScaleAhead], q_b0[kScaleAhead], q_b1[kScaleAhead];
-      if (vec4) {
-        const float4 t = __ldg(reinterpret_cast<const float4*>(sa_row));
-        q_act[0] = t.x; q_act[1] = t.y; q_act[2] = t.z; q_act[3] = t.w;
-      }
-#pragma unroll
-      for (int u = 0; u < kScaleAhead; ++u) {
-        n_act[u] = 0.f;
-        if (u < p.k_iters) {
-          if (!vec4) q_act[u] = __ldg(sa_row + u);
-          q_b0[u] = __ldg(sb0 + u);
-          q_b1[u] = kEpi == kEpiSiluMul ? __ldg(sb1 + u) : q_b0[u];
-        }
-      }
-      for (int k0 = 0; ok && k0 < p.k_iters; k0 += kScaleAhead) {
-        if (vec4 && k0 + kScaleAhead < p.k_iters) {
-          const float4 t = __ldg(reinterpret_cast<const float4*>(sa_row + k0 + kScaleAhead));
-          n_act[0] = t.x; n_act[1] = t.y; n_act[2] = t.z; n_act[3] = t.w;
-        }
-#pragma unroll
-      for (int u = 0; u < kScaleAhead; ++u) {
-        const int k = k0 + u;
-        if (k >= p.k_iters) break;
-        const float sc0 = q_act[u] * q_b0[u], sc1 = q_act[u] * q_b1[u];
-        const uint64_t sc0_2 = ptx::pack2(sc0, sc0), sc1_2 = ptx::pack2(sc1, sc1);
-        if (k + kScaleAhead < p.k_iters) {
-          if (!vec4) q_act[u] = __ldg(sa_row + k + kScaleAhead);
-          q_b0[u] = __ldg(sb0 + k + kScaleAhead);
-          q_b1[u] = kEpi == kEpiSiluMul ? __ldg(sb1 + k + kScaleAhead) : q_b0[u];
-        }
-        if (!ptx::mbar_wait(ptx::smem_u32(&part_full_bar[buf]), buf_phase, abort_flag)) {
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                               static_cast<uint32_t>(buf * kTileN);
-        uint32_t v[2][32];
-        const bool dbg_no_ld = p.debug_flags & 4u, dbg_no_fma = p.debug_flags & 1u, dbg_scalar = p.debug_flags & 8u;
-        if (!dbg_no_ld) {
-          ptx::tmem_ld_32x32(t_row + col0, v[0]);
-          ptx::tmem_ld_32x32(t_row + col0 + 32, v[1]);
-          ptx::tmem_ld_wait();
-        }
-        if (!dbg_no_fma && !dbg_scalar) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ptx::fma2(acc[j], v[0][2 * j], v[0][2 * j + 1], sc0_2);
-        }
-        if (!dbg_no_ld) ptx::tmem_ld_32x32(t_row + col1, v[0]);
-        if (!dbg_no_fma && !dbg_scalar) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ptx::fma2(acc[16 + j], v[1][2 * j], v[1][2 * j + 1], sc0_2);
-        }
-        if (!dbg_no_ld) {
-          ptx::tmem_ld_32x32(t_row + col1 + 32, v[1]);
-          ptx::tmem_ld_wait();
-        }
-        // all four loads have landed: the buffer can be overwritten while the last FMAs run
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&part_empty_bar[buf]));
-        if (!dbg_no_fma && !dbg_scalar) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ptx::fma2(acc[32 + j], v[0][2 * j], v[0][2 * j + 1], sc1_2);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ptx::fma2(acc[48 + j], v[1][2 * j], v[1][2 * j + 1], sc1_2);
-        }
-        if (dbg_scalar) {      // timing experiment: scalar FMAs on half of the data
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float lo, hi;
-            ptx::unpack2(acc[j], lo, hi);
-            lo = fmaf(__uint_as_float(v[0][j]), sc0, lo);
-            hi = fmaf(__uint_as_float(v[1][j]), sc1, hi);
-            acc[j] = ptx::pack2(lo, hi);
-          }
-        }
-        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
-      }
-        if (vec4) {
-#pragma unroll
-          for (int u = 0; u < kScaleAhead; ++u) q_act[u] = n_act[u];
-        }
-      }
-      if (!ok) break;
-      if (p.debug_flags & 16u) continue;
-      // Final stores go through a per-warp transpose (32 rows x 16 words at a time) so each
-      // store instruction writes 64-byte row segments instead of 16 bytes to 32 different rows.
-      uint32_t* stage = reinterpret_cast<uint32_t*>(misc + kSmemMisc) + (warp - 4) * (32 * 20);
-      const int row = p.sorted_rows[slot];
-      const int slot0 = slot - lane;
-      if (kEpi == kEpiSiluMul) {
-        // pairs 0..31: gate, 32..63: up, columns n_blk*128 + half*64 ..
-        __nv_bfloat16* ybase = reinterpret_cast<__nv_bfloat16*>(p.out) + tc.n_blk * kSlabRows + half * 64;
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {            // 32 columns (16 packed words) per chunk
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float g0, g1, u0, u1;
-            ptx::unpack2(acc[ch * 16 + j], g0, g1);
-            ptx::unpack2(acc[32 + ch * 16 + j], u0, u1);
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
-            w[j] = *reinterpret_cast<uint32_t*>(&v2);
-          }
-          __syncwarp();
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            reinterpret_cast<uint4*>(stage + lane * 20)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-          __syncwarp();
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int r = it * 8 + (lane >> 2);
-            const int seg = lane & 3;
-            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
-            if (__shfl_sync(0xffffffffu, row, r) >= 0)
-              *reinterpret_cast<uint4*>(ybase + static_cast<size_t>(slot0 + r) * p.ld_out + ch * 32 + seg * 8) = val;
-          }
-        }
-      } else if (kEpi == kEpiScaledSlots) {
-        const float wt = p.sorted_weights[slot];
-        float* obase = reinterpret_cast<float*>(p.out) + tc.n_blk * kTileN + half * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {            // 16 columns per chunk
-          __syncwarp();
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float a0, a1, a2, a3;
-            ptx::unpack2(acc[ch * 8 + 2 * q], a0, a1);
-            ptx::unpack2(acc[ch * 8 + 2 * q + 1], a2, a3);
-            reinterpret_cast<float4*>(stage + lane * 20)[q] = make_float4(wt * a0, wt * a1, wt * a2, wt * a3);
-          }
-          __syncwarp();
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int r = it * 8 + (lane >> 2);
-            const int seg = lane & 3;
-            const float4 val = *reinterpret_cast<const float4*>(stage + r * 20 + seg * 4);
-            const int row_r = __shfl_sync(0xffffffffu, row, r);
-            if (row_r >= 0)
-              *reinterpret_cast<float4*>(obase + static_cast<size_t>(row_r) * p.ld_out + ch * 16 + seg * 4) = val;
-          }
-        }
-      }
-    }
-    if (!ok && threadIdx.x == 128) atomicExch(p.status, kStatusGemmTimeout | 0x23);
-  }
-
-  ptx::pdl_release();     // the next kernel may start its prologue while this CTA winds down
-  ptx::tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -49,10 +49,11 @@ constexpr size_t sort_scratch_words(int E) { return 2 * 64 * static_cast<size_t>
 //   live_ids (optional, [cap]): slots whose entry is negative are skipped entirely.
 cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
-                               float* scales, cudaStream_t stream, const int32_t* live_ids = nullptr);
+                               void* scales, cudaStream_t stream, const int32_t* live_ids = nullptr);
 
-// out[t, :] = bf16( sum_k slots[t*K + k, :] ) over the k whose expert id lies in [0, E).
-cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
+// out[t, :] = bf16( sum_k slots[t*K + k, :] ) over the k whose expert id lies in [0, E);
+// slots are f32, or bf16 when slots_bf16.
+cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream,
                            const int32_t* num_tokens_dev = nullptr);
 
@@ -63,7 +64,7 @@ cudaError_t launch_combine_rows(const void* rows, const int32_t* index, int T, i
 
 struct GemmLaunch {
   bool fp8;
-  int epilogue;                 // kEpiSiluMul / kEpiScaledSlots
+  int epilogue;                 // kEpiSiluMul / kEpiScaledSlots / kEpiSilu
   const void* a;                // [a_rows, k_elems] row-major
   int64_t a_rows;
   const void* b;                // [E * b_rows_per_expert, k_elems] row-major
@@ -74,26 +75,27 @@ struct GemmLaunch {
   const int32_t* mblk_cum;
   const int32_t* sorted_rows;
   const float* sorted_weights;
-  const float* a_scale;
-  const float* b_scale;
+  const void* a_scale;          // f32 [a_rows] (per row), f32 [a_rows, K/128] (block promote) or the
+                                // packed UE8M0 image (block_scale MMA)
+  const float* b_scale;         // f32 [E * b_rows] or [E * b_rows / 128, K/128]
   void* out;
   int ld_out;
+  int64_t out_rows;             // rows of `out` (bound used by the checked build)
+  bool out_bf16;                // kEpiScaledSlots: weighted rows stored as bf16 instead of f32
+  void* out_scale;              // block flavours, first GEMM: when set, `out` receives e4m3 and this the
+                                // 1x128 scales of the intermediate (f32 [a_rows, ld_out/128] or packed UE8M0)
   int32_t* status;
   int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
-  int max_live_rows;            // upper bound on real rows in any block (0 = unknown, i.e. 128)
   bool b_tiled;                 // B is stored as contiguous 128-row x 128-byte tiles (see fmoe_weight_layout)
-  bool block_scale;             // fp8 with 1x128 activation groups and 128x128 weight blocks:
-                                // a_scale is [a_rows, K/128], b_scale [E*b_rows/128, K/128]
-  int mode;                     // 2 = CTA-pair kernel (cta_group::2), anything else = single-CTA kernel
-  uint64_t desc_template_override;  // 0 = the library's descriptor encoding (diagnostics only)
-  uint32_t idesc_override;          // 0 = the library's instruction descriptor
+  int flavour;                  // fmoe_gemm_kernel
 };
 // Returns cudaSuccess or the failing CUDA error; *drv_err receives a CUresult when the
 // tensor-map encode fails.
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err);
 
-// 0 = no override, 1 / 2 = FMOE_GEMM_MODE forces the single-CTA / CTA-pair kernel.
-int gemm_mode_from_env();
+// 0 = no override; 1 / 2 force the single-CTA / CTA-pair kernel.  Always 0 unless the library
+// was built with -DFMOE_TIMING_SWITCHES (then FMOE_GEMM_MODE=1cta|2cta is honoured).
+int gemm_mode_override();
 // SM count of the current device (cached).
 int device_sm_count();
 

@@ -137,6 +137,28 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
+// Block-scaled MMA: D[tmem] (+)= (A * SFA) * (B * SFB)^T with e4m3 operands in shared memory and
+// one UE8M0 scale per row and 32 elements of K, read from tensor memory.  A scale column holds
+// four bytes per lane; the instruction descriptor selects the byte (see make_idesc_block_scaled).
+__device__ __forceinline__ void umma_mxf8_block_scale(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Shared memory -> tensor memory: 32 rows of 16 bytes become four 32-bit columns of lanes 0..31,
+// replicated to the other three lane quadrants (the layout scale factors are read from).
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane
 // (taddr.lane + i), columns taddr.col .. +31.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -273,6 +295,23 @@ __host__ __device__ constexpr uint64_t sw128_kmajor_desc_template() {
 }
 __device__ __forceinline__ uint64_t make_smem_desc(uint64_t desc_template, uint32_t smem_addr) {
   return desc_template | static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // 16-byte units
+}
+
+// Descriptor of an unswizzled K-major matrix of 16-byte rows stored back to back (8-row groups
+// 128 bytes apart): the source of a scale-factor copy to tensor memory.
+__device__ __forceinline__ uint64_t make_rows16_desc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 16) |
+         (static_cast<uint64_t>(128 >> 4) << 32) | (static_cast<uint64_t>(1) << 46);
+}
+
+// Instruction descriptor of the block-scaled kind (e4m3 x e4m3, K-major, UE8M0 scales):
+// bits 4-5 byte of the B scale column, 7-9 / 10-12 operand formats (0 = e4m3), 17-22 N/8,
+// 23 scale format (1 = UE8M0), 24-28 M/16, 29-30 byte of the A scale column.
+__host__ __device__ constexpr uint32_t make_idesc_block_scaled(uint32_t m, uint32_t n) {
+  return ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t idesc_with_scale_byte(uint32_t idesc, uint32_t byte) {
+  return idesc | (byte << 4) | (byte << 29);
 }
 
 // Instruction descriptor: f32 accumulate, A and B K-major, dense.

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/fused_moe_c.h"
+#include "plan.hpp"
 
 namespace fmoe {
 namespace {
@@ -92,12 +93,16 @@ route_kernel(const float* __restrict__ logits, int T, int E, int K, int mode,
 
 extern "C" int fmoe_route(const float* logits, int32_t T, int32_t E, int32_t K, int32_t mode,
                           int32_t* topk_ids, float* topk_weight, void* stream) {
-  if (!logits || !topk_ids || !topk_weight) return FMOE_ERR_INVALID_ARG;
-  if (T < 0 || E <= 0 || K <= 0 || K > E || (mode != 0 && mode != 1)) return FMOE_ERR_INVALID_ARG;
-  if (E > 32 * fmoe::kMaxPerLane || K > 32) return FMOE_ERR_UNSUPPORTED;
+  if (!logits || !topk_ids || !topk_weight)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_route: logits, topk_ids and topk_weight are required");
+  if (T < 0 || E <= 0 || K <= 0 || K > E || (mode != 0 && mode != 1))
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_route: bad arguments (T=%d E=%d K=%d mode=%d)", T, E, K, mode);
+  if (E > 32 * fmoe::kMaxPerLane || K > 32)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_route: at most %d experts and 32 experts per token", 32 * fmoe::kMaxPerLane);
   if (T == 0) return FMOE_OK;
   const int grid = (T + fmoe::kRouteWarps - 1) / fmoe::kRouteWarps;
   fmoe::route_kernel<<<grid, fmoe::kRouteWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       logits, T, E, K, mode, topk_ids, topk_weight);
-  return cudaGetLastError() == cudaSuccess ? FMOE_OK : FMOE_ERR_CUDA;
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FMOE_OK : fmoe::fail(FMOE_ERR_CUDA, "fmoe_route launch failed: %s", cudaGetErrorString(e));
 }

@@ -8,6 +8,7 @@
 
 #include "internal.h"
 #include "ptx.cuh"
+#include "scales.cuh"
 
 namespace fmoe {
 namespace {
@@ -47,8 +48,9 @@ template <int kQuant>
 __global__ void __launch_bounds__(kRowThreads)
 gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
                    const int32_t* __restrict__ row_ids, const int32_t* __restrict__ num_post_pad,
-                   void* __restrict__ dst, float* __restrict__ scales,
+                   void* __restrict__ dst, void* __restrict__ scales_v,
                    const int32_t* __restrict__ live_ids) {
+  float* scales = reinterpret_cast<float*>(scales_v);
   ptx::pdl_wait();
   ptx::pdl_release();
   const int slot = blockIdx.x;
@@ -154,9 +156,16 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
         for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        const float sc = amax > 0.0f ? amax / 448.0f : 1.0f;
+        uint32_t sbyte;
+        const float sc = group_scale<kQuant == 3>(amax, sbyte);
         if (i < nvec) {
-          if ((i & 15) == 0) scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
+          if ((i & 15) == 0) {
+            if (kQuant == 3)   // one UE8M0 byte in the image the block-scaled MMA's scale copy reads
+              reinterpret_cast<uint8_t*>(scales_v)[packed_scale_offset(slot >> 7, slot & 127, i >> 4, (ngroups + 3) >> 2)] =
+                  static_cast<uint8_t>(sbyte);
+            else
+              scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
+          }
           d[i] = quant8(f, 1.0f / sc);
         }
       }
@@ -164,21 +173,31 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
   }
 }
 
+template <bool kBf16Slots>
 __global__ void __launch_bounds__(kRowThreads)
-combine_kernel(const float4* __restrict__ slots, const int32_t* __restrict__ topk_ids, int K, int E,
+combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ topk_ids, int K, int E,
                int H, uint2* __restrict__ out, const int32_t* __restrict__ num_tokens_dev) {
   ptx::pdl_wait();
   ptx::pdl_release();
   const int t = blockIdx.x;
   if (num_tokens_dev && t >= *num_tokens_dev) return;   // rows past the device-side count
   const int nvec = H >> 2;
+  const float4* slots = reinterpret_cast<const float4*>(slots_v);
+  const uint2* slots_h = reinterpret_cast<const uint2*>(slots_v);
   for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < K; ++k) {
       const int e = topk_ids[t * K + k];
       if (e < 0 || e >= E) continue;
-      const float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      const size_t idx = (static_cast<size_t>(t) * K + k) * nvec + i;
+      if (kBf16Slots) {
+        const uint2 h = slots_h[idx];
+        acc.x += bf16_bits_to_f32(h.x & 0xffffu); acc.y += bf16_bits_to_f32(h.x >> 16);
+        acc.z += bf16_bits_to_f32(h.y & 0xffffu); acc.w += bf16_bits_to_f32(h.y >> 16);
+      } else {
+        const float4 v = slots[idx];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
     __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
@@ -224,21 +243,26 @@ cudaError_t launch_combine_rows(const void* rows, const int32_t* index, int T, i
 
 cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
-                               float* scales, cudaStream_t stream, const int32_t* live_ids) {
+                               void* scales, cudaStream_t stream, const int32_t* live_ids) {
   const dim3 grid(static_cast<unsigned>(cap));
   const uint4* s = reinterpret_cast<const uint4*>(src);
   if (quant == 0)
     return launch_pdl(gather_rows_kernel<0>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   else if (quant == 1)
     return launch_pdl(gather_rows_kernel<1>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
-  else
+  else if (quant == 2)
     return launch_pdl(gather_rows_kernel<2>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
+  else
+    return launch_pdl(gather_rows_kernel<3>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
 }
 
-cudaError_t launch_combine(const float* slots, const int32_t* topk_ids, int T, int K, int E,
+cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev) {
-  return launch_pdl(combine_kernel, dim3(T), dim3(kRowThreads), 0, stream, reinterpret_cast<const float4*>(slots),
-                    topk_ids, K, E, H, reinterpret_cast<uint2*>(out), num_tokens_dev);
+  if (slots_bf16)
+    return launch_pdl(combine_kernel<true>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H,
+                      reinterpret_cast<uint2*>(out), num_tokens_dev);
+  return launch_pdl(combine_kernel<false>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H,
+                    reinterpret_cast<uint2*>(out), num_tokens_dev);
 }
 
 }  // namespace fmoe

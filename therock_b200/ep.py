@@ -310,7 +310,7 @@ class PeerExpertParallelMoE:
         self.barrier_timeout_ms = 0          # 0 = the library default (about four seconds)
         self.trace = None                    # set to [] to collect (phase, cuda event) marks
         self._ctypes = ctypes
-        self.launches_per_step = 8 + api.launches_per_run(traits)
+        self.launches_per_step = 8 + api.launches_per_run(traits, self.args)
 
     def _barrier(self, stream):
         # the epoch is a device-side counter, so the launch arguments never change
