@@ -1,0 +1,113 @@
+// Host-only exercise of the C-ABI's validation, workspace planning and kernel choice
+// (therock_b200/csrc/plan.hpp), built with -fsanitize=address,undefined by
+// tests/test_sanitizers.py.  Exits 0 when every expectation holds; the sanitizers abort the
+// program on any out-of-bounds access, overflow or misaligned use they see on the way.
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "../../therock_b200/csrc/plan.hpp"
+
+static int failures = 0;
+#define EXPECT(cond)                                                          \
+  do {                                                                        \
+    if (!(cond)) { std::printf("FAILED line %d: %s\n", __LINE__, #cond); ++failures; } \
+  } while (0)
+
+static fmoe_traits_c traits(int quant) {
+  fmoe_traits_c t;
+  std::memset(&t, 0, sizeof(t));
+  t.quant = quant;
+  t.weight_dtype = quant == FMOE_QUANT_NONE ? FMOE_BF16 : FMOE_FP8_E4M3;
+  t.block_m = 128;
+  return t;
+}
+
+static fmoe_args_c dims(int T, int H, int I, int E, int K) {
+  fmoe_args_c a;
+  std::memset(&a, 0, sizeof(a));
+  a.T = T; a.H = H; a.I = I; a.E = E; a.K = K;
+  return a;
+}
+
+int main() {
+  using namespace fmoe;
+  // null and malformed arguments
+  EXPECT(validate_traits(nullptr) == FMOE_ERR_INVALID_ARG);
+  EXPECT(std::strlen(last_error_buf()) > 0);
+  fmoe_traits_c t = traits(FMOE_QUANT_NONE);
+  EXPECT(validate_traits(&t) == FMOE_OK);
+  EXPECT(validate_dims(&t, nullptr) == FMOE_ERR_INVALID_ARG);
+  for (int q = -3; q <= 6; ++q) {
+    fmoe_traits_c tq = traits(q);
+    const int rc = validate_traits(&tq);
+    EXPECT((q >= 0 && q <= 3) ? rc == FMOE_OK : rc == FMOE_ERR_INVALID_ARG);
+  }
+  t.block_m = 64; EXPECT(validate_traits(&t) == FMOE_ERR_UNSUPPORTED); t.block_m = 128;
+  t.partial_dtype = 9; EXPECT(validate_traits(&t) == FMOE_ERR_INVALID_ARG); t.partial_dtype = 0;
+  t.gemm_mode = 3; EXPECT(validate_traits(&t) == FMOE_ERR_INVALID_ARG); t.gemm_mode = 0;
+  t.weight_layout = -1; EXPECT(validate_traits(&t) == FMOE_ERR_INVALID_ARG); t.weight_layout = 0;
+
+  // dimension limits, including the extremes that could overflow 32-bit products
+  fmoe_args_c a = dims(128, 512, 1024, 8, 2);
+  EXPECT(validate_dims(&t, &a) == FMOE_OK);
+  a = dims(-1, 512, 1024, 8, 2); EXPECT(validate_dims(&t, &a) == FMOE_ERR_INVALID_ARG);
+  a = dims(128, 500, 1024, 8, 2); EXPECT(validate_dims(&t, &a) == FMOE_ERR_UNSUPPORTED);
+  a = dims(128, 512, 1000, 8, 2); EXPECT(validate_dims(&t, &a) == FMOE_ERR_UNSUPPORTED);
+  a = dims(128, 512, 1024, 1025, 2); EXPECT(validate_dims(&t, &a) == FMOE_ERR_UNSUPPORTED);
+  a = dims(128, 512, 1024, 2, 9); EXPECT(validate_dims(&t, &a) == FMOE_OK);      // K > E is legal
+  a = dims(0x7fffffff, 512, 1024, 8, 0x7fffffff); EXPECT(validate_dims(&t, &a) == FMOE_ERR_UNSUPPORTED);
+  a = dims(1 << 23, 512, 1024, 8, 2); EXPECT(validate_dims(&t, &a) == FMOE_OK);  // T*K == 2^24, the limit
+  a = dims((1 << 23) + 1, 512, 1024, 8, 2); EXPECT(validate_dims(&t, &a) == FMOE_ERR_UNSUPPORTED);
+
+  // workspace plans: regions ascend, are 256-byte aligned, do not overlap, and fit the total
+  const int shapes[][5] = {{128, 512, 1024, 8, 2}, {4096, 4096, 14336, 8, 2}, {8192, 4096, 14336, 8, 2},
+                           {16, 4096, 14336, 8, 2}, {8192, 7168, 2048, 256, 8}, {0, 256, 128, 1, 1},
+                           {1 << 23, 16128, 16128, 1024, 2}};
+  for (const auto& s : shapes) {
+    for (int q = 0; q <= 3; ++q) {
+      for (int pd = 0; pd <= 1; ++pd) {
+        fmoe_traits_c tq = traits(q);
+        tq.partial_dtype = pd;
+        fmoe_args_c aq = dims(s[0], s[1], s[2], s[3], s[4]);
+        if (validate_dims(&tq, &aq) != FMOE_OK) continue;
+        Plan p;
+        EXPECT(make_plan(&tq, &aq, &p) == FMOE_OK);
+        const fmoe_ws_layout_c& l = p.l;
+        const uint64_t offs[] = {l.meta, l.sorted_token_ids, l.sorted_weights, l.sorted_rows, l.sorted_expert_ids,
+                                 l.mblk_cum, l.a_sorted, l.a_scale, l.y, l.y_quant, l.y_scale, l.slots,
+                                 l.sort_scratch, l.total_bytes};
+        for (size_t i = 0; i + 1 < sizeof(offs) / sizeof(offs[0]); ++i) {
+          EXPECT(offs[i] % 256 == 0);
+          EXPECT(offs[i] <= offs[i + 1]);
+        }
+        EXPECT(l.capacity % 128 == 0);
+        EXPECT(l.capacity >= static_cast<int64_t>(s[0]) * s[4]);
+        EXPECT(l.slots + static_cast<uint64_t>(s[0]) * s[4] * s[1] * (pd ? 2 : 4) <= l.sort_scratch);
+        fmoe_run_info_c info;
+        std::memset(&info, 0, sizeof(info));
+        EXPECT(describe_run(&tq, &aq, 148, 0, &info) == FMOE_OK);
+        EXPECT(info.gemm1_kernel >= FMOE_KERNEL_SINGLE && info.gemm1_kernel <= FMOE_KERNEL_SINGLE_DECODE);
+        EXPECT(info.launches >= 5 && info.launches <= 8);
+        if (q == FMOE_QUANT_BLOCK128_UE8M0) EXPECT(info.gemm1_kernel == FMOE_KERNEL_BLOCK_HW_SCALE);
+      }
+    }
+  }
+  // packed scale image: every (row, K group) of a block maps to a distinct byte inside the image
+  {
+    const int64_t cap = 256;
+    const int k_elems = 7 * 128;            // seven K groups: the last quad is partly used
+    const uint64_t bytes = packed_scale_bytes(cap, k_elems);
+    std::vector<unsigned char> seen(bytes, 0);
+    const int kg4 = (k_elems / 128 + 3) / 4;
+    for (int slot = 0; slot < cap; ++slot)
+      for (int kb = 0; kb < k_elems / 128; ++kb) {
+        const int r = slot & 127;
+        const uint64_t off = (static_cast<uint64_t>(slot >> 7) * kg4 + (kb >> 2)) * 512u + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3);
+        EXPECT(off < bytes);
+        if (off < bytes) { EXPECT(seen[off] == 0); seen[off] = 1; }
+      }
+  }
+  std::printf(failures ? "%d expectation(s) failed\n" : "ok\n", failures);
+  return failures ? 1 : 0;
+}

@@ -196,42 +196,78 @@ def test_repeat_runs_are_deterministic():
 
 # ------------------------------------------------------------------------------ full-size configurations
 
-def _full_size(name, n_check=24):
+def _coverage_tokens(sorted_tok, npp, mblk_cum, T, n_blocks_wanted, rng):
+    """Tokens that cover every expert that received rows and the first and the last live slot
+    of at least `n_blocks_wanted` row blocks (all of them when there are fewer), plus a few
+    random tokens."""
+    n_blocks = npp // 128
+    blocks = np.arange(n_blocks)
+    if n_blocks > n_blocks_wanted:
+        # every expert's first and last block, then evenly spread ones
+        edges = np.unique(np.concatenate([mblk_cum[:-1][np.diff(mblk_cum) > 0], mblk_cum[1:][np.diff(mblk_cum) > 0] - 1]))
+        rest = rng.choice(n_blocks, size=n_blocks_wanted, replace=False)
+        blocks = np.unique(np.concatenate([edges, rest]))
+    sel = []
+    for b in blocks:
+        seg = sorted_tok[b * 128:(b + 1) * 128]
+        live = np.nonzero(seg < T)[0]
+        if len(live):
+            sel += [int(seg[live[0]]), int(seg[live[-1]])]
+    sel += rng.choice(T, size=min(8, T), replace=False).tolist()
+    return np.unique(np.array(sel, dtype=np.int32))
+
+
+def _full_size(name, n_blocks_wanted=64):
     """Inputs generated on the device at the configuration's full size (the benchmark's own
-    generator); the oracle evaluates a random subset of tokens (each token's output depends
-    only on its own row)."""
+    generator).  The oracle evaluates the tokens that sit in the first and the last live slot of
+    at least 64 row blocks -- every expert's first and last block among them -- so every expert
+    and the block boundaries of the tile schedule are looked at (each token's output depends only
+    on its own row)."""
     import bench
     c = bench.CONFIGS[name]
-    quant, T = c["quant"], c["T"]
+    quant, T, E = c["quant"], c["T"], c["E"]
     d = bench.device_inputs(c, torch.device("cuda:0"))
     args = M.FusedMoeArgs(a=d["x"], g=d["w1"], d=d["w2"], topk_ids=d["ids"], topk_weight=d["w"],
                           g_scale=d["s1"], d_scale=d["s2"])
     out = M.fused_moe(traits_for(quant), args)
     torch.cuda.synchronize()
     assert api.check_status(args.workspace) == 0
-    sel = np.random.default_rng(1).choice(T, size=min(n_check, T), replace=False).astype(np.int32)
+    lay = M.workspace_layout(traits_for(quant), args)
+    ws, cap = args.workspace, lay["capacity"]
+    tok = ws[lay["sorted_token_ids"]:lay["sorted_token_ids"] + 4 * cap].view(torch.int32).cpu().numpy()
+    cum = ws[lay["mblk_cum"]:lay["mblk_cum"] + 4 * (E + 1)].view(torch.int32).cpu().numpy()
+    npp = int(ws[lay["meta"]:lay["meta"] + 4].view(torch.int32).item())
+    sel = _coverage_tokens(tok, npp, cum, T, n_blocks_wanted, np.random.default_rng(1))
+    ids_h = d["ids"].cpu().numpy()
+    hit = np.unique(ids_h[sel])
+    assert set(hit.tolist()) == set(np.unique(ids_h).tolist()), "every expert with rows is covered"
     w1 = out_bits(d["w1"]) if quant == 0 else d["w1"].cpu().numpy()
     w2 = out_bits(d["w2"]) if quant == 0 else d["w2"].cpu().numpy()
-    ref = O.fused_moe(out_bits(d["x"]), w1, w2, d["ids"].cpu().numpy(), d["w"].cpu().numpy(), quant,
+    ref = O.fused_moe(out_bits(d["x"]), w1, w2, ids_h, d["w"].cpu().numpy(), quant,
                       None if d["s1"] is None else d["s1"].cpu().numpy(),
                       None if d["s2"] is None else d["s2"].cpu().numpy(), sel=sel)
     check(dict(quant=quant), out_bits(out)[sel], ref)
+    return len(sel)
 
 
 def test_full_size_mixtral_prefill_bf16():
-    _full_size("C1")
+    assert _full_size("C1") >= 128
 
 
 def test_full_size_mixtral_prefill_fp8():
-    _full_size("C2")
+    assert _full_size("C2") >= 128
 
 
 def test_full_size_decode_fp8():
-    _full_size("C3", n_check=16)
+    assert _full_size("C3") == 16
 
 
 def test_full_size_deepseek_block_scaled_fp8():
-    _full_size("C4", n_check=16)
+    assert _full_size("C4", n_blocks_wanted=256) >= 512
+
+
+def test_full_size_deepseek_block_scaled_fp8_power_of_two_scales():
+    assert _full_size("C4m", n_blocks_wanted=256) >= 512
 
 
 def test_deepseek_shape_block_scaled_reduced():

@@ -1,0 +1,198 @@
+"""Stage-level GPU tests: the byte and integer results the operator leaves in its workspace
+(e4m3 rows, their scales) compared bit for bit with the CPU oracle, the torch-CPU fixture
+through the CUDA path, and the checked build of the library."""
+import ctypes
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+import therock_b200 as M
+from therock_b200 import api
+from tests.golden import torch_reference as TR
+from tests.util import args_for, out_bits, rel_l2, run_gpu, traits_for
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def ws_region(args, lay, name, nbytes, dtype):
+    return args.workspace[lay[name]:lay[name] + nbytes].view(dtype).cpu().numpy()
+
+
+def unpack_scales(img, cap, groups):
+    """Packed UE8M0 image -> [cap, groups] scale values (2^(byte-127))."""
+    kg4 = (groups + 3) // 4
+    slot = np.arange(cap)[:, None]
+    kb = np.arange(groups)[None, :]
+    r = slot % 128
+    off = ((slot // 128) * kg4 + kb // 4) * 512 + (r % 32) * 16 + (r // 32) * 4 + kb % 4
+    return np.ldexp(1.0, img[off].astype(np.int32) - 127).astype(np.float32)
+
+
+def special_rows(d):
+    """An all-zero row, a row of one repeated value (every element lands on +-448), a row with
+    one huge outlier, and a row of tiny values."""
+    x = O.bf16_to_f32(d["x"]).copy()
+    x[1] = 0.0
+    x[2] = np.where(np.arange(x.shape[1]) % 2 == 0, 3.0, -3.0)
+    x[3, 5] = 30000.0
+    x[4] *= 1e-30
+    d["x"] = O.f32_to_bf16(x)
+    return d
+
+
+@pytest.mark.parametrize("quant", [1, 2, 3])
+def test_gathered_activation_bytes_and_scales_are_bit_exact(quant):
+    T, H, I, E, K = 150, 512, 256, 6, 2
+    d = special_rows(O.make_inputs(T, H, I, E, K, quant, "softmax", seed=21))
+    _, args = run_gpu(d)
+    lay = M.workspace_layout(traits_for(quant), args)
+    cap = lay["capacity"]
+    tok = ws_region(args, lay, "sorted_token_ids", cap * 4, torch.int32)
+    npp = int(ws_region(args, lay, "meta", 8, torch.int32)[0])
+    a_q = ws_region(args, lay, "a_sorted", cap * H, torch.uint8).reshape(cap, H)
+    group = H if quant == 1 else 128
+    groups = H // group
+    xf = O.bf16_to_f32(d["x"])
+    ref_q, ref_s = O.quant_rows_e4m3(xf, group, pow2=(quant == 3))
+    if quant == 3:
+        got_s = unpack_scales(ws_region(args, lay, "a_scale", lay["y"] - lay["a_scale"], torch.uint8), cap, groups)
+    else:
+        got_s = ws_region(args, lay, "a_scale", cap * groups * 4, torch.float32).reshape(cap, groups)
+    live = tok[:npp] < T
+    assert live.sum() == (np.logical_and(d["topk_ids"] >= 0, d["topk_ids"] < E)).sum()
+    t_live = tok[:npp][live]
+    assert (a_q[:npp][live] == ref_q[t_live]).all()
+    assert (got_s[:npp][live].view(np.uint32) == ref_s[t_live].view(np.uint32)).all()
+    # pad slots inside the padded range hold zero rows with scale 1
+    assert (a_q[:npp][~live] == 0).all()
+    assert (got_s[:npp][~live] == 1.0).all()
+
+
+def test_intermediate_bytes_are_the_oracle_quantisation_of_the_stored_intermediate():
+    """token_channel mode keeps the bf16 intermediate: its e4m3 copy and the per-row scales must
+    be exactly what the oracle's quantiser makes of those bf16 values."""
+    T, H, I, E, K = 150, 512, 384, 6, 2
+    d = O.make_inputs(T, H, I, E, K, 1, "softmax", seed=22)
+    _, args = run_gpu(d)
+    lay = M.workspace_layout(traits_for(1), args)
+    cap = lay["capacity"]
+    rows = ws_region(args, lay, "sorted_rows", cap * 4, torch.int32)
+    y = O.bf16_to_f32(ws_region(args, lay, "y", cap * I * 2, torch.int16).view(np.uint16).reshape(cap, I))
+    yq = ws_region(args, lay, "y_quant", cap * I, torch.uint8).reshape(cap, I)
+    ys = ws_region(args, lay, "y_scale", cap * 4, torch.float32)
+    live = rows >= 0
+    ref_q, ref_s = O.quant_rows_e4m3(y[live], I)
+    assert (yq[live] == ref_q).all()
+    assert (ys[live].view(np.uint32) == ref_s[:, 0].view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("quant", [2, 3])
+def test_fused_intermediate_quantisation_of_the_block_scaled_modes(quant):
+    """The block-scaled modes quantise the intermediate inside the first GEMM (no bf16 copy is
+    kept).  Their e4m3 bytes and 1x128 scales are checked against the intermediate the numpy
+    restatement computes for the same (token, expert) rows: scales follow the mode's rule from a
+    group maximum that agrees to rounding, and the dequantised values agree to e4m3 precision."""
+    T, H, I, E, K = 96, 512, 256, 4, 2
+    d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=23)
+    _, args = run_gpu(d)
+    lay = M.workspace_layout(traits_for(quant), args)
+    cap = lay["capacity"]
+    rows = ws_region(args, lay, "sorted_rows", cap * 4, torch.int32)
+    yq = ws_region(args, lay, "y_quant", cap * I, torch.uint8).reshape(cap, I)
+    groups = I // 128
+    if quant == 3:
+        ys = unpack_scales(ws_region(args, lay, "y_scale", lay["slots"] - lay["y_scale"], torch.uint8), cap, groups)
+    else:
+        ys = ws_region(args, lay, "y_scale", cap * groups * 4, torch.float32).reshape(cap, groups)
+    x = O.bf16_to_f32(d["x"])
+    tab = O.np_e4m3_table()
+    checked = 0
+    for slot in np.nonzero(rows >= 0)[0][::7]:
+        t, k = divmod(int(rows[slot]), K)
+        e = int(d["topk_ids"][t, k])
+        q, s = O.np_quant(x[t:t + 1], 128, quant == 3)
+        wf = tab[d["w1"][e]]
+        gu = np.zeros(2 * I, np.float32)
+        for kb in range(H // 128):
+            part = tab[q[0, kb * 128:(kb + 1) * 128]] @ wf[:, kb * 128:(kb + 1) * 128].T
+            gu += part * s[0, kb] * np.repeat(d["w1_scale"][e][:, kb], 128)
+        g, u = gu[:I], gu[I:]
+        y_ref = O.bf16_to_f32(O.np_f32_to_bf16((g / (1 + np.exp(-g))) * u))
+        amax = np.abs(y_ref).reshape(groups, 128).max(axis=1)
+        want = amax / 448.0
+        if quant == 3:
+            assert (np.log2(ys[slot]) == np.round(np.log2(ys[slot]))).all()
+            assert (ys[slot] >= want * 0.99).all() and (ys[slot] <= want * 2.02).all()
+        else:
+            np.testing.assert_allclose(ys[slot], want, rtol=1e-2)
+        deq = (tab[yq[slot]].reshape(groups, 128) * ys[slot][:, None]).reshape(-1)
+        assert np.abs(deq - y_ref).max() <= (amax.max() / 448.0) * 16 * 2.1 + 1e-6     # half an e4m3 step at the top binade, doubled
+        assert float(np.linalg.norm(deq - y_ref) / np.linalg.norm(y_ref)) < 4e-2
+        checked += 1
+    assert checked >= 10
+
+
+@pytest.mark.parametrize("name", sorted(TR.FIXTURE_SHAPES))
+@pytest.mark.parametrize("quant", [0, 1, 2, 3])
+def test_cuda_path_matches_the_torch_cpu_fixture(name, quant):
+    """The committed fixture was computed by plain torch CPU ops (tests/golden/torch_reference.py)."""
+    npz = np.load(os.path.join(ROOT, "tests", "golden", "torch_ref.npz"))
+    d, out, out_pb = TR.load_fixture_case(npz, name, quant)
+    for partial, ref in (("f32", out), ("bf16", out_pb)):
+        got, _ = run_gpu(d, partial)
+        g, r = O.bf16_to_f32(got), O.bf16_to_f32(ref)
+        if quant == 0:
+            np.testing.assert_allclose(g, r, rtol=1e-2, atol=1e-2)
+        assert rel_l2(got, ref) <= (2e-3 if quant == 0 else 4e-2)
+
+
+def test_k_larger_than_the_expert_count_with_padded_id_lists():
+    """A rank of a de-duplicated expert-parallel dispatch sees K-wide id lists padded with -1
+    and may own fewer than K experts."""
+    T, H, I, E, K = 64, 256, 128, 2, 5
+    d = O.make_inputs(T, H, I, E, 2, 0, "softmax", seed=24)
+    ids = np.full((T, K), -1, np.int32)
+    w = np.zeros((T, K), np.float32)
+    ids[:, 1], ids[:, 3] = d["topk_ids"][:, 0], d["topk_ids"][:, 1]
+    w[:, 1], w[:, 3] = d["topk_w"][:, 0], d["topk_w"][:, 1]
+    d2 = dict(d, topk_ids=ids, topk_w=w)
+    got, _ = run_gpu(d2)
+    ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], 0)
+    assert (got == ref).all() or rel_l2(got, ref) < 2e-3
+
+
+CHECKED_DRIVER = r"""
+import ctypes, os, sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+import therock_b200.api as api
+api.LIB_PATH = sys.argv[2]                      # the checked build instead of the product library
+import therock_b200 as M
+from oracle import oracle as O
+from tests.util import run_gpu, run_oracle, rel_l2
+for quant in (0, 1, 2, 3):
+    for partial in ("f32", "bf16"):
+        d = O.make_inputs(200, 512, 256, 6, 2, quant, "softmax", seed=31)
+        got, args = run_gpu(d, partial)          # asserts status word == 0
+        assert rel_l2(got, run_oracle(d, partial=partial)) < 4e-2
+print("checked build ok")
+"""
+
+
+def test_checked_build_reports_no_bounds_violation(tmp_path):
+    """A second library built with -DFMOE_BOUNDS_CHECKS compares every computed output row with
+    its bound before the store and reports a violation through the status word; here it runs the
+    four quantisation modes and must stay silent while producing the same results."""
+    from therock_b200 import build
+    lib = build.build(checked=True)
+    drv = tmp_path / "drv.py"
+    drv.write_text(CHECKED_DRIVER)
+    r = subprocess.run([sys.executable, str(drv), ROOT, lib], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "checked build ok" in r.stdout

@@ -30,7 +30,21 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, checked: bool = False, timing_switches: bool = False) -> str:
+    """Builds the product library, or with checked=True libfmoe_b200_checked.so (the same
+    sources with -DFMOE_BOUNDS_CHECKS), or with timing_switches=True libfmoe_b200_timing.so
+    (-DFMOE_TIMING_SWITCHES: FMOE_DEBUG_FLAGS / FMOE_GEMM_MODE are honoured; results are invalid
+    while they are set).  The variants never replace the product library."""
+    if checked or timing_switches:
+        return _build_variant("checked" if checked else "timing",
+                              ["-DFMOE_BOUNDS_CHECKS"] if checked else ["-DFMOE_TIMING_SWITCHES"], force, verbose)
+    return _build_variant("", [], force, verbose)
+
+
+def _build_variant(suffix: str, defines: list, force: bool, verbose: bool) -> str:
+    OBJ_DIR = os.path.join(HERE, "build" + ("_" + suffix if suffix else ""))
+    LIB = os.path.join(HERE, "libfmoe_b200" + ("_" + suffix if suffix else "") + ".so")
+    NVCC_FLAGS = globals()["NVCC_FLAGS"] + defines
     os.makedirs(OBJ_DIR, exist_ok=True)
     hdrs = [os.path.join(CSRC, h) for h in HEADERS]
     jobs = []
@@ -65,4 +79,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    print(build(force="--force" in sys.argv, verbose=True, checked="--checked" in sys.argv,
+                timing_switches="--timing-switches" in sys.argv))
