@@ -628,7 +628,7 @@ def measure_ep(env, a, c, sampler):
     if os.environ.get("FMOE_EP_MODE", "peer") != "nccl":
         try:
             moe = ep.PeerExpertParallelMoE(c["E"], world, rank, traits, d["w1"], d["w2"], d["s1"], d["s2"],
-                                           tokens_per_rank=T_local, topk=c["K"], hidden=H)
+                                           tokens_per_rank=T_local, topk=c["K"], hidden=H, fused=a.ep_fused == "on")
             ep_transport = "peer_memory"
         except Exception as exc:  # noqa: BLE001
             if rank == 0:
@@ -659,6 +659,7 @@ def measure_ep(env, a, c, sampler):
     res["config"]["launch"] = "stream"
     res["config"]["weight_layout"] = a.weight_layout
     res["config"]["ep_transport"] = ep_transport
+    res["config"]["ep_step"] = "fused kernels" if getattr(moe, "fused", False) else "single-purpose kernels"
     if a.kernel_only:
         return res, None
 
@@ -810,6 +811,8 @@ def main():
                     help="how the K weighted expert outputs are held before the ordered sum")
     ap.add_argument("--per-config", choices=["on", "off"], default="on",
                     help="single GPU, default workload: also measure C2, C3, C4 and attach them as per_config")
+    ap.add_argument("--ep-fused", choices=["on", "off"], default="on",
+                    help="N > 1, peer memory: the fused step (send / recv_ready / wait_combine) or the single-purpose kernels")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-resident timed loop: no stage profile, e2e or CPU baseline")
     a = ap.parse_args()

@@ -48,6 +48,7 @@ struct fused_moe_args {
   int topk = 0;
   const int32_t* num_tokens_dev_ptr = nullptr;  // optional device-side token count (<= num_tokens)
   int expected_tokens = 0;                      // its typical value (kernel choice hint), 0 = num_tokens
+  const uint64_t* partial_row_ptrs = nullptr;   // optional [T*K] destinations of the weighted partial rows (bf16)
 };
 
 struct stream_config {
@@ -90,6 +91,7 @@ inline void to_c(const fused_moe_args& a, fmoe_args_c* c) {
   c->E = a.num_experts; c->K = a.topk;
   c->num_tokens_dev = a.num_tokens_dev_ptr;
   c->expected_tokens = a.expected_tokens;
+  c->partial_row_ptrs = a.partial_row_ptrs;
 }
 }  // namespace fmoe_detail
 

@@ -118,6 +118,23 @@ typedef struct fmoe_args_c {
                                     tokens are processed (T still sizes the workspace); used when
                                     the batch size is only known on the device, e.g. on the
                                     receiving side of an expert-parallel dispatch.  NULL = T. */
+  /* Scattered partial rows (optional; expert parallelism).  When set, traits.partial_dtype must
+   * be bf16, the weighted output row of routed pair (t, k) is stored as bf16 at the device
+   * address partial_row_ptrs[t*K + k] (which may lie in a peer GPU's memory: plain stores), `out`
+   * is not written and no combine runs -- whoever owns those rows adds them up
+   * (fmoe_ep_wait_combine).  Entries of pairs whose expert id is outside [0, E) are not read. */
+  const uint64_t* partial_row_ptrs;
+  /* Completion signal (optional; used with partial_row_ptrs).  When the last CTA of the second
+   * GEMM has stored its rows it writes *done_flag_value, with release semantics at system scope,
+   * to each of the done_flag_count addresses in done_flag_addrs (a device array; the addresses
+   * may be peer memory), so a consumer on another GPU can wait for the rows without another
+   * kernel launch.  done_counter is one zero-initialised device int32 the library uses to find
+   * the last CTA; it is left at zero. */
+  const uint64_t* done_flag_addrs;
+  const int32_t* done_flag_value;
+  int32_t* done_counter;
+  int32_t done_flag_count;
+  int32_t reserved2;
 } fmoe_args_c;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -162,8 +179,8 @@ typedef struct fmoe_ws_layout_c {
   uint64_t mblk_cum;          /* int32[E+1]: cumulative blocks per expert */
   uint64_t a_sorted;          /* [capacity, H] activations in sorted order (bf16 or e4m3) */
   uint64_t a_scale;           /* quant 1: float[capacity]; quant 2: float[capacity, H/128]; quant 3: one UE8M0
-                                 byte per row and 128-wide K group, per (128-row block, four K groups) a
-                                 512-byte image: byte (row%32)*16 + (row/32)*4 + group%4 */
+                                 byte (biased exponent) per row and 128-wide K group, row-major, rows
+                                 padded to a multiple of four bytes */
   uint64_t y;                 /* bf16 [capacity, I]: SiLU(gate)*up (quant 0, 1; the block-scaled modes
                                  quantise inside the first GEMM and keep no bf16 copy) */
   uint64_t y_quant;           /* e4m3 [capacity, I] (fp8 variants) */
@@ -250,6 +267,8 @@ typedef struct fmoe_ep_layout_c {
   uint64_t back;     /* bf16 [send_cap, H]: expert outputs returned to this rank */
   int64_t recv_cap;  /* rows the receive arrays hold (>= all routed pairs of the step) */
   int64_t send_cap;  /* rows of `back` (>= T*K of this rank) */
+  uint64_t flags_dispatch; /* int32[G]: epoch at which each peer finished writing its rows here (fused path) */
+  uint64_t flags_return;   /* int32[G]: epoch at which each peer finished returning this rank's rows (fused path) */
 } fmoe_ep_layout_c;
 
 /* Groups this rank's T*K routed pairs by the rank that owns the expert (stable):
@@ -283,6 +302,41 @@ FMOE_API int fmoe_ep_dispatch(const void* x, const int32_t* topk_ids, const floa
 FMOE_API int fmoe_ep_return(const void* out_rows, int32_t H, const int32_t* n_recv_dev,
                             const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
                             int32_t G, void* stream);
+
+/* ---- Fused expert-parallel step (one process per GPU, at most 16 ranks): three kernels around the
+ * local operator instead of eight.  All three read the step's epoch from the device word
+ * `epoch_dev` (initialise it to 1); fmoe_ep_wait_combine advances it when the step is over, so the
+ * launch arguments never change and a step can be captured in a CUDA graph.  Every wait is
+ * bounded (timeout_ms, 0 = about four seconds): on expiry `status` receives 0x300 | rank-not-seen
+ * (0x310 for the kernel's own grid barrier) and the kernel carries on without hanging the GPU.
+ *
+ * fmoe_ep_send: buckets this rank's T*K routed pairs by owner rank (stable), publishes the counts
+ * to every rank, waits for everybody's counts, stores each token row with its local expert id,
+ * weight and return address (source rank, pair index) into the owner's receive arrays, writes this
+ * rank's received-row count to n_recv_dev and finally tells every rank that its rows are complete.
+ * The kernel's CTAs meet at a barrier of their own: it must run with the GPU otherwise idle (it is
+ * launched without programmatic overlap, after everything earlier on the stream).
+ * scratch: int32[fmoe_ep_send_scratch_words(T, K, G)], zero-initialised once. */
+FMOE_API int64_t fmoe_ep_send_scratch_words(int32_t T, int32_t K, int32_t G);
+FMOE_API int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                          int32_t H, int32_t experts_per_rank, const uint64_t* peer_base,
+                          const fmoe_ep_layout_c* lay, int32_t me, int32_t G, int32_t* scratch,
+                          const int32_t* epoch_dev, int32_t* n_recv_dev, int32_t* status, int32_t timeout_ms,
+                          void* stream);
+/* Waits until every rank's rows have arrived and fills row_ptrs[i] (i < *n_recv_dev) with the
+ * address, in the source rank's `back` array, where the result of received row i belongs: the
+ * partial_row_ptrs of the local fmoe_run. */
+FMOE_API int fmoe_ep_recv_ready(int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base,
+                                const fmoe_ep_layout_c* lay, int32_t me, int32_t G, const int32_t* epoch_dev,
+                                uint64_t* row_ptrs, int32_t* status, int32_t timeout_ms, void* stream);
+/* Waits until every rank has returned this rank's rows (the done_flag_* signal of their local
+ * fmoe_run, aimed at flags_return) and adds them up: out[t] = bf16(sum over k ascending of
+ * back[t*K + k]) in f32, pairs with an expert id outside [0, num_experts) skipped.  Advances the
+ * epoch.  sync_counter: one zero-initialised device int32. */
+FMOE_API int fmoe_ep_wait_combine(const int32_t* topk_ids, int32_t T, int32_t K, int32_t H, int32_t num_experts,
+                                  const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
+                                  int32_t* epoch_dev, int32_t* sync_counter, void* out, int32_t* status,
+                                  int32_t timeout_ms, void* stream);
 
 /* What one fmoe_run with these traits and dimensions will launch on the current device: the
  * kernel flavour of each GEMM (the same decision fmoe_run takes) and the number of kernels

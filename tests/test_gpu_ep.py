@@ -22,10 +22,11 @@ def _free_port():
 
 
 def _close(got_bits, ref_bits, quant):
+    """The operator's own tolerances.  The expert-parallel paths return each (token, k) partial
+    row as bf16, so their reference is the oracle's bf16-partial mode (partial_bf16=True)."""
     g, r = O.bf16_to_f32(got_bits), O.bf16_to_f32(ref_bits)
-    # returned partial rows are bf16: one extra rounding per term compared with fused_moe
-    return (np.allclose(g, r, rtol=2e-2, atol=1e-2) or quant != 0) and \
-        np.linalg.norm(g - r) <= (6e-3 if quant == 0 else 4e-2) * np.linalg.norm(r)
+    return (np.allclose(g, r, rtol=1e-2, atol=1e-2) or quant != 0) and \
+        np.linalg.norm(g - r) <= (2e-3 if quant == 0 else 4e-2) * np.linalg.norm(r)
 
 
 def _rank_forward(d, rank, world, device, dedup=False):
@@ -57,7 +58,8 @@ def test_single_rank_expert_parallel_path(quant):
     d = O.make_inputs(200, 512, 256, 8, 2, quant, "softmax", seed=21)
     d["topk_ids"][::9, 1] = -1
     got, _ = _rank_forward(d, 0, 1, "cuda:0")
-    ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"])
+    ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
+                      partial_bf16=True)
     assert _close(got, ref, quant)
 
 
@@ -68,11 +70,12 @@ def test_single_rank_deduplicated_dispatch(quant):
     d = O.make_inputs(200, 512, 256, 8, 3, quant, "softmax", seed=22)
     d["topk_ids"][::7, 2] = -1
     got, _ = _rank_forward(d, 0, 1, "cuda:0", dedup=True)
+    # one rank owns every expert: the token's K terms are summed in f32 inside the operator
     ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"])
     assert _close(got, ref, quant)
 
 
-def _peer_worker(rank, world, port, quant, ret):
+def _peer_worker(rank, world, port, quant, ret, fused=True):
     import torch.distributed as dist
     from therock_b200 import ep
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
@@ -94,10 +97,10 @@ def _peer_worker(rank, world, port, quant, ret):
         t_local = T // world
         sl = slice(rank * t_local, (rank + 1) * t_local)
         moe = ep.PeerExpertParallelMoE(E, world, rank, traits_for(quant), w1, w2, s1, s2,
-                                       tokens_per_rank=t_local, topk=K, hidden=H)
+                                       tokens_per_rank=t_local, topk=K, hidden=H, fused=fused)
         x, ids, w = bf16_dev(d["x"][sl], dev), to_dev(d["topk_ids"][sl], device=dev), to_dev(d["topk_w"][sl], device=dev)
         ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
-                          sel=np.arange(sl.start, sl.stop, dtype=np.int32))
+                          sel=np.arange(sl.start, sl.stop, dtype=np.int32), partial_bf16=True)
         ok = True
         for _ in range(3):      # repeated steps reuse the same peer buffers
             out = moe.forward(x, ids, w)
@@ -107,15 +110,32 @@ def _peer_worker(rank, world, port, quant, ret):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("quant", [0, 1, 3])
+def test_peer_memory_step_with_a_single_rank(quant, fused):
+    """World size 1: the whole peer-memory step (fused: send, recv_ready, the operator storing
+    its partial rows through the return-address table and signalling, wait_combine) on one GPU,
+    where every flag this rank waits for is its own."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    p = ctx.Process(target=_peer_worker, args=(0, 1, _free_port(), quant, ret, fused))
+    p.start()
+    p.join(300)
+    assert p.exitcode == 0
+    assert ret.get(0), dict(ret)
+
+
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("quant", [0, 1])
-def test_two_gpu_peer_memory_expert_parallel(quant):
+def test_two_gpu_peer_memory_expert_parallel(quant, fused):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, quant, ret)) for r in range(2)]
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, quant, ret, fused)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -133,8 +153,9 @@ def _worker(rank, world, port, quant, ret, dedup=False):
         d = O.make_inputs(256, 512, 256, 8, 4 if dedup else 2, quant, "softmax", seed=22)
         got, sl = _rank_forward(d, rank, world, f"cuda:{rank}", dedup=dedup)
         ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
-                          sel=np.arange(sl.start, sl.stop, dtype=np.int32))
-        ret[rank] = bool(_close(got, ref, quant))
+                          sel=np.arange(sl.start, sl.stop, dtype=np.int32), partial_bf16=not dedup)
+        ret[rank] = bool(_close(got, ref, quant)) if not dedup else bool(
+            np.linalg.norm(O.bf16_to_f32(got) - O.bf16_to_f32(ref)) <= 4e-2 * np.linalg.norm(O.bf16_to_f32(ref)))
     finally:
         dist.destroy_process_group()
 
@@ -189,3 +210,66 @@ def test_barrier_wait_is_bounded_when_a_rank_never_arrives():
     torch.cuda.synchronize()
     assert rc == 0 and int(status.item()) == 0 and int(counter.item()) == 3
     assert int(theirs[:8].view(torch.int32)[0].item()) == 3
+
+
+def _fake_two_rank_layout(dev, T, K, H):
+    """Two full peer buffers on one GPU: rank 0 is driven by the test, rank 1 never acts."""
+    from therock_b200 import api
+    lay = api.EpLayout()
+    R, world = T * K, 2
+    recv_cap, off = R * world, 0
+    for name, nbytes in (("flags", 8), ("flags_dispatch", 8), ("flags_return", 8), ("matrix", 16),
+                         ("rows", recv_cap * H * 2), ("ids", recv_cap * 4), ("weights", recv_cap * 4),
+                         ("src", recv_cap * 8), ("back", R * H * 2)):
+        setattr(lay, name, off)
+        off = (off + nbytes + 255) // 256 * 256
+    lay.recv_cap, lay.send_cap = recv_cap, R
+    mine = torch.zeros(off, dtype=torch.uint8, device=dev)
+    theirs = torch.zeros(off, dtype=torch.uint8, device=dev)
+    peer_base = torch.tensor([mine.data_ptr(), theirs.data_ptr()], dtype=torch.int64, device=dev)
+    return lay, mine, theirs, peer_base
+
+
+def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
+    """Failure detection for the fused kernels without a fault: rank 1 of a two-rank step never
+    writes any flag.  Each of the three kernels must give up after its 50 ms limit, report rank 1
+    in the status word and return, leaving the context usable."""
+    import ctypes
+    from therock_b200 import api
+    dev = "cuda:0"
+    T, K, H, e_local = 64, 2, 256, 4
+    lay, mine, theirs, peer_base = _fake_two_rank_layout(dev, T, K, H)
+    lib, by = api.lib(), ctypes.byref
+    st = torch.cuda.current_stream().cuda_stream
+    d = O.make_inputs(T, H, 128, 2 * e_local, K, 0, "softmax", seed=41)
+    x, ids, w = bf16_dev(d["x"], dev), to_dev(d["topk_ids"], device=dev), to_dev(d["topk_w"], device=dev)
+    epoch = torch.ones(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    n_recv = torch.zeros(1, dtype=torch.int32, device=dev)
+    scratch = torch.zeros(int(lib.fmoe_ep_send_scratch_words(T, K, 2)), dtype=torch.int32, device=dev)
+    rc = lib.fmoe_ep_send(x.data_ptr(), ids.data_ptr(), w.data_ptr(), T, K, H, e_local, peer_base.data_ptr(), by(lay),
+                          0, 2, scratch.data_ptr(), epoch.data_ptr(), n_recv.data_ptr(), status.data_ptr(), 50, st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == (0x300 | 1)
+    # our own counts and the completion flag were still published to the silent rank
+    assert int(theirs[lay.flags:lay.flags + 4].view(torch.int32).item()) == 1
+    assert int(theirs[lay.flags_dispatch:lay.flags_dispatch + 4].view(torch.int32).item()) == 1
+    assert int(scratch[:2].abs().sum().item()) == 0                  # the kernel's own counters are back at zero
+    status.zero_()
+    row_ptrs = torch.zeros(int(lay.recv_cap), dtype=torch.int64, device=dev)
+    rc = lib.fmoe_ep_recv_ready(H, n_recv.data_ptr(), peer_base.data_ptr(), by(lay), 0, 2, epoch.data_ptr(),
+                                row_ptrs.data_ptr(), status.data_ptr(), 50, st)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == (0x300 | 1)
+    status.zero_()
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    sync = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = lib.fmoe_ep_wait_combine(ids.data_ptr(), T, K, H, 2 * e_local, peer_base.data_ptr(), by(lay), 0, 2,
+                                  epoch.data_ptr(), sync.data_ptr(), out.data_ptr(), status.data_ptr(), 50, st)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == (0x300 | 1)
+    assert int(epoch.item()) == 2 and int(sync.item()) == 0          # the step was closed all the same
+    # the context is healthy: a plain operator call still works
+    from tests.util import run_gpu
+    run_gpu(d)

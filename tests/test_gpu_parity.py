@@ -237,7 +237,8 @@ def _full_size(name, n_blocks_wanted=64):
     tok = ws[lay["sorted_token_ids"]:lay["sorted_token_ids"] + 4 * cap].view(torch.int32).cpu().numpy()
     cum = ws[lay["mblk_cum"]:lay["mblk_cum"] + 4 * (E + 1)].view(torch.int32).cpu().numpy()
     npp = int(ws[lay["meta"]:lay["meta"] + 4].view(torch.int32).item())
-    sel = _coverage_tokens(tok, npp, cum, T, n_blocks_wanted, np.random.default_rng(1))
+    sel = (np.arange(T, dtype=np.int32) if T <= 64 else
+           _coverage_tokens(tok, npp, cum, T, n_blocks_wanted, np.random.default_rng(1)))
     ids_h = d["ids"].cpu().numpy()
     hit = np.unique(ids_h[sel])
     assert set(hit.tolist()) == set(np.unique(ids_h).tolist()), "every expert with rows is covered"

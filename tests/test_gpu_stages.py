@@ -25,13 +25,10 @@ def ws_region(args, lay, name, nbytes, dtype):
 
 
 def unpack_scales(img, cap, groups):
-    """Packed UE8M0 image -> [cap, groups] scale values (2^(byte-127))."""
-    kg4 = (groups + 3) // 4
-    slot = np.arange(cap)[:, None]
-    kb = np.arange(groups)[None, :]
-    r = slot % 128
-    off = ((slot // 128) * kg4 + kb // 4) * 512 + (r % 32) * 16 + (r // 32) * 4 + kb % 4
-    return np.ldexp(1.0, img[off].astype(np.int32) - 127).astype(np.float32)
+    """UE8M0 bytes [cap, pitch] (pitch = groups rounded up to four) -> [cap, groups] scale values."""
+    pitch = (groups + 3) // 4 * 4
+    b = img[:cap * pitch].reshape(cap, pitch)[:, :groups]
+    return np.ldexp(1.0, b.astype(np.int32) - 127).astype(np.float32)
 
 
 def special_rows(d):

@@ -42,7 +42,10 @@ class _Args(ctypes.Structure):
                 ("workspace_bytes", ctypes.c_uint64),
                 ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("I", ctypes.c_int32),
                 ("E", ctypes.c_int32), ("K", ctypes.c_int32), ("expected_tokens", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 2), ("num_tokens_dev", ctypes.c_void_p)]
+                ("reserved", ctypes.c_int32 * 2), ("num_tokens_dev", ctypes.c_void_p),
+                ("partial_row_ptrs", ctypes.c_void_p), ("done_flag_addrs", ctypes.c_void_p),
+                ("done_flag_value", ctypes.c_void_p), ("done_counter", ctypes.c_void_p),
+                ("done_flag_count", ctypes.c_int32), ("reserved2", ctypes.c_int32)]
 
 
 class _Layout(ctypes.Structure):
@@ -55,7 +58,8 @@ class _Layout(ctypes.Structure):
 class EpLayout(ctypes.Structure):
     """Byte offsets inside the per-rank peer-addressable buffer (fmoe_ep_layout_c)."""
     _fields_ = [(n, ctypes.c_uint64) for n in ("flags", "matrix", "rows", "ids", "weights", "src", "back")] + \
-               [("recv_cap", ctypes.c_int64), ("send_cap", ctypes.c_int64)]
+               [("recv_cap", ctypes.c_int64), ("send_cap", ctypes.c_int64),
+                ("flags_dispatch", ctypes.c_uint64), ("flags_return", ctypes.c_uint64)]
 
 
 _lib: Optional[ctypes.CDLL] = None
@@ -105,6 +109,13 @@ def lib() -> ctypes.CDLL:
         l.fmoe_ep_dispatch.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, ctypes.POINTER(EpLayout),
                                        i32, i32, vp, vp]
         l.fmoe_ep_return.argtypes = [vp, i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp]
+        l.fmoe_ep_send_scratch_words.restype = ctypes.c_int64
+        l.fmoe_ep_send_scratch_words.argtypes = [i32, i32, i32]
+        l.fmoe_ep_send.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp,
+                                   vp, vp, i32, vp]
+        l.fmoe_ep_recv_ready.argtypes = [i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp, i32, vp]
+        l.fmoe_ep_wait_combine.argtypes = [vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp,
+                                           vp, i32, vp]
         _lib = l
     return _lib
 
@@ -167,6 +178,10 @@ class FusedMoeArgs:
     workspace: Optional[torch.Tensor] = None   # uint8, >= fused_moe_workspace_size bytes
     num_tokens_dev: Optional[torch.Tensor] = None  # int32[1] on the device: process only that many tokens
     expected_tokens: int = 0                   # typical value of num_tokens_dev (kernel choice hint)
+    partial_row_ptrs: Optional[torch.Tensor] = None  # int64 [T*K]: where each weighted partial row (bf16) goes
+    done_flag_addrs: Optional[torch.Tensor] = None   # int64 [n]: addresses that receive done_flag_value[0] at the end
+    done_flag_value: Optional[torch.Tensor] = None   # int32 [1] on the device
+    done_counter: Optional[torch.Tensor] = None      # int32 [1] on the device, zero
 
     def to_c(self, gate_only: bool = False) -> _Args:
         for name in ("a", "g", "d", "topk_ids", "topk_weight"):
@@ -196,6 +211,13 @@ class FusedMoeArgs:
         c.T, c.H, c.I, c.E, c.K = T, H, I, E, self.topk_ids.shape[1]
         c.num_tokens_dev = self.num_tokens_dev.data_ptr() if self.num_tokens_dev is not None else None
         c.expected_tokens = int(self.expected_tokens)
+        if self.partial_row_ptrs is not None:
+            c.partial_row_ptrs = self.partial_row_ptrs.data_ptr()
+        if self.done_flag_addrs is not None:
+            c.done_flag_addrs = self.done_flag_addrs.data_ptr()
+            c.done_flag_count = self.done_flag_addrs.numel()
+            c.done_flag_value = self.done_flag_value.data_ptr()
+            c.done_counter = self.done_counter.data_ptr()
         return c
 
 

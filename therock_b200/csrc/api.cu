@@ -163,10 +163,14 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     if (ms_out) *ms_out = 0.f;
     return FMOE_OK;
   }
-  if (!a.x || !a.w1 || !a.w2 || !a.topk_ids || !a.topk_weight || !a.out)
-    return fail(FMOE_ERR_INVALID_ARG, "x, w1, w2, topk_ids, topk_weight and out are required");
   const bool fp8 = fmoe::quant_is_fp8(traits->quant);
+  if (!a.x || !a.w1 || !a.w2 || !a.topk_ids || !a.topk_weight || (!a.out && !a.partial_row_ptrs))
+    return fail(FMOE_ERR_INVALID_ARG, "x, w1, w2, topk_ids, topk_weight and out are required");
   if (fp8 && (!a.w1_scale || !a.w2_scale)) return fail(FMOE_ERR_INVALID_ARG, "fp8 variants need w1_scale and w2_scale");
+  if (a.partial_row_ptrs && traits->partial_dtype != FMOE_PARTIAL_BF16)
+    return fail(FMOE_ERR_INVALID_ARG, "partial_row_ptrs needs partial_dtype = bf16");
+  if (a.done_flag_addrs && (!a.partial_row_ptrs || !a.done_flag_value || !a.done_counter || a.done_flag_count <= 0))
+    return fail(FMOE_ERR_INVALID_ARG, "done_flag_addrs needs partial_row_ptrs, done_flag_value, done_counter and a positive count");
   Plan plan;
   make_plan(traits, args, &plan);
   if (!a.workspace) return fail(FMOE_ERR_WORKSPACE, "workspace is null (%llu bytes needed)", (unsigned long long)plan.l.total_bytes);
@@ -282,6 +286,11 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   g.out_rows = static_cast<int64_t>(a.T) * a.K;
   g.out_scale = nullptr;
   g.out_bf16 = traits->partial_dtype == FMOE_PARTIAL_BF16;
+  g.row_ptrs = a.partial_row_ptrs;
+  g.done_addrs = a.done_flag_addrs;
+  g.done_value = a.done_flag_value;
+  g.done_counter = a.done_counter;
+  g.done_count = a.done_flag_count;
   {
     NvtxRange r("gemm2_weighted");
     if (fmoe::launch_grouped_gemm(g, stream, &drv) != cudaSuccess)
@@ -289,7 +298,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   }
   FMOE_STAGE(5);
 
-  {
+  if (!a.partial_row_ptrs) {    // scattered partial rows are added up by their owner
     NvtxRange r("combine");
     FMOE_CUDA(fmoe::launch_combine(slots, g.out_bf16, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream, a.num_tokens_dev));
   }

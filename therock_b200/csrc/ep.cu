@@ -11,6 +11,7 @@
 //   dispatch  : one CTA per send slot: token row + (local expert, weight, source) to the
 //               owner's receive arrays at  sum(counts of lower ranks) + index in my group
 //   return    : one CTA per received row: the expert output back to the source's slot
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "../../include/fused_moe_c.h"
@@ -112,6 +113,241 @@ ep_return_kernel(const uint4* __restrict__ out_rows, int H, const int32_t* __res
   for (int v = threadIdx.x; v < nvec; v += kEpThreads) dst[v] = src[v];
 }
 
+
+// ============================================================================= fused step
+// Three kernels around the local operator: send (plan + publish + wait + dispatch + signal),
+// recv_ready (wait + return-address table) and wait_combine (wait + ordered sum).
+
+constexpr int kSendThreads = 256;
+constexpr int kSendMaxRanks = 16;
+constexpr int kSendMaxChunk = 2048;       // routed pairs one CTA of the send kernel handles
+constexpr int kSendPairsPerCta = 8;       // target: enough CTAs to keep the links busy
+
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Thread p < G waits until flags[p] >= epoch; gives up after limit cycles and reports the rank.
+__device__ __forceinline__ void wait_flags(const int32_t* flags, int G, int epoch, long long limit, int32_t* status) {
+  const int p = threadIdx.x;
+  if (p < G) {
+    const long long t0 = clock64();
+    while (ld_acquire_sys(flags + p) < epoch) {
+      if (clock64() - t0 > limit) {
+        atomicExch(status, 0x300 | p);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+}
+
+struct EpSendParams {
+  const uint4* x;
+  const int32_t* topk_ids;
+  const float* topk_w;
+  int T, K, H, e_local;
+  const uint64_t* peer_base;
+  fmoe_ep_layout_c lay;
+  int me, G;
+  int32_t* cta_counts;     // [grid][G]
+  int32_t* sync;           // [0] grid barrier, [1] finished CTAs
+  const int32_t* epoch;
+  int32_t* n_recv_dev;
+  int32_t* status;
+  long long limit;
+};
+
+__global__ void __launch_bounds__(kSendThreads)
+ep_send_kernel(const EpSendParams p) {
+  __shared__ int32_t tcnt[kSendThreads][kSendMaxRanks];   // per thread and destination: count, then running offset
+  __shared__ int32_t dest_slot[kSendMaxChunk];
+  __shared__ int8_t dest_rank[kSendMaxChunk];
+  __shared__ int32_t cta_base[kSendMaxRanks], recv_base[kSendMaxRanks], total[kSendMaxRanks];
+  const int tid = threadIdx.x, G = p.G, C = gridDim.x;
+  const int R = p.T * p.K;
+  const int chunk = (R + C - 1) / C;
+  const int r0 = blockIdx.x * chunk;
+  const int n = max(0, min(R, r0 + chunk) - r0);
+  const int per = (chunk + kSendThreads - 1) / kSendThreads;   // consecutive pairs owned by one thread
+  const int epoch = *p.epoch;
+  const int n_exp = p.e_local * G;
+
+  // 1. destination of every pair of this CTA's chunk; counts per (thread, destination)
+  for (int d = 0; d < G; ++d) tcnt[tid][d] = 0;
+  for (int j = 0; j < per; ++j) {
+    const int i = tid * per + j;
+    if (i < n) {
+      const int e = p.topk_ids[r0 + i];
+      const int d = (e >= 0 && e < n_exp) ? e / p.e_local : -1;
+      dest_rank[i] = static_cast<int8_t>(d);
+      if (d >= 0) tcnt[tid][d]++;
+    }
+  }
+  __syncthreads();
+  if (tid < G) {
+    int run = 0;
+    for (int t = 0; t < kSendThreads; ++t) {
+      const int v = tcnt[t][tid];
+      tcnt[t][tid] = run;
+      run += v;
+    }
+    p.cta_counts[blockIdx.x * G + tid] = run;
+  }
+  // 2. all CTAs of this kernel meet (they are co-resident: at most one per SM, small footprint)
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    atomicAdd(&p.sync[0], 1);
+    const long long t0 = clock64();
+    while (atomicAdd(&p.sync[0], 0) < C) {
+      if (clock64() - t0 > p.limit) {
+        atomicExch(p.status, 0x310);
+        break;
+      }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  // 3. offsets of this CTA inside each destination's group; totals; CTA 0 publishes the totals
+  if (tid < G) {
+    int before = 0, all = 0;
+    for (int c = 0; c < C; ++c) {
+      const int v = __ldcg(&p.cta_counts[c * G + tid]);
+      if (c < static_cast<int>(blockIdx.x)) before += v;
+      all += v;
+    }
+    cta_base[tid] = before;
+    total[tid] = all;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < G * G; i += kSendThreads) {
+      const int peer = i / G, d = i % G;
+      peer_ptr<int32_t>(p.peer_base, peer, p.lay.matrix)[p.me * G + d] = total[d];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < G) st_release_sys(peer_ptr<int32_t>(p.peer_base, tid, p.lay.flags) + p.me, epoch);
+  }
+  // 4. everybody's counts
+  wait_flags(peer_ptr<int32_t>(p.peer_base, p.me, p.lay.flags), G, epoch, p.limit, p.status);
+  const int32_t* matrix = peer_ptr<int32_t>(p.peer_base, p.me, p.lay.matrix);
+  if (tid < G) {
+    int base = 0;
+    for (int s2 = 0; s2 < p.me; ++s2) base += __ldcg(&matrix[s2 * G + tid]);
+    recv_base[tid] = base;
+  }
+  if (blockIdx.x == 0 && tid == 0) {
+    int nr = 0;
+    for (int s2 = 0; s2 < G; ++s2) nr += __ldcg(&matrix[s2 * G + p.me]);
+    *p.n_recv_dev = nr;
+  }
+  __syncthreads();
+  // 5. receive slot of every pair (stable: CTA, thread, position)
+  for (int j = 0; j < per; ++j) {
+    const int i = tid * per + j;
+    if (i < n) {
+      const int d = dest_rank[i];
+      dest_slot[i] = d >= 0 ? recv_base[d] + cta_base[d] + tcnt[tid][d]++ : -1;
+    }
+  }
+  __syncthreads();
+  // 6. rows and their metadata into the owners' receive arrays (plain peer stores)
+  const int nvec = p.H >> 3;
+  for (int idx = tid; idx < n * nvec; idx += kSendThreads) {
+    const int i = idx / nvec, v = idx - i * nvec;
+    const int d = dest_rank[i], dst = dest_slot[i];
+    if (d < 0 || dst >= p.lay.recv_cap) continue;
+    const int r = r0 + i;
+    peer_ptr<uint4>(p.peer_base, d, p.lay.rows)[static_cast<size_t>(dst) * nvec + v] =
+        p.x[static_cast<size_t>(r / p.K) * nvec + v];
+  }
+  for (int i = tid; i < n; i += kSendThreads) {
+    const int d = dest_rank[i], dst = dest_slot[i];
+    if (d < 0 || dst >= p.lay.recv_cap) continue;
+    const int r = r0 + i;
+    peer_ptr<int32_t>(p.peer_base, d, p.lay.ids)[dst] = p.topk_ids[r] % p.e_local;
+    peer_ptr<float>(p.peer_base, d, p.lay.weights)[dst] = p.topk_w[r];
+    peer_ptr<int2>(p.peer_base, d, p.lay.src)[dst] = make_int2(p.me, r);
+  }
+  // 7. the last CTA to finish tells every rank that this rank's rows are complete
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const int prev = atomicAdd(&p.sync[1], 1);
+    if (prev == C - 1) {
+      p.sync[0] = 0;
+      p.sync[1] = 0;
+      __threadfence_system();
+      for (int peer = 0; peer < G; ++peer)
+        st_release_sys(peer_ptr<int32_t>(p.peer_base, peer, p.lay.flags_dispatch) + p.me, epoch);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+ep_recv_ready_kernel(int H, const int32_t* __restrict__ n_recv_dev, const uint64_t* __restrict__ peer_base,
+                     fmoe_ep_layout_c lay, int me, int G, const int32_t* __restrict__ epoch,
+                     uint64_t* __restrict__ row_ptrs, int32_t* __restrict__ status, long long limit) {
+  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_dispatch), G, *epoch, limit, status);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= *n_recv_dev || i >= lay.recv_cap) return;
+  const int2 s = __ldcg(peer_ptr<int2>(peer_base, me, lay.src) + i);
+  // never follow a bad return address: such a row goes to a scratch row of this rank instead
+  const bool ok = s.x >= 0 && s.x < G && s.y >= 0 && s.y < lay.send_cap;
+  row_ptrs[i] = ok ? peer_base[s.x] + lay.back + static_cast<uint64_t>(s.y) * H * 2
+                   : peer_base[me] + lay.rows;
+  if (!ok) atomicExch(status, 0x320);
+}
+
+__global__ void __launch_bounds__(128)
+ep_wait_combine_kernel(const int32_t* __restrict__ topk_ids, int K, int H, int E,
+                       const uint64_t* __restrict__ peer_base, fmoe_ep_layout_c lay, int me, int G,
+                       int32_t* __restrict__ epoch, int32_t* __restrict__ sync_counter, uint4* __restrict__ out,
+                       int32_t* __restrict__ status, long long limit) {
+  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_return), G, *epoch, limit, status);
+  const int t = blockIdx.x;
+  const int nvec = H >> 3;
+  const uint4* back = peer_ptr<uint4>(peer_base, me, lay.back);
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < K; ++k) {
+      const int e = topk_ids[t * K + k];
+      if (e < 0 || e >= E) continue;
+      const uint4 v = __ldcg(back + (static_cast<size_t>(t) * K + k) * nvec + i);   // written by a peer: skip L1
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      o[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    out[static_cast<size_t>(t) * nvec + i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  // the last CTA to finish opens the next step
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(sync_counter, 1);
+    if (prev == static_cast<int>(gridDim.x) - 1) {
+      *sync_counter = 0;
+      *epoch = *epoch + 1;
+    }
+  }
+}
+
 }  // namespace
 
 static int launch_status(const char* what) {
@@ -181,6 +417,79 @@ int fmoe_ep_return(const void* out_rows, int32_t H, const int32_t* n_recv_dev, c
                            static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint4*>(out_rows), H,
                                                                  n_recv_dev, peer_base, *lay, me, G);
   return fmoe::launch_status("expert-parallel kernel");
+}
+
+static long long wait_limit_cycles(int32_t timeout_ms) {
+  // clock64 ticks at the SM clock (<= ~2 GHz): 2e6 cycles per millisecond is an upper bound
+  return timeout_ms > 0 ? 2000000LL * timeout_ms : 8000000000LL;
+}
+
+static int ep_send_grid(int32_t T, int32_t K) {
+  const long long R = static_cast<long long>(T) * K;
+  long long c = (R + fmoe::kSendPairsPerCta - 1) / fmoe::kSendPairsPerCta;
+  const int sms = fmoe::device_sm_count();
+  if (c > sms) c = sms;
+  return c < 1 ? 1 : static_cast<int>(c);
+}
+
+int64_t fmoe_ep_send_scratch_words(int32_t T, int32_t K, int32_t G) {
+  (void)T; (void)K;
+  return 4 + 256LL * (G > 0 ? G : 1);      // two counters + per-CTA counts for up to 256 CTAs
+}
+
+int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t H,
+                 int32_t experts_per_rank, const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
+                 int32_t G, int32_t* scratch, const int32_t* epoch_dev, int32_t* n_recv_dev, int32_t* status,
+                 int32_t timeout_ms, void* stream) {
+  if (!x || !topk_ids || !topk_weight || !peer_base || !lay || !scratch || !epoch_dev || !n_recv_dev || !status)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send: a required pointer is null");
+  if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send: rank %d / world %d out of range (at most %d ranks)", me, G,
+                      fmoe::kSendMaxRanks);
+  if (H <= 0 || H % 8 || T <= 0 || K <= 0 || experts_per_rank <= 0 || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send: H must be a positive multiple of 8; T, K, experts_per_rank positive");
+  const int grid = ep_send_grid(T, K);
+  if ((static_cast<long long>(T) * K + grid - 1) / grid > fmoe::kSendMaxChunk)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send: at most %d routed pairs per rank", grid * fmoe::kSendMaxChunk);
+  fmoe::EpSendParams p;
+  p.x = reinterpret_cast<const uint4*>(x);
+  p.topk_ids = topk_ids; p.topk_w = topk_weight;
+  p.T = T; p.K = K; p.H = H; p.e_local = experts_per_rank;
+  p.peer_base = peer_base; p.lay = *lay; p.me = me; p.G = G;
+  p.sync = scratch; p.cta_counts = scratch + 4;
+  p.epoch = epoch_dev; p.n_recv_dev = n_recv_dev; p.status = status;
+  p.limit = wait_limit_cycles(timeout_ms);
+  fmoe::ep_send_kernel<<<grid, fmoe::kSendThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return fmoe::launch_status("fmoe_ep_send");
+}
+
+int fmoe_ep_recv_ready(int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,
+                       int32_t me, int32_t G, const int32_t* epoch_dev, uint64_t* row_ptrs, int32_t* status,
+                       int32_t timeout_ms, void* stream) {
+  if (!n_recv_dev || !peer_base || !lay || !epoch_dev || !row_ptrs || !status)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_recv_ready: a required pointer is null");
+  if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G || H <= 0 || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_recv_ready: bad arguments (rank %d, world %d, H %d)", me, G, H);
+  if (lay->recv_cap <= 0) return FMOE_OK;
+  const unsigned grid = static_cast<unsigned>((lay->recv_cap + 255) / 256);
+  fmoe::ep_recv_ready_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      H, n_recv_dev, peer_base, *lay, me, G, epoch_dev, row_ptrs, status, wait_limit_cycles(timeout_ms));
+  return fmoe::launch_status("fmoe_ep_recv_ready");
+}
+
+int fmoe_ep_wait_combine(const int32_t* topk_ids, int32_t T, int32_t K, int32_t H, int32_t num_experts,
+                         const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
+                         int32_t* epoch_dev, int32_t* sync_counter, void* out, int32_t* status, int32_t timeout_ms,
+                         void* stream) {
+  if (!topk_ids || !peer_base || !lay || !epoch_dev || !sync_counter || !out || !status)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_wait_combine: a required pointer is null");
+  if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G || T <= 0 || K <= 0 || H <= 0 || H % 8 || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_wait_combine: bad arguments (rank %d, world %d, T %d, K %d, H %d)", me,
+                      G, T, K, H);
+  fmoe::ep_wait_combine_kernel<<<T, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      topk_ids, K, H, num_experts, peer_base, *lay, me, G, epoch_dev, sync_counter, reinterpret_cast<uint4*>(out),
+      status, wait_limit_cycles(timeout_ms));
+  return fmoe::launch_status("fmoe_ep_wait_combine");
 }
 
 }  // extern "C"

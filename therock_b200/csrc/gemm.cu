@@ -177,6 +177,11 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   p.ld_out = g.ld_out;
   p.out_bf16 = g.out_bf16 ? 1 : 0;
   p.out_rows = g.out_rows;
+  p.row_ptrs = g.row_ptrs;
+  p.done_addrs = g.done_addrs;
+  p.done_value = g.done_value;
+  p.done_counter = g.done_counter;
+  p.done_count = g.done_count;
   p.status = g.status;
   p.b_tiled_kb = g.b_tiled ? k_blocks : 0;
 #ifdef FMOE_TIMING_SWITCHES

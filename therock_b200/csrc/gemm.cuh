@@ -57,6 +57,12 @@ struct GemmParams {
   int ld_out;                   // elements per output row
   int out_bf16;                 // kEpiScaledSlots: 1 = weighted rows are rounded to bf16
   int64_t out_rows;             // rows of `out` (bound for the checked build)
+  const uint64_t* row_ptrs;     // kEpiScaledSlots with bf16 rows: destination address of each routed pair's row
+                                // (may be peer memory) instead of out + pair * ld_out; nullptr = contiguous
+  const uint64_t* done_addrs;   // completion signal: the last CTA to finish writes *done_value to these
+  const int* done_value;        // addresses (release, system scope); nullptr = none
+  int* done_counter;
+  int done_count;
   int* status;                  // device status word
   uint64_t desc_template;       // shared-memory matrix descriptor without the address
   uint32_t idesc;               // tcgen05 instruction descriptor
@@ -109,6 +115,22 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const int* cum, int E
   t.n_blk = local / cnt;
   t.m_blk = base + local % cnt;
   return t;
+}
+
+// Completion signal of a whole grid: every CTA calls this after its last store (all threads,
+// after a CTA-wide barrier).  The last CTA to arrive publishes *done_value to the given
+// addresses, which may lie in other GPUs' memory, so their kernels can wait for this grid's
+// rows without a further launch.
+__device__ __forceinline__ void grid_done_signal(const GemmParams& p) {
+  if (p.done_addrs == nullptr || threadIdx.x != 0) return;
+  __threadfence_system();                         // this CTA's stores (seen through the barrier) first
+  const int prev = atomicAdd(p.done_counter, 1);
+  if (prev != static_cast<int>(gridDim.x) - 1) return;
+  __threadfence_system();
+  const int v = *p.done_value;
+  for (int i = 0; i < p.done_count; ++i)
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.done_addrs[i]), "r"(v) : "memory");
+  *p.done_counter = 0;                            // ready for the next launch
 }
 
 // SiLU with the fast exponential and division (a few ulp; far inside the bf16 rounding of y).
@@ -282,8 +304,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
           const uint4 val = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
                                        *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
           const int row_r = __shfl_sync(0xffffffffu, row, r);
-          if (row_r >= 0 && FMOE_ROW_OK(p, row_r))
-            *reinterpret_cast<uint4*>(hbase + static_cast<size_t>(row_r) * p.ld_out + c * 32 + seg * 8) = val;
+          if (row_r >= 0 && FMOE_ROW_OK(p, row_r)) {
+            __nv_bfloat16* drow = p.row_ptrs
+                ? reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row_r]) + n_blk * kTileN
+                : hbase + static_cast<size_t>(row_r) * p.ld_out;
+            *reinterpret_cast<uint4*>(drow + c * 32 + seg * 8) = val;
+          }
         }
       } else {
         // 8 lanes per row, 4 rows per store instruction: 128 contiguous bytes per row
@@ -491,6 +517,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (kEpi == kEpiScaledSlots) grid_done_signal(p);
 }
 
 // ============================================================================= CTA-pair variant
@@ -710,6 +737,7 @@ fmoe_grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (kEpi == kEpiScaledSlots) grid_done_signal(p);
 }
 
 }  // namespace fmoe

@@ -12,9 +12,10 @@
 //   whole K loop, as in the unscaled kernels.  A scale column of tensor memory holds four bytes
 //   per row; they are filled with the scales of four consecutive K blocks and every stage selects
 //   its byte through the instruction descriptor, so scales are copied to tensor memory (tcgen05.cp)
-//   once per four stages.  Warp 2 stages them in shared memory: the activation scales arrive as
-//   the ready-made 512-byte image the quantising kernels write, the weight scales are turned from
-//   f32 powers of two into exponent bytes and replicated over the slab's 128 rows on the fly.
+//   once per four stages.  Warp 2 stages them in shared memory as the 32 x 16-byte image that copy
+//   reads: the activation scales are row-major bytes, four K groups to a word, so an image row is
+//   four word loads; the weight scales are turned from f32 powers of two into exponent bytes and
+//   replicated over the slab's 128 rows on the fly.
 //   When the accumulator is complete the eight epilogue warps drain it into registers, hand the
 //   tensor memory back at once and run their epilogue while the next tile is multiplied.
 //
@@ -54,11 +55,11 @@ constexpr int kSfTmemCol = 256;          // scale columns start behind the accum
 
 struct BlockGemmParams {
   GemmParams g;                 // a_scale / b_scale of g are unused here
-  const void* a_scale;          // f32 [cap, k_blocks], or the packed UE8M0 image (kHw)
+  const void* a_scale;          // f32 [cap, k_blocks], or UE8M0 bytes [cap, scale_pitch(k_blocks)] (kHw)
   const float* b_scale;         // [E * b_rows_per_expert / 128, k_blocks]
   int k_blocks;                 // K / 128 (== g.k_iters)
   void* out_scale;              // first GEMM: scales of the quantised intermediate, f32 [cap, ld_out/128]
-                                // or the packed UE8M0 image (kHw); `g.out` then receives e4m3
+                                // or UE8M0 bytes [cap, scale_pitch(ld_out/128)] (kHw); `g.out` then receives e4m3
 };
 
 template <int kEpi, bool kHw>
@@ -243,7 +244,8 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       int slot = 0;
       uint32_t sphase = 0;
       bool ok = true;
-      const uint8_t* a_img = reinterpret_cast<const uint8_t*>(bp.a_scale);
+      const uint8_t* a_img = reinterpret_cast<const uint8_t*>(bp.a_scale);   // [rows, a_pitch] bytes
+      const size_t a_pitch = static_cast<size_t>(scale_pitch(kb_n));
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
         const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
@@ -251,8 +253,13 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         const float* sb1 = bp.b_scale + static_cast<size_t>((b_row0 + p.second_slab_offset) / 128) * kb_n;
         for (int g = 0; g < kg_n; ++g) {
           // loads first, so their latency overlaps the wait for a free slot
-          const uint4 av = __ldg(reinterpret_cast<const uint4*>(
-              a_img + (static_cast<size_t>(tc.m_blk) * kg_n + g) * 512u) + lane);
+          // image row `lane` = the four-byte words (K groups 4g..4g+3) of rows lane, 32+lane, 64+lane, 96+lane
+          const uint8_t* arow = a_img + (static_cast<size_t>(tc.m_blk) * kBlockM + lane) * a_pitch + 4 * g;
+          uint4 av;
+          av.x = __ldg(reinterpret_cast<const uint32_t*>(arow));
+          av.y = __ldg(reinterpret_cast<const uint32_t*>(arow + 32 * a_pitch));
+          av.z = __ldg(reinterpret_cast<const uint32_t*>(arow + 64 * a_pitch));
+          av.w = __ldg(reinterpret_cast<const uint32_t*>(arow + 96 * a_pitch));
           uint32_t w0 = 0, w1 = 0;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -450,7 +457,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (half == 0 && row >= 0 && FMOE_ROW_OK(p, slot)) {
           const int groups = p.ld_out >> 7;
           if (kHw)
-            reinterpret_cast<uint8_t*>(bp.out_scale)[packed_scale_offset(tc.m_blk, row_in_blk, tc.n_blk, (groups + 3) >> 2)] =
+            reinterpret_cast<uint8_t*>(bp.out_scale)[static_cast<size_t>(slot) * scale_pitch(groups) + tc.n_blk] =
                 static_cast<uint8_t>(sbyte);
           else
             reinterpret_cast<float*>(bp.out_scale)[static_cast<size_t>(slot) * groups + tc.n_blk] = sc;
@@ -506,8 +513,12 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
               const int seg = lane & 3;
               const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
               const int row_r = __shfl_sync(0xffffffffu, row, r);
-              if (row_r >= 0 && FMOE_ROW_OK(p, row_r))
-                *reinterpret_cast<uint4*>(hbase + static_cast<size_t>(row_r) * p.ld_out + ch * 32 + seg * 8) = val;
+              if (row_r >= 0 && FMOE_ROW_OK(p, row_r)) {
+                __nv_bfloat16* drow = p.row_ptrs
+                    ? reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row_r]) + tc.n_blk * kTileN + half * 128
+                    : hbase + static_cast<size_t>(row_r) * p.ld_out;
+                *reinterpret_cast<uint4*>(drow + ch * 32 + seg * 8) = val;
+              }
             }
           }
         } else {
@@ -545,6 +556,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (kEpi == kEpiScaledSlots) grid_done_signal(p);
 }
 
 }  // namespace fmoe

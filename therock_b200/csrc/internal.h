@@ -76,14 +76,19 @@ struct GemmLaunch {
   const int32_t* sorted_rows;
   const float* sorted_weights;
   const void* a_scale;          // f32 [a_rows] (per row), f32 [a_rows, K/128] (block promote) or the
-                                // packed UE8M0 image (block_scale MMA)
+                                // UE8M0 bytes (block_scale MMA)
   const float* b_scale;         // f32 [E * b_rows] or [E * b_rows / 128, K/128]
   void* out;
   int ld_out;
   int64_t out_rows;             // rows of `out` (bound used by the checked build)
   bool out_bf16;                // kEpiScaledSlots: weighted rows stored as bf16 instead of f32
+  const uint64_t* row_ptrs;     // with out_bf16: destination address of each routed pair's row (nullptr = out + pair * ld_out)
+  const uint64_t* done_addrs;   // completion signal written by the last CTA (nullptr = none)
+  const int32_t* done_value;
+  int32_t* done_counter;
+  int done_count;
   void* out_scale;              // block flavours, first GEMM: when set, `out` receives e4m3 and this the
-                                // 1x128 scales of the intermediate (f32 [a_rows, ld_out/128] or packed UE8M0)
+                                // 1x128 scales of the intermediate (f32 [a_rows, ld_out/128] or UE8M0 bytes)
   int32_t* status;
   int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
   bool b_tiled;                 // B is stored as contiguous 128-row x 128-byte tiles (see fmoe_weight_layout)

@@ -94,12 +94,12 @@ struct Plan {
   fmoe_ws_layout_c l{};
 };
 
-// Bytes of the packed UE8M0 scale array of a [cap, k_elems] activation matrix: one byte per
-// row and 128-wide K group, stored per (128-row block, group of four K groups) as the 512-byte
-// image tcgen05.cp copies to tensor memory: byte (row % 32) * 16 + (row / 32) * 4 + (group % 4).
+// Bytes of the UE8M0 scale array of a [cap, k_elems] activation matrix: one byte per row and
+// 128-wide K group, row-major, each row padded to a multiple of four bytes so that the scales of
+// four consecutive K groups are one aligned 32-bit word.
+inline int packed_scale_pitch(int k_elems) { return ((k_elems / 128) + 3) & ~3; }
 inline uint64_t packed_scale_bytes(int64_t cap, int k_elems) {
-  const int64_t kb = k_elems / 128;
-  return static_cast<uint64_t>(cap / kPlanBlockM) * static_cast<uint64_t>((kb + 3) / 4) * 512u;
+  return static_cast<uint64_t>(cap) * static_cast<uint64_t>(packed_scale_pitch(k_elems));
 }
 
 inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {

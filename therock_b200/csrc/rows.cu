@@ -160,8 +160,8 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
         const float sc = group_scale<kQuant == 3>(amax, sbyte);
         if (i < nvec) {
           if ((i & 15) == 0) {
-            if (kQuant == 3)   // one UE8M0 byte in the image the block-scaled MMA's scale copy reads
-              reinterpret_cast<uint8_t*>(scales_v)[packed_scale_offset(slot >> 7, slot & 127, i >> 4, (ngroups + 3) >> 2)] =
+            if (kQuant == 3)   // one UE8M0 byte per row and K group
+              reinterpret_cast<uint8_t*>(scales_v)[static_cast<size_t>(slot) * scale_pitch(ngroups) + (i >> 4)] =
                   static_cast<uint8_t>(sbyte);
             else
               scales[static_cast<size_t>(slot) * ngroups + (i >> 4)] = sc;
@@ -176,28 +176,46 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
 template <bool kBf16Slots>
 __global__ void __launch_bounds__(kRowThreads)
 combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ topk_ids, int K, int E,
-               int H, uint2* __restrict__ out, const int32_t* __restrict__ num_tokens_dev) {
+               int H, void* __restrict__ out_v, const int32_t* __restrict__ num_tokens_dev) {
   ptx::pdl_wait();
   ptx::pdl_release();
   const int t = blockIdx.x;
   if (num_tokens_dev && t >= *num_tokens_dev) return;   // rows past the device-side count
+  if (kBf16Slots) {
+    // bf16 partial rows: 8 elements (16 bytes) per thread and term
+    const int nvec = H >> 3;
+    const uint4* slots = reinterpret_cast<const uint4*>(slots_v);
+    uint4* out = reinterpret_cast<uint4*>(out_v);
+    for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int k = 0; k < K; ++k) {
+        const int e = topk_ids[t * K + k];
+        if (e < 0 || e >= E) continue;
+        float f[8];
+        unpack8(slots[(static_cast<size_t>(t) * K + k) * nvec + i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&v);
+      }
+      out[static_cast<size_t>(t) * nvec + i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    return;
+  }
   const int nvec = H >> 2;
   const float4* slots = reinterpret_cast<const float4*>(slots_v);
-  const uint2* slots_h = reinterpret_cast<const uint2*>(slots_v);
+  uint2* out = reinterpret_cast<uint2*>(out_v);
   for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < K; ++k) {
       const int e = topk_ids[t * K + k];
       if (e < 0 || e >= E) continue;
-      const size_t idx = (static_cast<size_t>(t) * K + k) * nvec + i;
-      if (kBf16Slots) {
-        const uint2 h = slots_h[idx];
-        acc.x += bf16_bits_to_f32(h.x & 0xffffu); acc.y += bf16_bits_to_f32(h.x >> 16);
-        acc.z += bf16_bits_to_f32(h.y & 0xffffu); acc.w += bf16_bits_to_f32(h.y >> 16);
-      } else {
-        const float4 v = slots[idx];
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-      }
+      const float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
     __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
@@ -259,10 +277,10 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev) {
   if (slots_bf16)
-    return launch_pdl(combine_kernel<true>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H,
-                      reinterpret_cast<uint2*>(out), num_tokens_dev);
-  return launch_pdl(combine_kernel<false>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H,
-                    reinterpret_cast<uint2*>(out), num_tokens_dev);
+    return launch_pdl(combine_kernel<true>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
+                      num_tokens_dev);
+  return launch_pdl(combine_kernel<false>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
+                    num_tokens_dev);
 }
 
 }  // namespace fmoe

@@ -21,10 +21,7 @@ __device__ __forceinline__ float group_scale(float amax, uint32_t& byte) {
   return __uint_as_float(e << 23);
 }
 
-// Byte offset of (row of a 128-row block, K group) inside the packed UE8M0 image.
-__device__ __forceinline__ size_t packed_scale_offset(int m_blk, int row_in_blk, int kb, int k_groups4) {
-  return (static_cast<size_t>(m_blk) * k_groups4 + (kb >> 2)) * 512u + (row_in_blk & 31) * 16 +
-         (row_in_blk >> 5) * 4 + (kb & 3);
-}
+// UE8M0 scale arrays are row-major bytes [rows, pitch], pitch = K groups rounded up to four.
+__host__ __device__ __forceinline__ int scale_pitch(int k_groups) { return (k_groups + 3) & ~3; }
 
 }  // namespace fmoe

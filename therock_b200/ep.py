@@ -240,19 +240,28 @@ class PeerExpertParallelMoE:
     """Expert parallelism over NVLink peer memory with no host synchronisation.
 
     Every rank owns one peer-addressable buffer (torch symmetric memory, NVLS multicast not
-    used).  A step is a fixed sequence of asynchronous launches on the current stream:
+    used).  A step is a fixed sequence of asynchronous launches on the current stream.
 
-        plan -> publish counts -> barrier -> dispatch (P2P stores of rows + metadata into the
-        owner's receive arrays) -> barrier -> local fused_moe on the received rows (row count
-        read on the device) -> return (P2P stores into the source's slots) -> barrier ->
-        ordered k-sum.
+    fused=True (default, at most 16 ranks): seven launches --
+        send (bucket the routed pairs by owner, publish the counts, wait for everybody's, store
+        rows + metadata into the owners' receive arrays, signal) -> recv_ready (wait for all
+        rows, build the table of return addresses) -> local fused_moe on the received rows, whose
+        second GEMM stores every weighted row as bf16 straight into the source rank's `back`
+        array and whose last CTA signals completion -> wait_combine (wait for all returns,
+        ordered k-sum).
+    fused=False: the same step from single-purpose kernels (plan, publish, barrier, dispatch,
+        barrier, local operator, return, barrier, combine), thirteen launches.
 
-    The barriers are flag kernels with bounded spins; a rank that never arrives shows up in
-    `status` instead of hanging the GPU.
+    Arithmetic in both: each (token, k) partial row crosses NVLink as bf16 and the k-sum is f32 with
+    one more rounding -- the operator's partial_dtype = bf16 contract.
+    Every wait is a bounded spin; a rank that never arrives shows up in `status` instead of
+    hanging the GPU.
     """
 
     def __init__(self, num_experts: int, world: int, rank: int, traits, w1_local, w2_local,
-                 w1_scale=None, w2_scale=None, *, tokens_per_rank: int, topk: int, hidden: int, group=None):
+                 w1_scale=None, w2_scale=None, *, tokens_per_rank: int, topk: int, hidden: int, group=None,
+                 fused: bool = True):
+        import copy
         import ctypes
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -260,7 +269,11 @@ class PeerExpertParallelMoE:
         from . import api
         if num_experts % world:
             raise ValueError("experts must divide evenly over ranks")
-        self.api, self.traits = api, traits
+        self.api = api
+        self.fused = bool(fused) and world <= 16
+        self.traits = copy.copy(traits)
+        if self.fused:
+            self.traits.partial_dtype = "bf16"
         self.E, self.world, self.rank = num_experts, world, rank
         self.e_local = num_experts // world
         self.T, self.K, self.H = tokens_per_rank, topk, hidden
@@ -272,7 +285,8 @@ class PeerExpertParallelMoE:
             return (n + 255) // 256 * 256
         lay = api.EpLayout()
         off = 0
-        for name, nbytes in (("flags", world * 4), ("matrix", world * world * 4),
+        for name, nbytes in (("flags", world * 4), ("flags_dispatch", world * 4), ("flags_return", world * 4),
+                             ("matrix", world * world * 4),
                              ("rows", recv_cap * hidden * 2), ("ids", recv_cap * 4), ("weights", recv_cap * 4),
                              ("src", recv_cap * 8), ("back", R * hidden * 2)):
             setattr(lay, name, off)
@@ -304,13 +318,27 @@ class PeerExpertParallelMoE:
         self.args = api.FusedMoeArgs(a=self.rows, g=w1_local, d=w2_local, topk_ids=self.ids,
                                      topk_weight=self.wts, o=self.out_rows, g_scale=w1_scale,
                                      d_scale=w2_scale, num_tokens_dev=self.n_recv, expected_tokens=R)
-        self.args.workspace = torch.empty(api.fused_moe_workspace_size(traits, self.args), dtype=torch.uint8,
-                                          device=dev)
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self.fused:
+            # fused step: the epoch starts at 1 and is advanced on the device by wait_combine
+            self.epoch_dev.fill_(1)
+            self.send_scratch = torch.zeros(int(api.lib().fmoe_ep_send_scratch_words(tokens_per_rank, topk, world)),
+                                            dtype=torch.int32, device=dev)
+            self.row_ptrs = torch.zeros(recv_cap, dtype=torch.int64, device=dev)
+            self.sync_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.args.partial_row_ptrs = self.row_ptrs
+            self.args.done_flag_addrs = (self.peer_base + (lay.flags_return + 4 * rank)).contiguous()
+            self.args.done_flag_value = self.epoch_dev
+            self.args.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.args.workspace = torch.empty(api.fused_moe_workspace_size(self.traits, self.args), dtype=torch.uint8,
+                                          device=dev)
         self.barrier_timeout_ms = 0          # 0 = the library default (about four seconds)
         self.trace = None                    # set to [] to collect (phase, cuda event) marks
         self._ctypes = ctypes
-        self.launches_per_step = 8 + api.launches_per_run(traits, self.args)
+        ops = api.launches_per_run(self.traits, self.args)
+        self.launches_per_step = (3 + ops - 1) if self.fused else (8 + ops)   # fused: the operator runs no combine
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
 
     def _barrier(self, stream):
         # the epoch is a device-side counter, so the launch arguments never change
@@ -318,11 +346,38 @@ class PeerExpertParallelMoE:
                                                        self.rank, self.world, 0, self.epoch_dev.data_ptr(),
                                                        self.status.data_ptr(), self.barrier_timeout_ms, stream))
 
+    def _forward_fused(self, x, topk_ids, topk_weight, out):
+        api, lib, by = self.api, self.api.lib(), self._ctypes.byref
+        T, K, H, G = self.T, self.K, self.H, self.world
+        st = api._stream_ptr(None)
+        pb = self.peer_base.data_ptr()
+        if out is None:
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        self._mark("start")
+        api._check(lib.fmoe_ep_send(x.data_ptr(), topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, H, self.e_local,
+                                    pb, by(self.lay), self.rank, G, self.send_scratch.data_ptr(),
+                                    self.epoch_dev.data_ptr(), self.n_recv.data_ptr(), self.status.data_ptr(),
+                                    self.barrier_timeout_ms, st))
+        self._mark("send")
+        api._check(lib.fmoe_ep_recv_ready(H, self.n_recv.data_ptr(), pb, by(self.lay), self.rank, G,
+                                          self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(), self.status.data_ptr(),
+                                          self.barrier_timeout_ms, st))
+        self._mark("recv_ready")
+        api.fused_moe(self.traits, self.args)
+        self._mark("local_moe")
+        api._check(lib.fmoe_ep_wait_combine(topk_ids.data_ptr(), T, K, H, self.E, pb, by(self.lay), self.rank, G,
+                                            self.epoch_dev.data_ptr(), self.sync_counter.data_ptr(), out.data_ptr(),
+                                            self.status.data_ptr(), self.barrier_timeout_ms, st))
+        self._mark("wait_combine")
+        return out
+
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weight: torch.Tensor,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
         api, lib, by = self.api, self.api.lib(), self._ctypes.byref
         T, K, H, G = self.T, self.K, self.H, self.world
         assert x.shape == (T, H) and topk_ids.shape == (T, K)
+        if self.fused:
+            return self._forward_fused(x, topk_ids, topk_weight, out)
         st = api._stream_ptr(None)
         pb = self.peer_base.data_ptr()
         self._mark("start")
