@@ -565,23 +565,24 @@ def measure_single(env, a, c, cfg_name, headline, sampler):
         ids_h = d["ids"].cpu().pin_memory()
         w_h = d["w"].cpu().pin_memory()
         out_h = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
-        depth = 2
-        outs = [torch.empty_like(d["x"]) for _ in range(depth)]
+        outs = [torch.empty_like(d["x"]) for _ in range(2)]
 
         def pipe_step(x, ids, w, slot):
             args.a, args.topk_ids, args.topk_weight, args.o = x, ids, w, outs[slot]
             return M.fused_moe(traits, args, stream=torch.cuda.current_stream())
-        pipe = api.HostPipeline(pipe_step, T, H, c["K"], dev, depth=depth)
+        # one CUDA-graph launch per step: operator on this batch, copy-in of the next batch and
+        # copy-out of the previous result as concurrent branches (therock_b200.api.GraphPipeline)
+        pipe = api.GraphPipeline(pipe_step, x_h, ids_h, w_h, out_h, dev)
         n_e2e = max(3, min(a.steps, 100))
         for _ in range(3):
-            pipe.submit(x_h, ids_h, w_h, out_h)
-        pipe.drain()
+            pipe.submit()
+        pipe.flush()
         env.barrier()
         e0 = pipe.mark()
         for _ in range(n_e2e):
-            pipe.submit(x_h, ids_h, w_h, out_h)
+            pipe.submit()
         e1 = pipe.mark()
-        pipe.drain()
+        pipe.flush()
         env.barrier()
         ms_e2e = e0.elapsed_time(e1)
         args.a, args.topk_ids, args.topk_weight, args.o = d["x"], d["ids"], d["w"], outs[0]
@@ -683,37 +684,30 @@ def measure_ep(env, a, c, sampler):
     ids_h = d["ids"].cpu().pin_memory()
     w_h = d["w"].cpu().pin_memory()
     out_h = torch.empty(T_local, H, dtype=torch.bfloat16).pin_memory()
-    depth = 2
     if ep_transport == "peer_memory":
-        # the whole expert-parallel step (no host sync inside) is captured once per pipeline slot
-        # and replayed: the host then issues one graph launch per step
-        ep_out = [torch.empty_like(d["x"]) for _ in range(depth)]
-        ep_graphs = [None] * depth
+        # the whole expert-parallel step has no host synchronisation inside, so it is captured,
+        # with the copies of the neighbouring batches, in one graph per pipeline slot
+        ep_out = [torch.empty_like(d["x"]) for _ in range(2)]
 
         def pipe_step(x, ids, w, slot):
-            if ep_graphs[slot] is None:
-                moe.forward(x, ids, w, out=ep_out[slot])          # warm-up outside capture
-                torch.cuda.current_stream().synchronize()
-                g_ = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g_, stream=torch.cuda.current_stream()):
-                    moe.forward(x, ids, w, out=ep_out[slot])
-                ep_graphs[slot] = g_
-            ep_graphs[slot].replay()
-            return ep_out[slot]
+            return moe.forward(x, ids, w, out=ep_out[slot])
+        pipe = api.GraphPipeline(pipe_step, x_h, ids_h, w_h, out_h, dev)
+        submit, finish = pipe.submit, pipe.flush
     else:
         def pipe_step(x, ids, w, slot):
             return moe.forward(x, ids, w)
-    pipe = api.HostPipeline(pipe_step, T_local, H, c["K"], dev, depth=depth)
+        pipe = api.HostPipeline(pipe_step, T_local, H, c["K"], dev, depth=2)
+        submit, finish = (lambda: pipe.submit(x_h, ids_h, w_h, out_h)), pipe.drain
     n_e2e = max(3, min(a.steps, 100))
     for _ in range(3):
-        pipe.submit(x_h, ids_h, w_h, out_h)
-    pipe.drain()
+        submit()
+    finish()
     env.barrier()
     e0 = pipe.mark()
     for _ in range(n_e2e):
-        pipe.submit(x_h, ids_h, w_h, out_h)
+        submit()
     e1 = pipe.mark()
-    pipe.drain()
+    finish()
     env.barrier()
     ms_e2e = env.max_over_ranks(e0.elapsed_time(e1))
     e2e = {"value": fl / (ms_e2e / n_e2e) / 1e9, "unit": "TFLOP/s",

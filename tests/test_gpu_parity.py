@@ -90,6 +90,32 @@ def test_sort_stage_inside_fused_moe_is_bit_exact():
     assert int(region("meta", 2, torch.int32)[0]) == int(ref["num_tokens_post_pad"][0])
 
 
+@pytest.mark.parametrize("T,K,E,quant", [(16, 2, 8, 1), (16, 2, 8, 0), (40, 3, 300, 1), (1, 1, 1, 0), (128, 1, 5, 1),
+                                          (9, 8, 256, 0)])
+def test_decode_prologue_sorting_is_bit_exact(T, K, E, quant):
+    """Decode-sized batches (at most 128 routed pairs) run moe_sorting and the gather as one
+    kernel: its sorted arrays must be the oracle's, bit for bit, invalid ids included."""
+    H, I = 256, 128
+    d = O.make_inputs(T, H, I, E, K, quant, "sigmoid", seed=T + E)
+    if T > 4:
+        d["topk_ids"][1, 0] = -1
+        d["topk_ids"][3, K - 1] = E + 2
+    got, args = run_gpu(d)
+    lay = M.workspace_layout(traits_for(quant), args)
+    ref = O.moe_sorting(d["topk_ids"], d["topk_w"], E, 128)
+    ws, cap = args.workspace, lay["capacity"]
+
+    def region(name, n):
+        return ws[lay[name]:lay[name] + 4 * n].view(torch.int32).cpu().numpy()
+    assert (region("sorted_token_ids", cap) == ref["sorted_token_ids"]).all()
+    assert (region("sorted_rows", cap) == ref["sorted_rows"]).all()
+    assert (region("sorted_weights", cap) == ref["sorted_weights"].view(np.int32)).all()
+    assert (region("sorted_expert_ids", cap // 128) == ref["sorted_expert_ids"]).all()
+    assert (region("mblk_cum", E + 1) == ref["mblk_cum"]).all()
+    assert int(region("meta", 2)[0]) == int(ref["num_tokens_post_pad"][0])
+    check(d, got, run_oracle(d))
+
+
 # ------------------------------------------------------------------------------ fused MoE
 
 @pytest.mark.parametrize("quant", [0, 1, 2, 3])
@@ -493,6 +519,40 @@ def test_host_pipeline_overlaps_copies_and_keeps_results():
         di = dict(d)
         di["x"] = xs[i].view(torch.int16).numpy().view(np.uint16)
         check(di, res[i].view(torch.int16).numpy().view(np.uint16), run_oracle(di))
+
+
+def test_graph_pipeline_one_launch_per_step_keeps_results():
+    """GraphPipeline: the step, the copy-in of the next batch and the copy-out of the previous
+    result run as branches of one CUDA graph per step; every batch must still get its own result."""
+    d = O.make_inputs(128, 512, 256, 8, 2, 1, "softmax", seed=62)
+    args = args_for(d)
+    traits = traits_for(1)
+    args.workspace = torch.empty(M.fused_moe_workspace_size(traits, args), dtype=torch.uint8, device="cuda:0")
+    outs = [torch.empty_like(args.a) for _ in range(2)]
+
+    def step(x, ids, w, slot):
+        args.a, args.topk_ids, args.topk_weight, args.o = x, ids, w, outs[slot]
+        return M.fused_moe(traits, args, stream=torch.cuda.current_stream())
+    n = 5
+    batches = [O.f32_to_bf16(O.normal((128, 512), 80 + i, 1)) for i in range(n)]
+    x_h = torch.from_numpy(batches[0].view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+    ids_h = torch.from_numpy(d["topk_ids"]).pin_memory()
+    w_h = torch.from_numpy(d["topk_w"]).pin_memory()
+    out_h = torch.empty(128, 512, dtype=torch.bfloat16).pin_memory()
+    pipe = api.GraphPipeline(step, x_h, ids_h, w_h, out_h, torch.device("cuda:0"))
+    got = []
+    for i in range(n):
+        if i + 1 < n:
+            x_h.copy_(torch.from_numpy(batches[i + 1].view(np.int16).copy()).view(torch.bfloat16))
+        pipe.submit()
+        pipe.main.synchronize()
+        if i > 0:
+            got.append(out_h.view(torch.int16).numpy().view(np.uint16).copy())
+    pipe.flush()
+    got.append(out_h.view(torch.int16).numpy().view(np.uint16).copy())
+    for i in range(n):
+        di = dict(d, x=batches[i])
+        check(di, got[i], run_oracle(di))
 
 
 @pytest.mark.parametrize("quant", [0, 1])

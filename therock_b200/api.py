@@ -448,3 +448,87 @@ def route(logits: torch.Tensor, topk: int, mode: str = "softmax", stream=None):
     _check(lib().fmoe_route(logits.data_ptr(), T, E, topk, 0 if mode == "softmax" else 1, ids.data_ptr(),
                             w.data_ptr(), _stream_ptr(stream)))
     return ids, w
+
+
+class GraphPipeline:
+    """Host-resident batches with one CUDA-graph launch per step.
+
+    Two device-side slots.  The graph of slot s holds three independent branches that run
+    concurrently on the device: the operator step on slot s (whose inputs the previous replay
+    copied in), the host->device copy of the next batch into slot s^1, and the device->host copy of
+    the result the previous replay computed in slot s^1.  Consecutive replays alternate between
+    the two graphs, so every step still moves its inputs in from pinned host memory and its result
+    back out, the copies hide behind the neighbouring step's compute, and the host issues a single
+    launch per step (the Python-side stream and event calls of HostPipeline are gone from the loop).
+
+    step(x, topk_ids, topk_weight, slot) -> output tensor; it must write a tensor that is fixed per
+    slot (capture records addresses) and must neither allocate nor synchronise.
+    The host buffers are fixed at construction: x_host [T, H] bf16, ids_host [T, K] int32,
+    w_host [T, K] f32, out_host [T, H] bf16, all pinned.  The constructor copies the first batch
+    in.  submit() number i (from 0) computes batch i, copies in whatever the host buffers hold while
+    it runs (batch i+1: fill them before the call and leave them alone until it has completed) and
+    copies the result of batch i-1 to out_host; flush() delivers the last result."""
+
+    def __init__(self, step, x_host, ids_host, w_host, out_host, device):
+        T, H = x_host.shape
+        K = ids_host.shape[1]
+        self.device = device
+        self.main, self.s_in, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
+        self.x = [torch.empty(T, H, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.ids = [torch.empty(T, K, dtype=torch.int32, device=device) for _ in range(2)]
+        self.w = [torch.empty(T, K, dtype=torch.float32, device=device) for _ in range(2)]
+        self.hosts = (x_host, ids_host, w_host, out_host)
+        self.n = 0
+        with torch.cuda.stream(self.main):
+            # warm-up outside capture (lazy initialisation, per-slot output tensors)
+            self.out = []
+            for s in range(2):
+                self._copy_in(s)
+                self.out.append(step(self.x[s], self.ids[s], self.w[s], s))
+            self.main.synchronize()
+            self.graphs = []
+            for s in range(2):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.main):
+                    fork = torch.cuda.Event()
+                    fork.record(self.main)
+                    self.s_in.wait_event(fork)
+                    self.s_out.wait_event(fork)
+                    with torch.cuda.stream(self.s_in):
+                        self._copy_in(s ^ 1)
+                        j_in = torch.cuda.Event()
+                        j_in.record(self.s_in)
+                    with torch.cuda.stream(self.s_out):
+                        out_host.copy_(self.out[s ^ 1], non_blocking=True)
+                        j_out = torch.cuda.Event()
+                        j_out.record(self.s_out)
+                    step(self.x[s], self.ids[s], self.w[s], s)
+                    self.main.wait_event(j_in)
+                    self.main.wait_event(j_out)
+                self.graphs.append(g)
+            self._copy_in(0)              # the first batch is in place before the first replay
+            self.main.synchronize()
+
+    def _copy_in(self, s):
+        x_host, ids_host, w_host, _ = self.hosts
+        self.x[s].copy_(x_host, non_blocking=True)
+        self.ids[s].copy_(ids_host, non_blocking=True)
+        self.w[s].copy_(w_host, non_blocking=True)
+
+    def submit(self):
+        """One step: a single graph launch on the pipeline's stream."""
+        with torch.cuda.stream(self.main):
+            self.graphs[self.n & 1].replay()
+        self.n += 1
+
+    def mark(self) -> "torch.cuda.Event":
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(self.main)
+        return ev
+
+    def flush(self):
+        """Copies the last computed result out and waits for everything."""
+        with torch.cuda.stream(self.main):
+            if self.n:
+                self.hosts[3].copy_(self.out[(self.n - 1) & 1], non_blocking=True)
+        self.main.synchronize()

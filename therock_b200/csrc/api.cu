@@ -210,18 +210,25 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     FMOE_CUDA(cudaEventRecord(ev.a, stream));
   }
 
-  {
-    NvtxRange r("moe_sorting");
-    FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
-                                       sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
-                                       mblk_cum, status, stream, a.num_tokens_dev, 1, nullptr,
-                                       reinterpret_cast<int32_t*>(ws + l.sort_scratch)));
-  }
-  FMOE_STAGE(1);
   const bool blk = fmoe::quant_is_block(traits->quant);
   const bool hw = traits->quant == FMOE_QUANT_BLOCK128_UE8M0;
   const int qmode = !fp8 ? 0 : (hw ? 3 : (blk ? 2 : 1));
-  {
+  if (fmoe::decode_prologue_applies(a.T, a.K, qmode)) {
+    // decode-sized batch: sorting and gather (+ quantisation) are one launch
+    NvtxRange r("decode_prologue");
+    FMOE_CUDA(fmoe::launch_decode_prologue(a.topk_ids, a.topk_weight, a.T, a.K, a.E, plan.cap, a.x, a.H, qmode,
+                                           sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad, mblk_cum,
+                                           status, a_sorted, static_cast<float*>(a_scale), stream, a.num_tokens_dev));
+    FMOE_STAGE(1);
+  } else {
+    {
+      NvtxRange r("moe_sorting");
+      FMOE_CUDA(fmoe::launch_moe_sorting(a.topk_ids, a.topk_weight, a.T, a.K, a.E, traits->block_m, plan.cap,
+                                         sorted_ids, sorted_w, sorted_rows, expert_ids, num_post_pad,
+                                         mblk_cum, status, stream, a.num_tokens_dev, 1, nullptr,
+                                         reinterpret_cast<int32_t*>(ws + l.sort_scratch)));
+    }
+    FMOE_STAGE(1);
     NvtxRange r("gather_quant");
     FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
                                        a_sorted, a_scale, stream));

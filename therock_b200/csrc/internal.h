@@ -51,6 +51,15 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
                                void* scales, cudaStream_t stream, const int32_t* live_ids = nullptr);
 
+// Decode-sized batches (T*K <= 128, bf16 or per-token-quantised activations): moe_sorting and the
+// gather (+ quantisation) in one launch.  Pad slots of a_sorted are left unwritten.
+bool decode_prologue_applies(int T, int K, int quant);
+cudaError_t launch_decode_prologue(const int32_t* topk_ids, const float* topk_weight, int T, int K, int E, int64_t cap,
+                                   const void* x, int H, int quant, int32_t* sorted_token_ids, float* sorted_weights,
+                                   int32_t* sorted_rows, int32_t* sorted_expert_ids, int32_t* num_post_pad,
+                                   int32_t* mblk_cum, int32_t* status_to_clear, void* a_sorted, float* a_scale,
+                                   cudaStream_t stream, const int32_t* num_tokens_dev);
+
 // out[t, :] = bf16( sum_k slots[t*K + k, :] ) over the k whose expert id lies in [0, E);
 // slots are f32, or bf16 when slots_bf16.
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,

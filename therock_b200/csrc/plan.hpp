@@ -164,8 +164,13 @@ inline int describe_run(const fmoe_traits_c* t, const fmoe_args_c* a, int sms, i
   const bool multi_sort = static_cast<long long>(a->T) * a->K >= kSortMultiCtaPairs;
   info->sort_launches = multi_sort ? 3 : 1;
   info->quant_y_launch = (t->quant == FMOE_QUANT_TOKEN_CHANNEL || (quant_is_block(t->quant) && !kFusedBlockQuant)) ? 1 : 0;
-  // sort, gather(+quant), gemm1, [quant of the intermediate], gemm2, combine
+  // sort, gather(+quant), gemm1, [quant of the intermediate], gemm2, combine; decode-sized
+  // batches without block scales run sort and gather as one kernel
+  const bool fused_prologue = static_cast<long long>(a->T) * a->K <= 128 &&
+                              (t->quant == FMOE_QUANT_NONE || t->quant == FMOE_QUANT_TOKEN_CHANNEL);
+  if (fused_prologue) info->sort_launches = 0;
   info->launches = info->sort_launches + 1 + 1 + info->quant_y_launch + 1 + 1;
+  if (a->partial_row_ptrs) info->launches -= 1;      // scattered partial rows: no combine
   return FMOE_OK;
 }
 

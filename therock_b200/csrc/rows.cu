@@ -224,6 +224,131 @@ combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ top
   }
 }
 
+// ----------------------------------------------------------------------------- decode prologue
+// moe_sorting + gather (+ per-token quantisation) in one launch for decode-sized batches: at
+// most kProloguePairs routed pairs, so every expert that is hit owns exactly one row block.
+// One CTA per routed pair: each CTA reads all the ids (a few hundred bytes), works out the slot of
+// its own pair with block-wide counts -- bit-identical to the moe_sorting kernels -- and moves its
+// row; CTA 0 also writes the sorted arrays, the block table and the counters.  Pad slots of the
+// activation matrix are left untouched: their rows of every later result are never stored.
+constexpr int kProloguePairs = 128;
+
+template <int kQuant>
+__global__ void __launch_bounds__(kRowThreads)
+decode_prologue_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_weight, int T_max,
+                       const int32_t* __restrict__ num_tokens_dev, int K, int E, int cap, const uint4* __restrict__ x,
+                       int H, int32_t* __restrict__ sorted_token_ids, float* __restrict__ sorted_weights,
+                       int32_t* __restrict__ sorted_rows, int32_t* __restrict__ sorted_expert_ids,
+                       int32_t* __restrict__ num_post_pad, int32_t* __restrict__ mblk_cum,
+                       int32_t* __restrict__ status_to_clear, void* __restrict__ a_sorted, float* __restrict__ a_scale) {
+  ptx::pdl_wait();
+  ptx::pdl_release();
+  __shared__ int32_t ids_s[kProloguePairs];
+  __shared__ int32_t slot_s[kProloguePairs];
+  __shared__ float warp_max[kRowThreads / 32];
+  __shared__ float row_scale;
+  const int tid = threadIdx.x;
+  const int T = num_tokens_dev ? min(T_max, max(0, *num_tokens_dev)) : T_max;
+  const int R = T * K;                               // <= kProloguePairs (checked by the launcher)
+  int my_e = -1;
+  if (tid < R) {
+    const int e = topk_ids[tid];
+    my_e = (e >= 0 && e < E) ? e : -1;
+  }
+  if (tid < kProloguePairs) ids_s[tid] = my_e;
+  __syncthreads();
+  // slot of pair `tid`: (distinct experts below mine that are hit) * 128 + (earlier pairs of my expert)
+  if (tid < R) {
+    int blocks_before = 0, rank = 0;
+    if (my_e >= 0) {
+      for (int j = 0; j < R; ++j) {
+        const int ej = ids_s[j];
+        if (ej < 0) continue;
+        if (ej == my_e) { rank += (j < tid); continue; }
+        if (ej < my_e) {
+          bool first = true;                         // count each expert once: at its first pair
+          for (int j2 = 0; j2 < j; ++j2) first = first && (ids_s[j2] != ej);
+          blocks_before += first;
+        }
+      }
+    }
+    slot_s[tid] = my_e >= 0 ? blocks_before * 128 + rank : -1;
+  }
+  __syncthreads();
+
+  if (blockIdx.x == 0) {
+    // sorted arrays, block table and counters (what the moe_sorting kernel writes)
+    for (int i = tid; i < cap; i += kRowThreads) {
+      sorted_token_ids[i] = T_max;
+      sorted_weights[i] = 0.0f;
+      sorted_rows[i] = -1;
+    }
+    for (int i = tid; i < cap / 128; i += kRowThreads) sorted_expert_ids[i] = -1;
+    __syncthreads();
+    if (tid < R && slot_s[tid] >= 0) {
+      const int sl = slot_s[tid];
+      sorted_token_ids[sl] = tid / K;
+      sorted_weights[sl] = topk_weight[tid];
+      sorted_rows[sl] = tid;
+      if ((sl & 127) == 0) sorted_expert_ids[sl >> 7] = my_e;
+    }
+    // cumulative blocks per expert: experts that are hit own one block each
+    for (int e = tid; e <= E; e += kRowThreads) {
+      int below = 0;                                 // distinct hit experts with id < e
+      for (int j = 0; j < R; ++j) {
+        const int ej = ids_s[j];
+        if (ej < 0 || ej >= e) continue;
+        bool first = true;
+        for (int j2 = 0; j2 < j; ++j2) first = first && (ids_s[j2] != ej);
+        below += first;
+      }
+      mblk_cum[e] = below;
+      if (e == E) num_post_pad[0] = below * 128;
+    }
+    if (tid == 0 && status_to_clear) status_to_clear[0] = 0;
+  }
+
+  // this CTA's row
+  const int pair = blockIdx.x;
+  if (pair >= R) return;
+  const int slot = slot_s[pair];
+  if (slot < 0) return;
+  const int nvec = H >> 3;
+  const uint4* src = x + static_cast<size_t>(pair / K) * nvec;
+  if (kQuant == 0) {
+    uint4* d = reinterpret_cast<uint4*>(a_sorted) + static_cast<size_t>(slot) * nvec;
+    for (int i = tid; i < nvec; i += kRowThreads) d[i] = src[i];
+    return;
+  }
+  float amax = 0.0f;
+  for (int i = tid; i < nvec; i += kRowThreads) {
+    float f[8];
+    unpack8(src[i], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
+  __syncthreads();
+  if (tid == 0) {
+    float m = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; ++w) m = fmaxf(m, warp_max[w]);
+    const float sc = m > 0.0f ? m / 448.0f : 1.0f;
+    row_scale = sc;
+    a_scale[slot] = sc;
+  }
+  __syncthreads();
+  const float inv = 1.0f / row_scale;
+  uint2* d = reinterpret_cast<uint2*>(a_sorted) + static_cast<size_t>(slot) * nvec;
+  for (int i = tid; i < nvec; i += kRowThreads) {
+    float f[8];
+    unpack8(src[i], f);                               // second read of the row comes from L1/L2
+    d[i] = quant8(f, inv);
+  }
+}
+
 // Expert-parallel combine: bf16 partial rows picked through an index, f32 sum in k order.
 __global__ void __launch_bounds__(kRowThreads)
 combine_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ index, int K, int H,
@@ -272,6 +397,26 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
     return launch_pdl(gather_rows_kernel<2>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
   else
     return launch_pdl(gather_rows_kernel<3>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids);
+}
+
+bool decode_prologue_applies(int T, int K, int quant) {
+  return static_cast<long long>(T) * K <= kProloguePairs && (quant == 0 || quant == 1);
+}
+
+cudaError_t launch_decode_prologue(const int32_t* topk_ids, const float* topk_weight, int T, int K, int E, int64_t cap,
+                                   const void* x, int H, int quant, int32_t* sorted_token_ids, float* sorted_weights,
+                                   int32_t* sorted_rows, int32_t* sorted_expert_ids, int32_t* num_post_pad,
+                                   int32_t* mblk_cum, int32_t* status_to_clear, void* a_sorted, float* a_scale,
+                                   cudaStream_t stream, const int32_t* num_tokens_dev) {
+  const dim3 grid(static_cast<unsigned>(T * K > 0 ? T * K : 1));
+  const uint4* xs = reinterpret_cast<const uint4*>(x);
+  if (quant == 0)
+    return launch_pdl(decode_prologue_kernel<0>, grid, dim3(kRowThreads), 0, stream, topk_ids, topk_weight, T,
+                      num_tokens_dev, K, E, static_cast<int>(cap), xs, H, sorted_token_ids, sorted_weights, sorted_rows,
+                      sorted_expert_ids, num_post_pad, mblk_cum, status_to_clear, a_sorted, a_scale);
+  return launch_pdl(decode_prologue_kernel<1>, grid, dim3(kRowThreads), 0, stream, topk_ids, topk_weight, T,
+                    num_tokens_dev, K, E, static_cast<int>(cap), xs, H, sorted_token_ids, sorted_weights, sorted_rows,
+                    sorted_expert_ids, num_post_pad, mblk_cum, status_to_clear, a_sorted, a_scale);
 }
 
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,

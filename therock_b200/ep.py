@@ -336,7 +336,7 @@ class PeerExpertParallelMoE:
         self.trace = None                    # set to [] to collect (phase, cuda event) marks
         self._ctypes = ctypes
         ops = api.launches_per_run(self.traits, self.args)
-        self.launches_per_step = (3 + ops - 1) if self.fused else (8 + ops)   # fused: the operator runs no combine
+        self.launches_per_step = (3 + ops) if self.fused else (8 + ops)
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
