@@ -2,9 +2,11 @@
 
 Layout: 16-byte magic/version, a JSON header (dims, quantisation mode, byte offsets), then the
 tensors back to back in exactly the layout the kernels consume -- W1 [E, 2I, H] (gate rows then
-up rows), W2 [E, H, I], K contiguous, bf16 or e4m3 bytes, plus f32 scales.  No tile
-pre-shuffle is needed: the TMA descriptors address the natural row-major tensors.  Because
-experts are the outermost dimension, an expert-parallel rank maps only its own slice."""
+up rows), W2 [E, H, I], K contiguous, bf16 or e4m3 bytes, plus f32 scales.  The kernels address
+these natural row-major tensors directly through their TMA descriptors; `tile_weights` below is an
+optional offline pre-shuffle into contiguous 16 KiB operand tiles (weight_layout = "tiled128":
+same results, a faster weight stream for decode-sized batches).  Because experts are the
+outermost dimension, an expert-parallel rank maps only its own slice."""
 from __future__ import annotations
 
 import json
