@@ -68,11 +68,13 @@ def _worker(rank, world, port, T, H, I, E, K, quant, drop, ret, dedup=False):
         moe = ep.ExpertParallelMoE(E, world, rank, local_moe, gather=_cpu_gather, combine=_cpu_combine,
                                    dedup=dedup)
         out = moe.forward(x, ids, wts)
+        # partial rows travel as bf16 before the k-sum: the oracle's bf16-partial mode is the
+        # reference (de-duplicated dispatch sums a rank's experts in f32 first: looser bound there)
         ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
-                          sel=np.arange(sl.start, sl.stop, dtype=np.int32))
+                          sel=np.arange(sl.start, sl.stop, dtype=np.int32), partial_bf16=not dedup)
         g, r = O.bf16_to_f32(_bits(out)), O.bf16_to_f32(ref)
-        # partial rows are rounded to bf16 before the k-sum: one extra bf16 rounding per term
-        ok = np.allclose(g, r, rtol=1e-2, atol=1e-2) and np.linalg.norm(g - r) <= 5e-3 * np.linalg.norm(r)
+        bound = 5e-3 if dedup else (2e-3 if quant == 0 else 4e-2)
+        ok = np.allclose(g, r, rtol=1e-2, atol=1e-2) and np.linalg.norm(g - r) <= bound * np.linalg.norm(r)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
@@ -138,3 +140,48 @@ def test_plan_dispatch_groups_by_destination():
     dest = torch.where((flat >= 0) & (flat < 4), flat // 2, torch.full_like(flat, 2))
     order = torch.argsort(dest, stable=True)[:7]
     assert order.tolist() == [1, 2, 4, 0, 3, 5, 6]     # rank 0 pairs first, original order kept
+
+
+def _timeout_worker(rank, world, port, ret):
+    """Rank 0 runs a step with a 2 s limit; rank 1 joins the group but never enters the step
+    (a rank that stalls between steps), then leaves."""
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        if rank == 1:
+            time.sleep(8.0)
+            ret[rank] = "stalled"
+            return
+        moe = ep.ExpertParallelMoE(4, world, rank, lambda x, i, w: x, gather=_cpu_gather, combine=_cpu_combine,
+                                   timeout_s=2.0)
+        x = torch.zeros(8, 64, dtype=torch.bfloat16)
+        ids = torch.zeros(8, 2, dtype=torch.int32)
+        wts = torch.ones(8, 2)
+        t0 = time.time()
+        try:
+            moe.forward(x, ids, wts)
+            ret[rank] = "no error"
+        except ep.ExpertParallelTimeout as exc:
+            ret[rank] = f"timeout after {time.time() - t0:.1f}s: {str(exc)[:60]}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_missing_rank_raises_a_timeout_instead_of_blocking():
+    """Failure detection of the collective transport, injected on the host: one rank never
+    enters the step; the other must get ExpertParallelTimeout within its own short limit."""
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_timeout_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    assert str(ret.get(0, "")).startswith("timeout after"), dict(ret)
+    assert float(str(ret[0]).split()[2].rstrip("s:")) < 7.0

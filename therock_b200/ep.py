@@ -31,7 +31,8 @@ class DispatchPlan:
     n_recv: int
 
 
-def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
+def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, group=None,
+                  timeout_s=None) -> DispatchPlan:
     """Stable grouping of the routed pairs by destination rank and the count exchange."""
     flat = topk_ids.reshape(-1).to(torch.int64)
     n_exp = experts_per_rank * world
@@ -43,10 +44,7 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int, gro
     order = order[:n_send]
     send_counts_t = counts.to(torch.int64)
     recv_counts_t = torch.empty_like(send_counts_t)
-    if world > 1:
-        dist.all_to_all_single(recv_counts_t, send_counts_t, group=group)
-    else:
-        recv_counts_t.copy_(send_counts_t)
+    _a2a(recv_counts_t, send_counts_t, None, None, world, group, timeout_s, "count exchange")
     send_counts = send_counts_t.tolist()
     recv_counts = recv_counts_t.tolist()
     inv = torch.full((flat.numel(),), -1, dtype=torch.int32, device=flat.device)
@@ -69,7 +67,7 @@ class DedupPlan:
 
 
 def plan_dispatch_dedup(topk_ids: torch.Tensor, topk_weight: torch.Tensor, experts_per_rank: int, world: int,
-                        group=None) -> DedupPlan:
+                        group=None, timeout_s=None) -> DedupPlan:
     """Groups a token's pairs by owning rank: a token whose K experts live on d distinct ranks
     sends d rows (each with the K-wide id/weight lists of that rank, k positions kept) instead of K."""
     T, K = topk_ids.shape
@@ -91,19 +89,38 @@ def plan_dispatch_dedup(topk_ids: torch.Tensor, topk_weight: torch.Tensor, exper
     row_ids = torch.where(mine, ids[tok] % experts_per_rank, torch.full_like(ids[tok], -1)).to(torch.int32)
     row_w = torch.where(mine, topk_weight[tok], torch.zeros_like(topk_weight[tok]))
     recv_counts_t = torch.empty_like(counts)
-    if world > 1:
-        dist.all_to_all_single(recv_counts_t, counts, group=group)
-    else:
-        recv_counts_t.copy_(counts)
+    _a2a(recv_counts_t, counts, None, None, world, group, timeout_s, "count exchange")
     recv_counts = recv_counts_t.tolist()
     return DedupPlan(tok=tok.to(torch.int32), ids=row_ids.contiguous(), weights=row_w.contiguous(),
                      send_counts=counts.tolist(), recv_counts=recv_counts, index=index, n_send=n_send,
                      n_recv=int(sum(recv_counts)))
 
 
-def _a2a(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, world: int, group=None):
+class ExpertParallelTimeout(RuntimeError):
+    """A collective of the expert-parallel step did not complete within its limit: a peer rank is
+    missing or stuck.  The process group should be torn down; the step's buffers are undefined."""
+
+
+def _wait(work, timeout_s, what):
+    """Waits for an asynchronous collective with the step's own limit.  (With the NCCL backend
+    torch's watchdog additionally polls the communicator's asynchronous error state and aborts it
+    after the process group's timeout; this limit is usually much shorter.)"""
+    import datetime
+    try:
+        ok = work.wait(timeout=datetime.timedelta(seconds=timeout_s))
+    except RuntimeError as exc:           # gloo raises on expiry, NCCL returns or raises depending on the mode
+        raise ExpertParallelTimeout(f"{what} did not complete within {timeout_s} s: {exc}") from exc
+    if ok is False:
+        raise ExpertParallelTimeout(f"{what} did not complete within {timeout_s} s")
+
+
+def _a2a(out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, world: int, group=None, timeout_s=None,
+         what="all-to-all"):
     if world > 1:
-        dist.all_to_all_single(out, inp, out_splits, in_splits, group=group)
+        if timeout_s is None:
+            dist.all_to_all_single(out, inp, out_splits, in_splits, group=group)
+        else:
+            _wait(dist.all_to_all_single(out, inp, out_splits, in_splits, group=group, async_op=True), timeout_s, what)
     else:
         out.copy_(inp)
 
@@ -118,13 +135,17 @@ class ExpertParallelMoE:
 
     def __init__(self, num_experts: int, world: int, rank: int, local_moe: Callable,
                  gather: Optional[Callable] = None, combine: Optional[Callable] = None, group=None,
-                 dedup: bool = False):
+                 dedup: bool = False, timeout_s: Optional[float] = None):
         if num_experts % world:
             raise ValueError("experts must divide evenly over ranks")
         self.E, self.world, self.rank, self.group = num_experts, world, rank, group
         # dedup: one row per (token, destination rank); the owner sums the token's local experts
         # (k ascending) and returns one partial row, the sender adds the partials in rank order
         self.dedup = dedup
+        # failure detection: with a limit every collective of the step is waited for on the host
+        # and a missing peer raises ExpertParallelTimeout instead of blocking for the process
+        # group's (much longer) timeout
+        self.timeout_s = timeout_s
         self.e_local = num_experts // world
         self.local_moe = local_moe
         self.gather = gather or _cuda_gather
@@ -142,22 +163,22 @@ class ExpertParallelMoE:
         K = topk_ids.shape[1]
         dev = x.device
         self._mark("start")
-        plan = plan_dispatch_dedup(topk_ids, topk_weight, self.e_local, self.world, self.group)
+        plan = plan_dispatch_dedup(topk_ids, topk_weight, self.e_local, self.world, self.group, self.timeout_s)
         self._mark("plan")
         send_rows = self.gather(x, plan.tok)
         send_meta = torch.cat([plan.ids.to(torch.float32), plan.weights.to(torch.float32)], dim=1).contiguous()
         self._mark("pack")
         recv_rows = torch.empty(plan.n_recv, H, dtype=x.dtype, device=dev)
         recv_meta = torch.empty(plan.n_recv, 2 * K, dtype=torch.float32, device=dev)
-        _a2a(recv_rows, send_rows, plan.recv_counts, plan.send_counts, self.world, self.group)
-        _a2a(recv_meta, send_meta, plan.recv_counts, plan.send_counts, self.world, self.group)
+        _a2a(recv_rows, send_rows, plan.recv_counts, plan.send_counts, self.world, self.group, self.timeout_s)
+        _a2a(recv_meta, send_meta, plan.recv_counts, plan.send_counts, self.world, self.group, self.timeout_s)
         self._mark("dispatch")
         ids_local = recv_meta[:, :K].to(torch.int32).contiguous()       # -1 entries are skipped by the operator
         w_local = recv_meta[:, K:].contiguous()
         part = self.local_moe(recv_rows, ids_local, w_local) if plan.n_recv > 0 else recv_rows
         self._mark("local_moe")
         back = torch.empty(plan.n_send, H, dtype=x.dtype, device=dev)
-        _a2a(back, part, plan.send_counts, plan.recv_counts, self.world, self.group)
+        _a2a(back, part, plan.send_counts, plan.recv_counts, self.world, self.group, self.timeout_s)
         self._mark("return")
         out = self.combine(back, plan.index, T, self.world)             # partial rows added in rank order
         self._mark("combine")
@@ -169,7 +190,7 @@ class ExpertParallelMoE:
         T, H = x.shape
         K = topk_ids.shape[1]
         self._mark("start")
-        plan = plan_dispatch(topk_ids, self.e_local, self.world, self.group)
+        plan = plan_dispatch(topk_ids, self.e_local, self.world, self.group, self.timeout_s)
         self._mark("plan")
         dev = x.device
         order32 = plan.order.to(torch.int32)
@@ -182,8 +203,8 @@ class ExpertParallelMoE:
         self._mark("pack")
         recv_rows = torch.empty(plan.n_recv, H, dtype=x.dtype, device=dev)
         recv_meta = torch.empty(plan.n_recv, 2, dtype=torch.float32, device=dev)
-        _a2a(recv_rows, send_rows, plan.recv_counts, plan.send_counts, self.world, self.group)
-        _a2a(recv_meta, send_meta, plan.recv_counts, plan.send_counts, self.world, self.group)
+        _a2a(recv_rows, send_rows, plan.recv_counts, plan.send_counts, self.world, self.group, self.timeout_s)
+        _a2a(recv_meta, send_meta, plan.recv_counts, plan.send_counts, self.world, self.group, self.timeout_s)
         self._mark("dispatch")
         # local experts: every received row is a token with a single expert
         ids_local = recv_meta[:, 0].to(torch.int32).reshape(-1, 1).contiguous()
@@ -192,7 +213,7 @@ class ExpertParallelMoE:
         self._mark("local_moe")
         # return trip and ordered reduction
         back = torch.empty(plan.n_send, H, dtype=x.dtype, device=dev)
-        _a2a(back, part, plan.send_counts, plan.recv_counts, self.world, self.group)
+        _a2a(back, part, plan.send_counts, plan.recv_counts, self.world, self.group, self.timeout_s)
         self._mark("return")
         out = self.combine(back, plan.inv_index, T, K)
         self._mark("combine")
