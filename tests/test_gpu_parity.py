@@ -158,6 +158,17 @@ def test_empty_experts_and_skew():
     check(d, got, run_oracle(d))
 
 
+@pytest.mark.parametrize("partial", ["f32", "bf16"])
+@pytest.mark.parametrize("T,H,I,E,K", [(200, 1792, 256, 6, 2), (64, 3584, 128, 3, 1)])
+def test_hardware_scaled_down_gemm_with_224_column_tiles(T, H, I, E, K, partial):
+    """Hidden sizes that are multiples of 224 (as 7168 is) run the second GEMM of the UE8M0 mode
+    with two 224-column accumulators in tensor memory; the tile's 32-row scale groups then cut
+    across the 128-row weight-scale blocks."""
+    d = O.make_inputs(T, H, I, E, K, 3, "softmax", seed=H + T)
+    got, _ = run_gpu(d, partial)
+    check(d, got, run_oracle(d, partial=partial))
+
+
 def test_tiny_sigmoid_golden():
     cfg = dict(T=48, H=256, I=256, E=16, K=4, routing="sigmoid")
     g = np.load(os.path.join(GOLD, "tiny_sigmoid.npz"))

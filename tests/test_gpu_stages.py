@@ -66,9 +66,9 @@ def test_gathered_activation_bytes_and_scales_are_bit_exact(quant):
     t_live = tok[:npp][live]
     assert (a_q[:npp][live] == ref_q[t_live]).all()
     assert (got_s[:npp][live].view(np.uint32) == ref_s[t_live].view(np.uint32)).all()
-    # pad slots inside the padded range hold zero rows with scale 1
-    assert (a_q[:npp][~live] == 0).all()
-    assert (got_s[:npp][~live] == 1.0).all()
+    # pad slots are left unwritten (their results are never stored): the canary fill is still there
+    from tests.util import CANARY
+    assert (a_q[:npp][~live] == CANARY).all()
 
 
 def test_intermediate_bytes_are_the_oracle_quantisation_of_the_stored_intermediate():

@@ -231,7 +231,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     FMOE_STAGE(1);
     NvtxRange r("gather_quant");
     FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
-                                       a_sorted, a_scale, stream));
+                                       a_sorted, a_scale, stream, nullptr, /*skip_pad=*/true));
   }
   FMOE_STAGE(2);
 

@@ -126,19 +126,19 @@ bool pdl_enabled() {
   return on == 1;
 }
 
-template <int kEpi, bool kHw>
+template <int kEpi, bool kHw, int kNT = kTileN>
 cudaError_t launch_block_variant(const CUtensorMap& ta, const CUtensorMap& tb, const BlockGemmParams& bp, int grid,
                                  cudaStream_t stream) {
   static bool configured[kMaxDevices] = {false};
   const int dev = current_device();
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpi, kHw>,
+    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_block_kernel<kEpi, kHw, kNT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kBlockSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpi, kHw>, dim3(grid), dim3(kBlockGemmThreads), kBlockSmemBytes,
-                    stream, ta, tb, bp);
+  return launch_pdl(fmoe_grouped_gemm_block_kernel<kEpi, kHw, kNT>, dim3(grid), dim3(kBlockGemmThreads),
+                    kBlockSmemBytes, stream, ta, tb, bp);
 }
 
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
@@ -205,6 +205,22 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     bp.k_blocks = p.k_iters;
     bp.out_scale = g.out_scale;
     const bool hw = g.flavour == FMOE_KERNEL_BLOCK_HW_SCALE;
+    if (hw && g.epilogue == kEpiScaledSlots && !g.b_tiled && g.ld_out % 224 == 0 && g.n_stride == kTileN) {
+      // Output width tiles by 224: two 224-column accumulators fit tensor memory beside the scale
+      // buffers, so the drain of one tile overlaps the MMAs of the next.
+      CUtensorMap tb224;
+      CUresult r2 = make_map(&tb224, g.b, true, static_cast<int64_t>(g.num_experts) * g.b_rows_per_expert, g.k_elems, 112);
+      if (r2 != CUDA_SUCCESS) {
+        if (drv_err) *drv_err = static_cast<int>(r2);
+        return cudaErrorInvalidValue;
+      }
+      bp.g.n_blocks = g.ld_out / 224;
+      bp.g.n_stride = 224;
+      bp.g.second_slab_offset = 112;
+      const long long tiles224 = static_cast<long long>(g.max_m_blocks) * bp.g.n_blocks;
+      const int grid224 = static_cast<int>(tiles224 < sm_count() ? (tiles224 > 0 ? tiles224 : 1) : sm_count());
+      return launch_block_variant<kEpiScaledSlots, true, 224>(ta, tb224, bp, grid224, stream);
+    }
     if (g.epilogue == kEpiSiluMul) {
       if (g.out_scale == nullptr) return cudaErrorInvalidValue;   // the first GEMM always quantises its output
       return hw ? launch_block_variant<kEpiSiluMul, true>(ta, tb, bp, grid, stream)

@@ -62,7 +62,11 @@ struct BlockGemmParams {
                                 // or UE8M0 bytes [cap, scale_pitch(ld_out/128)] (kHw); `g.out` then receives e4m3
 };
 
-template <int kEpi, bool kHw>
+// kNT: accumulator columns of one tile.  256 in general.  224 is the double-buffered form of the
+// hardware-scaled second GEMM: two 224-column accumulators and the scale buffers fit the 512
+// columns of tensor memory (2 * 224 + 2 * 16), so the drain of tile i overlaps the MMAs of tile
+// i+1; it needs an output width that is a multiple of 224 (7168 = 32 * 224) and row-major weights.
+template <int kEpi, bool kHw, int kNT = kTileN>
 __global__ void __launch_bounds__(kBlockGemmThreads, 1)
 fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
                                const __grid_constant__ CUtensorMap tm_b, const BlockGemmParams bp) {
@@ -88,6 +92,11 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   constexpr int kUmmaKBytes = 32;
+  static_assert(kNT == kTileN || (kNT == 224 && kHw && kEpi == kEpiScaledSlots), "224-column tiles: hardware-scaled second GEMM only");
+  constexpr int kSlab = kNT / 2;                       // rows of one B slab
+  constexpr int kAccBufs = kNT == kTileN ? 1 : 2;      // accumulators in tensor memory (hardware-scaled flavour)
+  constexpr int kSfCol = kAccBufs * kNT;               // scale columns start behind the accumulators
+  constexpr int kTxBytes = kABytes + kNT * kStageKBytes;
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_a);
@@ -149,14 +158,14 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
             continue;
           }
-          ptx::mbar_arrive_expect_tx(full, kStageBytes);
+          ptx::mbar_arrive_expect_tx(full, kTxBytes);
           const int kx = k * 128;
           int bx, by0, by1;
           b_coords(p, b_row0, k, 128, bx, by0);
           b_coords(p, b_row1, k, 128, bx, by1);
           ptx::tma_load_2d(sa, &tm_a, full, kx, a_row);
           ptx::tma_load_2d(sb, &tm_b, full, bx, by0);
-          ptx::tma_load_2d(sb + kSlabRows * kStageKBytes, &tm_b, full, bx, by1);
+          ptx::tma_load_2d(sb + kSlab * kStageKBytes, &tm_b, full, bx, by1);
           if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -167,22 +176,24 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t phase = 0;
       bool ok = true;
       if (kHw) {
-        // one accumulator; scales copied to tensor memory once per four stages
+        // accumulator(s) stay in tensor memory; scales copied there once per four stages
+        int acc = 0;
         uint32_t acc_phase = 0;
         int sf_slot = 0;
         uint32_t sf_phase = 0;
         int sf_buf = 0;
-        const uint32_t idesc0 = ptx::make_idesc_block_scaled(kBlockM, kTileN);
+        const uint32_t idesc0 = ptx::make_idesc_block_scaled(kBlockM, kNT);
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-          if (!ptx::mbar_wait(ptx::smem_u32(&part_empty_bar[0]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(ptx::smem_u32(&part_empty_bar[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kNT);
           uint32_t sfa_t = 0, sfb_t = 0;
           for (int k = 0; k < p.k_iters; ++k) {
             if ((k & 3) == 0) {
               if (!ptx::mbar_wait(ptx::smem_u32(&sf_full_bar[sf_slot]), sf_phase, abort_flag)) { ok = false; break; }
               ptx::tc_fence_after();
               const uint32_t src = ptx::smem_u32(sf_ring + sf_slot * kSfSlotBytes);
-              sfa_t = tmem_base + static_cast<uint32_t>(kSfTmemCol + sf_buf * 16);
+              sfa_t = tmem_base + static_cast<uint32_t>(kSfCol + sf_buf * 16);
               sfb_t = sfa_t + 4;
               ptx::tmem_cp_32x128b_warpx4(sfa_t, ptx::make_rows16_desc(src));
               ptx::tmem_cp_32x128b_warpx4(sfb_t, ptx::make_rows16_desc(src + 512));
@@ -201,14 +212,14 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
             for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
               const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
               if (!FMOE_DBG(p, 2u))
-                ptx::umma_mxf8_block_scale(tmem_base, da + adv, db + adv, idesc, sfa_t, sfb_t, (k | kk) ? 1u : 0u);
+                ptx::umma_mxf8_block_scale(d_tmem, da + adv, db + adv, idesc, sfa_t, sfb_t, (k | kk) ? 1u : 0u);
             }
             ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
             if (++stage == kBlockStages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
-          ptx::umma_commit(ptx::smem_u32(&part_full_bar[0]));
-          acc_phase ^= 1u;
+          ptx::umma_commit(ptx::smem_u32(&part_full_bar[acc]));
+          if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
         }
       } else {
         int buf = 0;
@@ -249,8 +260,12 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
         const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
-        const float* sb0 = bp.b_scale + static_cast<size_t>(b_row0 / 128) * kb_n;
-        const float* sb1 = bp.b_scale + static_cast<size_t>((b_row0 + p.second_slab_offset) / 128) * kb_n;
+        // lane c < 8 serves the 32-row group c of the B tile: rows below kSlab belong to the first
+        // slab, the others to the second; a group never straddles a 128-row scale block
+        const int grow = 32 * (lane & 7);
+        const int g_row = grow < kSlab ? b_row0 + grow : b_row0 + p.second_slab_offset + (grow - kSlab);
+        const float* sb_l = bp.b_scale + static_cast<size_t>(g_row / 128) * kb_n;
+        const bool g_live = grow < kNT;
         for (int g = 0; g < kg_n; ++g) {
           // loads first, so their latency overlaps the wait for a free slot
           // image row `lane` = the four-byte words (K groups 4g..4g+3) of rows lane, 32+lane, 64+lane, 96+lane
@@ -260,21 +275,23 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
           av.y = __ldg(reinterpret_cast<const uint32_t*>(arow + 32 * a_pitch));
           av.z = __ldg(reinterpret_cast<const uint32_t*>(arow + 64 * a_pitch));
           av.w = __ldg(reinterpret_cast<const uint32_t*>(arow + 96 * a_pitch));
-          uint32_t w0 = 0, w1 = 0;
+          uint32_t wl = 0;
+          if (g_live) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int kb = 4 * g + j;
-            if (kb < kb_n) {
+            for (int j = 0; j < 4; ++j) {
+              const int kb = 4 * g + j;
               // a power of two's biased exponent is its UE8M0 byte
-              w0 |= ((__float_as_uint(__ldg(sb0 + kb)) >> 23) & 0xffu) << (8 * j);
-              w1 |= ((__float_as_uint(__ldg(sb1 + kb)) >> 23) & 0xffu) << (8 * j);
+              if (kb < kb_n) wl |= ((__float_as_uint(__ldg(sb_l + kb)) >> 23) & 0xffu) << (8 * j);
             }
           }
+          uint32_t w[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) w[c] = __shfl_sync(0xffffffffu, wl, c);
           if (!ptx::mbar_wait(ptx::smem_u32(&sf_empty_bar[slot]), sphase ^ 1u, abort_flag)) { ok = false; break; }
           uint4* dst = reinterpret_cast<uint4*>(sf_ring + slot * kSfSlotBytes);
           dst[lane] = av;
-          dst[32 + lane] = make_uint4(w0, w0, w0, w0);
-          dst[64 + lane] = make_uint4(w1, w1, w1, w1);
+          dst[32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);     // every row of a 32-row group shares its scale
+          dst[64 + lane] = make_uint4(w[4], w[5], w[6], w[7]);
           ptx::fence_proxy_async();      // generic-proxy stores above are read by tcgen05.cp
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&sf_full_bar[slot]));
@@ -302,27 +319,49 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int col0 = (kEpi == kEpiSiluMul) ? half * 64 : half * 128;
       const int col1 = (kEpi == kEpiSiluMul) ? kSlabRows + half * 64 : half * 128 + 64;
       if (kHw) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&part_full_bar[0]), buf_phase, abort_flag)) { ok = false; break; }
+        if (!ptx::mbar_wait(ptx::smem_u32(&part_full_bar[buf]), buf_phase, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
-        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(buf * kNT);
+        if (kNT == kTileN) {
 #pragma unroll
-        for (int rnd = 0; rnd < 2; ++rnd) {
+          for (int rnd = 0; rnd < 2; ++rnd) {
+            uint32_t v[2][32];
+            const int cbase = rnd == 0 ? col0 : col1;
+            ptx::tmem_ld_32x32(t_row + cbase, v[0]);
+            ptx::tmem_ld_32x32(t_row + cbase + 32, v[1]);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                acc[rnd * 32 + c * 16 + j] = ptx::pack2(__uint_as_float(v[c][2 * j]), __uint_as_float(v[c][2 * j + 1]));
+          }
+        } else {
+          // 112 columns per thread: 32 + 32 + 32 + 16
+          const int cb = half * (kNT / 2);
           uint32_t v[2][32];
-          const int cbase = rnd == 0 ? col0 : col1;
-          ptx::tmem_ld_32x32(t_row + cbase, v[0]);
-          ptx::tmem_ld_32x32(t_row + cbase + 32, v[1]);
+          ptx::tmem_ld_32x32(t_row + cb, v[0]);
+          ptx::tmem_ld_32x32(t_row + cb + 32, v[1]);
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              acc[rnd * 32 + c * 16 + j] = ptx::pack2(__uint_as_float(v[c][2 * j]), __uint_as_float(v[c][2 * j + 1]));
+              acc[c * 16 + j] = ptx::pack2(__uint_as_float(v[c][2 * j]), __uint_as_float(v[c][2 * j + 1]));
+          uint32_t t16[16];
+          ptx::tmem_ld_32x32(t_row + cb + 64, v[0]);
+          ptx::tmem_ld_32x16(t_row + cb + 96, t16);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[32 + j] = ptx::pack2(__uint_as_float(v[0][2 * j]), __uint_as_float(v[0][2 * j + 1]));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[48 + j] = ptx::pack2(__uint_as_float(t16[2 * j]), __uint_as_float(t16[2 * j + 1]));
         }
-        // the accumulator is in registers: the next tile may overwrite tensor memory
+        // the accumulator is in registers: a later tile may overwrite this part of tensor memory
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&part_empty_bar[0]));
-        buf_phase ^= 1u;
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&part_empty_bar[buf]));
+        if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1u; }
       } else {
         const float* a_scale_f = reinterpret_cast<const float*>(bp.a_scale);
         const float* sa_row = a_scale_f + static_cast<size_t>(slot) * kb_n;
@@ -490,41 +529,41 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
       } else if (kEpi == kEpiScaledSlots) {
         const float wt = p.sorted_weights[slot];
+        constexpr int kOwn = kNT / 2;                 // output channels of this thread: acc[0 .. kOwn/2)
+        const int col_base = tc.n_blk * kNT + half * kOwn;
         if (p.out_bf16) {
-          __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.out) + tc.n_blk * kTileN + half * 128;
+          __nv_bfloat16* hbase = reinterpret_cast<__nv_bfloat16*>(p.out) + col_base;
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {            // 32 columns (16 bf16 pairs) per chunk
-            uint32_t w[16];
+          for (int ch = 0; ch < kOwn / 16; ++ch) {     // 16 columns (8 bf16 pairs) per chunk
+            uint32_t w[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < 8; ++j) {
               float a0, a1;
-              ptx::unpack2(acc[ch * 16 + j], a0, a1);
+              ptx::unpack2(acc[ch * 8 + j], a0, a1);
               const __nv_bfloat162 v2 = __floats2bfloat162_rn(wt * a0, wt * a1);
               w[j] = *reinterpret_cast<const uint32_t*>(&v2);
             }
             __syncwarp();
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              reinterpret_cast<uint4*>(stage + lane * 20)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            reinterpret_cast<uint4*>(stage + lane * 20)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(stage + lane * 20)[1] = make_uint4(w[4], w[5], w[6], w[7]);
             __syncwarp();
 #pragma unroll
-            for (int it = 0; it < 4; ++it) {
-              const int r = it * 8 + (lane >> 2);
-              const int seg = lane & 3;
+            for (int it = 0; it < 2; ++it) {           // 2 lanes per row, 16 rows per store instruction
+              const int r = it * 16 + (lane >> 1);
+              const int seg = lane & 1;
               const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 20 + seg * 4);
               const int row_r = __shfl_sync(0xffffffffu, row, r);
               if (row_r >= 0 && FMOE_ROW_OK(p, row_r)) {
-                __nv_bfloat16* drow = p.row_ptrs
-                    ? reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row_r]) + tc.n_blk * kTileN + half * 128
-                    : hbase + static_cast<size_t>(row_r) * p.ld_out;
-                *reinterpret_cast<uint4*>(drow + ch * 32 + seg * 8) = val;
+                __nv_bfloat16* drow = p.row_ptrs ? reinterpret_cast<__nv_bfloat16*>(p.row_ptrs[row_r]) + col_base
+                                                 : hbase + static_cast<size_t>(row_r) * p.ld_out;
+                *reinterpret_cast<uint4*>(drow + ch * 16 + seg * 8) = val;
               }
             }
           }
         } else {
-          float* obase = reinterpret_cast<float*>(p.out) + tc.n_blk * kTileN + half * 128;
+          float* obase = reinterpret_cast<float*>(p.out) + col_base;
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {            // 16 columns per chunk
+          for (int ch = 0; ch < kOwn / 16; ++ch) {     // 16 columns per chunk
             __syncwarp();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {

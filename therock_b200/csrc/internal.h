@@ -47,9 +47,11 @@ constexpr size_t sort_scratch_words(int E) { return 2 * 64 * static_cast<size_t>
 //   quant 0: dst bf16 [cap, cols].  quant 1: dst e4m3 [cap, cols] + scales[cap] (one per
 //   row).  quant 2: dst e4m3 + scales [cap, cols/128] (one per 128 columns).
 //   live_ids (optional, [cap]): slots whose entry is negative are skipped entirely.
+//   skip_pad: pad slots (row id outside the source) are left unwritten instead of zero-filled.
 cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32_t* row_ids,
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
-                               void* scales, cudaStream_t stream, const int32_t* live_ids = nullptr);
+                               void* scales, cudaStream_t stream, const int32_t* live_ids = nullptr,
+                               bool skip_pad = false);
 
 // Decode-sized batches (T*K <= 128, bf16 or per-token-quantised activations): moe_sorting and the
 // gather (+ quantisation) in one launch.  Pad slots of a_sorted are left unwritten.
