@@ -249,6 +249,7 @@ decode_prologue_kernel(const int32_t* __restrict__ topk_ids, const float* __rest
   ptx::pdl_release();
   __shared__ int32_t ids_s[kProloguePairs];
   __shared__ int32_t slot_s[kProloguePairs];
+  __shared__ int32_t first_s[kProloguePairs];
   __shared__ float warp_max[kRowThreads / 32];
   __shared__ float row_scale;
   const int tid = threadIdx.x;
@@ -261,21 +262,24 @@ decode_prologue_kernel(const int32_t* __restrict__ topk_ids, const float* __rest
   }
   if (tid < kProloguePairs) ids_s[tid] = my_e;
   __syncthreads();
-  // slot of pair `tid`: (distinct experts below mine that are hit) * 128 + (earlier pairs of my expert)
-  if (tid < R) {
-    int blocks_before = 0, rank = 0;
-    if (my_e >= 0) {
-      for (int j = 0; j < R; ++j) {
-        const int ej = ids_s[j];
-        if (ej < 0) continue;
-        if (ej == my_e) { rank += (j < tid); continue; }
-        if (ej < my_e) {
-          bool first = true;                         // count each expert once: at its first pair
-          for (int j2 = 0; j2 < j; ++j2) first = first && (ids_s[j2] != ej);
-          blocks_before += first;
-        }
+  // first_s[j]: pair j is the first pair of its expert.  The slot of pair `tid` is
+  // (experts below mine that are hit) * 128 + (earlier pairs of my expert).
+  int rank = 0;
+  if (tid < kProloguePairs) {
+    bool first = my_e >= 0;
+    if (my_e >= 0)
+      for (int j = 0; j < tid; ++j) {
+        const bool same = ids_s[j] == my_e;
+        rank += same;
+        first = first && !same;
       }
-    }
+    first_s[tid] = first ? 1 : 0;
+  }
+  __syncthreads();
+  if (tid < R) {
+    int blocks_before = 0;
+    if (my_e >= 0)
+      for (int j = 0; j < R; ++j) blocks_before += (first_s[j] && ids_s[j] < my_e);
     slot_s[tid] = my_e >= 0 ? blocks_before * 128 + rank : -1;
   }
   __syncthreads();
@@ -299,13 +303,7 @@ decode_prologue_kernel(const int32_t* __restrict__ topk_ids, const float* __rest
     // cumulative blocks per expert: experts that are hit own one block each
     for (int e = tid; e <= E; e += kRowThreads) {
       int below = 0;                                 // distinct hit experts with id < e
-      for (int j = 0; j < R; ++j) {
-        const int ej = ids_s[j];
-        if (ej < 0 || ej >= e) continue;
-        bool first = true;
-        for (int j2 = 0; j2 < j; ++j2) first = first && (ids_s[j2] != ej);
-        below += first;
-      }
+      for (int j = 0; j < R; ++j) below += (first_s[j] && ids_s[j] < e);
       mblk_cum[e] = below;
       if (e == E) num_post_pad[0] = below * 128;
     }
