@@ -43,8 +43,10 @@ __device__ __forceinline__ uint2 quant8(const float (&f)[8], float inv_scale) {
   return make_uint2(lo, hi);
 }
 
-// One CTA per sorted slot.
-template <int kQuant>
+// One CTA per sorted slot.  kHeld: 16-byte vectors of the row one thread keeps in registers in
+// the per-row mode (4 covers rows of up to 4096 elements with 128 threads); a smaller value
+// means fewer registers, more resident CTAs and more bytes in flight for the common widths.
+template <int kQuant, int kHeld = 16>
 __global__ void __launch_bounds__(kRowThreads)
 gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
                    const int32_t* __restrict__ row_ids, const int32_t* __restrict__ num_post_pad,
@@ -78,7 +80,7 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
     // per-row scale: the row is read once into registers (up to kMaxVec vectors per thread,
     // i.e. rows of up to 16384 elements with 128 threads), reduced block-wide, then quantised from registers;
     // longer rows fall back to a second read.
-    constexpr int kMaxVec = 16;
+    constexpr int kMaxVec = kHeld;
     __shared__ float warp_max[kRowThreads / 32];
     __shared__ float row_scale;
     const bool in_regs = nvec <= kMaxVec * kRowThreads;
@@ -394,8 +396,14 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
   const int sp = skip_pad ? 1 : 0;
   if (quant == 0)
     return launch_pdl(gather_rows_kernel<0>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
-  else if (quant == 1)
+  else if (quant == 1) {
+    const int nvec = cols >> 3;
+    if (nvec <= 4 * kRowThreads)
+      return launch_pdl(gather_rows_kernel<1, 4>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
+    if (nvec <= 8 * kRowThreads)
+      return launch_pdl(gather_rows_kernel<1, 8>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
     return launch_pdl(gather_rows_kernel<1>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
+  }
   else if (quant == 2)
     return launch_pdl(gather_rows_kernel<2>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
   else
