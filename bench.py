@@ -79,10 +79,14 @@ def route_on_device(logits, K, mode):
 # last capture has no entry and reports traffic = null.
 GEMM1_DRAM_TRAFFIC = {
     "C1": dict(read=1957748480, write=241425664, source="profiles/grouped_gemm_bf16_mixtral_prefill.md",
-               quote="1,957,748,480 B read + 241,425,664 B written"),
+               quotes=["1,957,748,480 B read + 241,425,664 B written"]),
     "C2": dict(read=1.300e9, write=456e6, source="profiles/grouped_gemm_pair_fp8_mixtral_prefill.md",
-               quote="1.300 GB / 456 MB"),
-    "C3": dict(read=947.1e6, write=4.6e6, source="profiles/decode_fp8_stage_times.md", quote="947.1 MB / 4.6 MB"),
+               quotes=["1.300 GB / 456 MB"]),
+    "C3": dict(read=942.0e6, write=5.8e6, source="profiles/decode_fp8_stage_times.md", quotes=["942.0 MB + 5.8 MB"]),
+    # captured on one eighth of the workload (32 of 256 experts, 1024 of 8192 tokens: the same rows
+    # per expert); weights, activations and outputs all scale with that factor
+    "C4m": dict(read=8 * 1.035734e9, write=8 * 19.909376e6, source="profiles/deepseek_block128_ue8m0_fp8.md",
+                quotes=["1.035734", "19.909376"], scaled="x8 from the 32-expert / 1024-token capture"),
 }
 NOMINAL = dict(bf16_tflops=2250.0, fp8_tflops=4500.0, hbm_gbs=8000.0)
 
@@ -475,7 +479,7 @@ def roofline_entry(c, cfg_name, info, per, clocks, ms_total, ms_step, peaks, fp8
     r["ms_per_launch"] = g1_ms
     r["traffic"] = None if tr is None else tr["read"] + tr["write"]
     if tr is not None:
-        r["traffic_source"] = f"{tr['source']}: {tr['quote']}"
+        r["traffic_source"] = f"{tr['source']}: {' / '.join(tr['quotes'])}" + (f" ({tr['scaled']})" if "scaled" in tr else "")
     r["gemm2_kernel"] = info["gemm2_kernel_name"]
     return r
 

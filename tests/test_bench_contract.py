@@ -15,7 +15,9 @@ def test_traffic_table_is_quoted_in_the_profiles():
     for name, t in bench.GEMM1_DRAM_TRAFFIC.items():
         path = os.path.join(ROOT, t["source"])
         assert os.path.exists(path), f"{name}: {t['source']} is missing"
-        assert t["quote"] in open(path).read(), f"{name}: '{t['quote']}' does not appear in {t['source']}"
+        text = open(path).read()
+        for q in t["quotes"]:
+            assert q in text, f"{name}: '{q}' does not appear in {t['source']}"
         assert t["read"] > 0 and t["write"] >= 0
 
 
@@ -59,7 +61,10 @@ def test_decode_roofline_is_against_hbm():
 def test_fine_grained_shape_reports_both_rooflines():
     c = dict(bench.CONFIGS["C4m"])
     r = bench.roofline_entry(c, "C4m", INFO, dict(STAGES, gemm1=2.2), None, 100.0, 4.2, PEAKS, None, False)
-    assert r["bound"] == "tensor" and "hbm" in r and r["traffic"] is None
+    assert r["bound"] == "tensor" and "hbm" in r
+    assert abs(r["traffic"] - 8 * (1.035734e9 + 19.909376e6)) < 1 and "x8" in r["traffic_source"]
+    c4 = dict(bench.CONFIGS["C4"])
+    assert bench.roofline_entry(c4, "C4", INFO, dict(STAGES, gemm1=3.4), None, 100.0, 6.7, PEAKS, None, False)["traffic"] is None
 
 
 def test_workload_config_names_the_workload_without_model_keys():
