@@ -150,7 +150,9 @@ def _worker(rank, world, port, quant, ret, dedup=False):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        d = O.make_inputs(256, 512, 256, 8, 4 if dedup else 2, quant, "softmax", seed=22)
+        # de-duplicated: K = 5 exceeds the 4 experts a rank owns, so the local operator sees
+        # K-wide id lists with more columns than it has experts
+        d = O.make_inputs(256, 512, 256, 8, 5 if dedup else 2, quant, "softmax", seed=22)
         got, sl = _rank_forward(d, rank, world, f"cuda:{rank}", dedup=dedup)
         ref = O.fused_moe(d["x"], d["w1"], d["w2"], d["topk_ids"], d["topk_w"], quant, d["w1_scale"], d["w2_scale"],
                           sel=np.arange(sl.start, sl.stop, dtype=np.int32), partial_bf16=not dedup)
