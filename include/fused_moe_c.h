@@ -187,6 +187,9 @@ typedef struct fmoe_ws_layout_c {
   uint64_t y_scale;           /* as a_scale, with I in place of H */
   uint64_t slots;             /* float or bf16 (traits.partial_dtype) [T*K, H]: weighted expert outputs */
   uint64_t sort_scratch;      /* int32[128*E]: per-CTA histograms of the multi-CTA moe_sorting */
+  uint64_t x_quant;           /* e4m3 [T, H]: the token rows quantised once (fp8 variants with K >= 2, not
+                                 decode-sized); a_sorted is then gathered from here */
+  uint64_t x_quant_scale;     /* their scales, laid out as a_scale with T rows */
 } fmoe_ws_layout_c;
 
 FMOE_API int fmoe_get_workspace_layout(const fmoe_traits_c* traits, const fmoe_args_c* args,

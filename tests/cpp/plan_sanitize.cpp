@@ -75,7 +75,7 @@ int main() {
         const fmoe_ws_layout_c& l = p.l;
         const uint64_t offs[] = {l.meta, l.sorted_token_ids, l.sorted_weights, l.sorted_rows, l.sorted_expert_ids,
                                  l.mblk_cum, l.a_sorted, l.a_scale, l.y, l.y_quant, l.y_scale, l.slots,
-                                 l.sort_scratch, l.total_bytes};
+                                 l.sort_scratch, l.x_quant, l.x_quant_scale, l.total_bytes};
         for (size_t i = 0; i + 1 < sizeof(offs) / sizeof(offs[0]); ++i) {
           EXPECT(offs[i] % 256 == 0);
           EXPECT(offs[i] <= offs[i + 1]);
@@ -87,7 +87,7 @@ int main() {
         std::memset(&info, 0, sizeof(info));
         EXPECT(describe_run(&tq, &aq, 148, 0, &info) == FMOE_OK);
         EXPECT(info.gemm1_kernel >= FMOE_KERNEL_SINGLE && info.gemm1_kernel <= FMOE_KERNEL_SINGLE_DECODE);
-        EXPECT(info.launches >= 4 && info.launches <= 8);   // decode prologue (one launch for sort + gather) up to the multi-CTA sort + quantised intermediate
+        EXPECT(info.launches >= 4 && info.launches <= 9);   // decode prologue (one launch for sort + gather) up to multi-CTA sort + quantise-once + quantised intermediate
         if (q == FMOE_QUANT_BLOCK128_UE8M0) EXPECT(info.gemm1_kernel == FMOE_KERNEL_BLOCK_HW_SCALE);
       }
     }

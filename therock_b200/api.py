@@ -52,7 +52,7 @@ class _Layout(ctypes.Structure):
     _fields_ = [("capacity", ctypes.c_int64)] + [(n, ctypes.c_uint64) for n in (
         "total_bytes", "meta", "sorted_token_ids", "sorted_weights", "sorted_rows",
         "sorted_expert_ids", "mblk_cum", "a_sorted", "a_scale", "y", "y_quant", "y_scale", "slots",
-        "sort_scratch")]
+        "sort_scratch", "x_quant", "x_quant_scale")]
 
 
 class EpLayout(ctypes.Structure):

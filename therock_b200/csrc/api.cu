@@ -230,8 +230,17 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     }
     FMOE_STAGE(1);
     NvtxRange r("gather_quant");
-    FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
-                                       a_sorted, a_scale, stream, nullptr, /*skip_pad=*/true));
+    if (fmoe::quantise_once(traits, args)) {
+      // every token row is quantised once; the routed pairs then copy e4m3 rows and scales
+      void* xq = ws + l.x_quant;
+      void* xq_scale = ws + l.x_quant_scale;
+      FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, nullptr, a.num_tokens_dev, a.T, qmode, xq, xq_scale, stream));
+      FMOE_CUDA(fmoe::launch_gather_quantised(xq, xq_scale, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
+                                              a_sorted, a_scale, stream));
+    } else {
+      FMOE_CUDA(fmoe::launch_gather_rows(a.x, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
+                                         a_sorted, a_scale, stream, nullptr, /*skip_pad=*/true));
+    }
   }
   FMOE_STAGE(2);
 

@@ -43,7 +43,7 @@ constexpr size_t sort_scratch_words(int E) { return 2 * 64 * static_cast<size_t>
 
 // Gather rows of a bf16 matrix into sorted order, optionally quantising each row to e4m3.
 //   src [n_src, cols] bf16; row_ids [cap] (entry >= n_src means pad -> zero row) or null
-//   for identity; only slots < *num_post_pad are touched.
+//   for identity; only slots < *num_post_pad are touched (num_post_pad null: all `cap` slots).
 //   quant 0: dst bf16 [cap, cols].  quant 1: dst e4m3 [cap, cols] + scales[cap] (one per
 //   row).  quant 2: dst e4m3 + scales [cap, cols/128] (one per 128 columns).
 //   live_ids (optional, [cap]): slots whose entry is negative are skipped entirely.
@@ -52,6 +52,12 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
                                const int32_t* num_post_pad, int64_t cap, int quant, void* dst,
                                void* scales, cudaStream_t stream, const int32_t* live_ids = nullptr,
                                bool skip_pad = false);
+
+// dst[slot] = src[row_ids[slot]] for rows that are already e4m3 with their scales (quant 1, 2, 3 as
+// above); only slots < *num_post_pad with a valid row id are written.  cols must be a multiple of 16.
+cudaError_t launch_gather_quantised(const void* src, const void* src_scale, int n_src, int cols,
+                                    const int32_t* row_ids, const int32_t* num_post_pad, int64_t cap, int quant,
+                                    void* dst, void* dst_scale, cudaStream_t stream);
 
 // Decode-sized batches (T*K <= 128, bf16 or per-token-quantised activations): moe_sorting and the
 // gather (+ quantisation) in one launch.  Pad slots of a_sorted are left unwritten.

@@ -102,6 +102,16 @@ inline uint64_t packed_scale_bytes(int64_t cap, int k_elems) {
   return static_cast<uint64_t>(cap) * static_cast<uint64_t>(packed_scale_pitch(k_elems));
 }
 
+// Decode-sized batches without block scales run sorting + gather (+ quantisation) as one kernel.
+inline bool fused_prologue(const fmoe_traits_c* t, const fmoe_args_c* a) {
+  return static_cast<long long>(a->T) * a->K <= 128 &&
+         (t->quant == FMOE_QUANT_NONE || t->quant == FMOE_QUANT_TOKEN_CHANNEL);
+}
+// fp8, K >= 2 and not decode-sized: quantise the T token rows once, then gather e4m3 rows.
+inline bool quantise_once(const fmoe_traits_c* t, const fmoe_args_c* a) {
+  return quant_is_fp8(t->quant) && a->K >= 2 && !fused_prologue(t, a) && a->H % 16 == 0;
+}
+
 inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
   const int64_t cap = sort_capacity(a->T, a->K, a->E, t->block_m);
   const bool fp8 = quant_is_fp8(t->quant);
@@ -130,6 +140,12 @@ inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
   else l.y_scale = take(static_cast<uint64_t>(cap) * 4 * (blk ? a->I / 128 : 1));
   l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * (t->partial_dtype == FMOE_PARTIAL_BF16 ? 2 : 4));
   l.sort_scratch = take(static_cast<uint64_t>(2 * kSortMaxCtasPlan) * a->E * 4);
+  // fp8 with several experts per token: the token rows are quantised once, then gathered as e4m3
+  const bool once = quantise_once(t, a);
+  l.x_quant = take(once ? static_cast<uint64_t>(a->T) * a->H : 0);
+  if (!once) l.x_quant_scale = take(0);
+  else if (hw) l.x_quant_scale = take(packed_scale_bytes(a->T, a->H));
+  else l.x_quant_scale = take(static_cast<uint64_t>(a->T) * 4 * (blk ? a->H / 128 : 1));
   l.total_bytes = off;
   return FMOE_OK;
 }
@@ -166,10 +182,9 @@ inline int describe_run(const fmoe_traits_c* t, const fmoe_args_c* a, int sms, i
   info->quant_y_launch = (t->quant == FMOE_QUANT_TOKEN_CHANNEL || (quant_is_block(t->quant) && !kFusedBlockQuant)) ? 1 : 0;
   // sort, gather(+quant), gemm1, [quant of the intermediate], gemm2, combine; decode-sized
   // batches without block scales run sort and gather as one kernel
-  const bool fused_prologue = static_cast<long long>(a->T) * a->K <= 128 &&
-                              (t->quant == FMOE_QUANT_NONE || t->quant == FMOE_QUANT_TOKEN_CHANNEL);
-  if (fused_prologue) info->sort_launches = 0;
+  if (fused_prologue(t, a)) info->sort_launches = 0;
   info->launches = info->sort_launches + 1 + 1 + info->quant_y_launch + 1 + 1;
+  if (quantise_once(t, a)) info->launches += 1;      // quantise the token rows, then gather them
   if (a->partial_row_ptrs) info->launches -= 1;      // scattered partial rows: no combine
   return FMOE_OK;
 }

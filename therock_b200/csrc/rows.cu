@@ -56,7 +56,7 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
   ptx::pdl_wait();
   ptx::pdl_release();
   const int slot = blockIdx.x;
-  if (slot >= *num_post_pad) return;
+  if (num_post_pad != nullptr && slot >= *num_post_pad) return;
   // identity mode (quantising the intermediate): slots without a token are skipped outright
   if (live_ids != nullptr && live_ids[slot] < 0) return;
   const int row = row_ids ? row_ids[slot] : slot;
@@ -227,6 +227,36 @@ combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ top
     __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
     out[static_cast<size_t>(t) * nvec + i] =
         make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+}
+
+// Rows that are already quantised (one pass over the T token rows) -> sorted order: each routed
+// pair copies its token's e4m3 row and scale(s).  With K experts per token this moves K e4m3 rows
+// instead of quantising the same bf16 row K times.  Pad slots are left unwritten.
+//   kQuant 1: scales f32 [rows]; 2: f32 [rows, cols/128]; 3: UE8M0 bytes [rows, pitch].
+template <int kQuant>
+__global__ void __launch_bounds__(kRowThreads)
+gather_quantised_kernel(const uint4* __restrict__ src, const void* __restrict__ src_scale, int n_src, int cols,
+                        const int32_t* __restrict__ row_ids, const int32_t* __restrict__ num_post_pad,
+                        uint4* __restrict__ dst, void* __restrict__ dst_scale) {
+  ptx::pdl_wait();
+  ptx::pdl_release();
+  const int slot = blockIdx.x;
+  if (slot >= *num_post_pad) return;
+  const int row = row_ids[slot];
+  if (row < 0 || row >= n_src) return;
+  const int nvec = cols >> 4;                       // 16 e4m3 per 16-byte vector
+  const uint4* s = src + static_cast<size_t>(row) * nvec;
+  uint4* d = dst + static_cast<size_t>(slot) * nvec;
+  for (int i = threadIdx.x; i < nvec; i += kRowThreads) d[i] = s[i];
+  if (kQuant == 1) {
+    if (threadIdx.x == 0) reinterpret_cast<float*>(dst_scale)[slot] = reinterpret_cast<const float*>(src_scale)[row];
+  } else {
+    // 32-bit words per row: cols/128 floats, or pitch/4 words of packed UE8M0 bytes
+    const int words = kQuant == 2 ? (cols >> 7) : (scale_pitch(cols >> 7) >> 2);
+    const uint32_t* ss = reinterpret_cast<const uint32_t*>(src_scale) + static_cast<size_t>(row) * words;
+    uint32_t* ds = reinterpret_cast<uint32_t*>(dst_scale) + static_cast<size_t>(slot) * words;
+    for (int i = threadIdx.x; i < words; i += kRowThreads) ds[i] = ss[i];
   }
 }
 
@@ -408,6 +438,19 @@ cudaError_t launch_gather_rows(const void* src, int n_src, int cols, const int32
     return launch_pdl(gather_rows_kernel<2>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
   else
     return launch_pdl(gather_rows_kernel<3>, grid, dim3(kRowThreads), 0, stream, s, n_src, cols, row_ids, num_post_pad, dst, scales, live_ids, sp);
+}
+
+cudaError_t launch_gather_quantised(const void* src, const void* src_scale, int n_src, int cols,
+                                    const int32_t* row_ids, const int32_t* num_post_pad, int64_t cap, int quant,
+                                    void* dst, void* dst_scale, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>(cap));
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  if (quant == 1)
+    return launch_pdl(gather_quantised_kernel<1>, grid, dim3(kRowThreads), 0, stream, s, src_scale, n_src, cols, row_ids, num_post_pad, d, dst_scale);
+  if (quant == 2)
+    return launch_pdl(gather_quantised_kernel<2>, grid, dim3(kRowThreads), 0, stream, s, src_scale, n_src, cols, row_ids, num_post_pad, d, dst_scale);
+  return launch_pdl(gather_quantised_kernel<3>, grid, dim3(kRowThreads), 0, stream, s, src_scale, n_src, cols, row_ids, num_post_pad, d, dst_scale);
 }
 
 bool decode_prologue_applies(int T, int K, int quant) {
