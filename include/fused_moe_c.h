@@ -217,8 +217,9 @@ FMOE_API int fmoe_run(const fmoe_traits_c* traits, const fmoe_args_c* args, void
  * performs no cudaMalloc / cudaFree and uses no allocating library routine.
  * The first call on each device looks up the array's device address; make that first
  * call outside any stream capture.  All calls on a device share the one array and it keeps
- * the previous call's contents (everything later stages read is rewritten by the call's
- * first kernel), so two calls that may overlap on the GPU -- different streams, or
+ * the previous call's contents (every index and count later stages act on is rewritten by the
+ * call's first kernel; stale activation rows of padding slots only feed results that are never
+ * stored), so two calls that may overlap on the GPU -- different streams, or
  * different threads -- race: serialise them on one stream.  Asynchronous on `stream`.
  * The status word of a bounded device wait is not readable through this variant; use
  * fmoe_run with fmoe_check_status where that is needed. */

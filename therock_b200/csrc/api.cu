@@ -446,8 +446,10 @@ int fmoe_run_static_ws(const fmoe_traits_c* traits, const fmoe_args_c* args, voi
   fmoe_args_c a = *args;
   a.workspace = ws;
   a.workspace_bytes = FMOE_STATIC_WS_BYTES;
-  // The sorting kernel rewrites every word later kernels read (pad slots, block ids, the
-  // status word), so nothing left over from the previous call needs clearing here.
+  // The first kernel rewrites every index, count and status word later kernels act on (sorted
+  // ids, block table, pad markers).  Activation rows of pad slots may hold what an earlier call
+  // left there: the GEMMs multiply them, but rows without a token are never stored, so nothing
+  // needs clearing here.
   return run_impl(traits, &a, stream, nullptr, nullptr);
 }
 
