@@ -182,7 +182,8 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
 template <bool kBf16Slots>
 __global__ void __launch_bounds__(kRowThreads)
 combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ topk_ids, int K, int E,
-               int H, void* __restrict__ out_v, const int32_t* __restrict__ num_tokens_dev) {
+               int H, void* __restrict__ out_v, const int32_t* __restrict__ num_tokens_dev, int k_splits,
+               int64_t split_stride) {
   ptx::pdl_wait();
   ptx::pdl_release();
   const int t = blockIdx.x;
@@ -220,7 +221,12 @@ combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ top
     for (int k = 0; k < K; ++k) {
       const int e = topk_ids[t * K + k];
       if (e < 0 || e >= E) continue;
-      const float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
+      // the K slices of a (token, k) row are added first, in slice order, then the rows in k order
+      float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
+      for (int sidx = 1; sidx < k_splits; ++sidx) {
+        const float4 u = slots[(static_cast<size_t>(t) * K + k) * nvec + i + static_cast<size_t>(sidx) * (split_stride >> 2)];
+        v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+      }
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
@@ -474,12 +480,13 @@ cudaError_t launch_decode_prologue(const int32_t* topk_ids, const float* topk_we
 }
 
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
-                           int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev) {
+                           int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev, int k_splits) {
+  const int64_t split_stride = static_cast<int64_t>(T) * K * H;     // f32 elements between K slices
   if (slots_bf16)
     return launch_pdl(combine_kernel<true>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
-                      num_tokens_dev);
+                      num_tokens_dev, 1, split_stride);
   return launch_pdl(combine_kernel<false>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
-                    num_tokens_dev);
+                    num_tokens_dev, k_splits, split_stride);
 }
 
 }  // namespace fmoe
