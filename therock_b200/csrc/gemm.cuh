@@ -170,6 +170,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
                                               uint32_t* stage, int64_t split_offset = 0) {
   const int lane = threadIdx.x & 31;
   const int row = p.sorted_rows[slot];               // flat (token, k) index, < 0 for a pad slot
+  // a warp whose 32 rows are all padding has nothing to store: it skips the tensor-memory reads too
+  if (__ballot_sync(0xffffffffu, row >= 0) == 0u) return;
   if (kEpi == kEpiSiluMul) {
     // pad slots carry no token: their rows of y are never used, so they are not stored
     __nv_bfloat16* ybase = reinterpret_cast<__nv_bfloat16*>(p.out) + n_blk * kSlabRows;

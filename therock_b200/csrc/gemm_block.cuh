@@ -321,6 +321,16 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (kHw) {
         if (!ptx::mbar_wait(ptx::smem_u32(&part_full_bar[buf]), buf_phase, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
+        // A warp whose 32 rows are all padding has nothing to store: it hands the accumulator
+        // back without reading it.  Its partner warp of the other column half sees the same rows
+        // and does the same, so the group-maximum exchange stays in step.
+        if (__ballot_sync(0xffffffffu, p.sorted_rows[slot] >= 0) == 0u) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&part_empty_bar[buf]));
+          if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1u; }
+          continue;
+        }
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(buf * kNT);
         if (kNT == kTileN) {
 #pragma unroll

@@ -188,12 +188,15 @@ combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ top
   ptx::pdl_release();
   const int t = blockIdx.x;
   if (num_tokens_dev && t >= *num_tokens_dev) return;   // rows past the device-side count
+  // grid.y spreads a row's vectors over several CTAs, so a thread has few dependent loads
+  const int i0 = blockIdx.y * kRowThreads + threadIdx.x;
+  const int istep = gridDim.y * kRowThreads;
   if (kBf16Slots) {
     // bf16 partial rows: 8 elements (16 bytes) per thread and term
     const int nvec = H >> 3;
     const uint4* slots = reinterpret_cast<const uint4*>(slots_v);
     uint4* out = reinterpret_cast<uint4*>(out_v);
-    for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+    for (int i = i0; i < nvec; i += istep) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int k = 0; k < K; ++k) {
         const int e = topk_ids[t * K + k];
@@ -216,16 +219,22 @@ combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ top
   const int nvec = H >> 2;
   const float4* slots = reinterpret_cast<const float4*>(slots_v);
   uint2* out = reinterpret_cast<uint2*>(out_v);
-  for (int i = threadIdx.x; i < nvec; i += kRowThreads) {
+  for (int i = i0; i < nvec; i += istep) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < K; ++k) {
       const int e = topk_ids[t * K + k];
       if (e < 0 || e >= E) continue;
       // the K slices of a (token, k) row are added first, in slice order, then the rows in k order
-      float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
-      for (int sidx = 1; sidx < k_splits; ++sidx) {
-        const float4 u = slots[(static_cast<size_t>(t) * K + k) * nvec + i + static_cast<size_t>(sidx) * (split_stride >> 2)];
-        v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+      const float4* base = slots + (static_cast<size_t>(t) * K + k) * nvec + i;
+      float4 v = base[0];
+      for (int s0 = 1; s0 < k_splits; s0 += 4) {           // four independent loads in flight, added in order
+        float4 u[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          u[j] = (s0 + j < k_splits) ? base[static_cast<size_t>(s0 + j) * (split_stride >> 2)] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (s0 + j < k_splits) { v.x += u[j].x; v.y += u[j].y; v.z += u[j].z; v.w += u[j].w; }
       }
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
@@ -482,10 +491,17 @@ cudaError_t launch_decode_prologue(const int32_t* topk_ids, const float* topk_we
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev, int k_splits) {
   const int64_t split_stride = static_cast<int64_t>(T) * K * H;     // f32 elements between K slices
+  // few tokens: spread each row over several CTAs so the whole GPU takes part
+  const int nvec = slots_bf16 ? H >> 3 : H >> 2;
+  int gy = 1;
+  if (T < 1024) {
+    gy = (nvec + kRowThreads - 1) / kRowThreads;
+    if (gy > 16) gy = 16;
+  }
   if (slots_bf16)
-    return launch_pdl(combine_kernel<true>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
+    return launch_pdl(combine_kernel<true>, dim3(T, gy), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
                       num_tokens_dev, 1, split_stride);
-  return launch_pdl(combine_kernel<false>, dim3(T), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
+  return launch_pdl(combine_kernel<false>, dim3(T, gy), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
                     num_tokens_dev, k_splits, split_stride);
 }
 
