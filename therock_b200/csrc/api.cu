@@ -300,12 +300,6 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   g.a_scale = y_scale; g.b_scale = fp8 ? a.w2_scale : nullptr;
   g.out = slots; g.ld_out = a.H;
   g.out_rows = static_cast<int64_t>(a.T) * a.K;
-  int k_splits = 1;
-  if (fmoe::decode_k_split_allowed(traits, args) && g.flavour == FMOE_KERNEL_SINGLE_DECODE) {
-    const long long hit = static_cast<long long>(a.T) * a.K < a.E ? static_cast<long long>(a.T) * a.K : a.E;
-    k_splits = fmoe::decode_k_splits(hit * g.n_blocks, (a.I * (fp8 ? 1 : 2) + 127) / 128, sms);
-  }
-  g.k_splits = k_splits;
   g.out_scale = nullptr;
   g.out_bf16 = traits->partial_dtype == FMOE_PARTIAL_BF16;
   g.row_ptrs = a.partial_row_ptrs;
@@ -322,8 +316,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
 
   if (!a.partial_row_ptrs) {    // scattered partial rows are added up by their owner
     NvtxRange r("combine");
-    FMOE_CUDA(fmoe::launch_combine(slots, g.out_bf16, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream, a.num_tokens_dev,
-                                   k_splits));
+    FMOE_CUDA(fmoe::launch_combine(slots, g.out_bf16, a.topk_ids, a.T, a.K, a.E, a.H, a.out, stream, a.num_tokens_dev));
   }
   FMOE_STAGE(6);
 #undef FMOE_STAGE

@@ -177,8 +177,6 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
   p.ld_out = g.ld_out;
   p.out_bf16 = g.out_bf16 ? 1 : 0;
   p.out_rows = g.out_rows;
-  p.k_splits = (few_rows && g.epilogue == kEpiScaledSlots && !g.out_bf16 && g.k_splits > 1) ? g.k_splits : 1;
-  p.split_stride = g.out_rows * static_cast<int64_t>(g.ld_out);
   p.row_ptrs = g.row_ptrs;
   p.done_addrs = g.done_addrs;
   p.done_value = g.done_value;
@@ -245,12 +243,9 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     return g.fp8 ? FMOE_DISPATCH_EPI(launch_pair_variant, true, pgrid) : FMOE_DISPATCH_EPI(launch_pair_variant, false, pgrid);
   }
 #define FMOE_COMMA_DECODE , kDecodeARows
-  if (few_rows) {
-    const long long units = max_tiles * p.k_splits;
-    const int ugrid = static_cast<int>(units < sm_count() ? (units > 0 ? units : 1) : sm_count());
-    return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, ugrid, FMOE_COMMA_DECODE)
-                 : FMOE_DISPATCH_EPI(launch_variant, false, ugrid, FMOE_COMMA_DECODE);
-  }
+  if (few_rows)
+    return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, grid, FMOE_COMMA_DECODE)
+                 : FMOE_DISPATCH_EPI(launch_variant, false, grid, FMOE_COMMA_DECODE);
   return g.fp8 ? FMOE_DISPATCH_EPI(launch_variant, true, grid) : FMOE_DISPATCH_EPI(launch_variant, false, grid);
 #undef FMOE_COMMA_DECODE
 #undef FMOE_DISPATCH_EPI

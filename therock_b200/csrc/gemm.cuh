@@ -59,9 +59,6 @@ struct GemmParams {
   int64_t out_rows;             // rows of `out` (bound for the checked build)
   const uint64_t* row_ptrs;     // kEpiScaledSlots with bf16 rows: destination address of each routed pair's row
                                 // (may be peer memory) instead of out + pair * ld_out; nullptr = contiguous
-  int k_splits;                 // kEpiScaledSlots, f32 rows, single-CTA kernel: the K loop of every tile is cut into
-                                // this many units (0 or 1 = none); unit s adds to out + s * split_stride
-  int64_t split_stride;         // elements between the partial outputs of consecutive K units
   const uint64_t* done_addrs;   // completion signal: the last CTA to finish writes *done_value to these
   const int* done_value;        // addresses (release, system scope); nullptr = none
   int* done_counter;
@@ -167,7 +164,7 @@ constexpr int kEpiStageBytes = 4 * kEpiStageBytesPerWarp;             // four ep
 template <int kEpi>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_row, int slot, int n_blk,
                                               const float* bs0, const float* bs1, float a_s,
-                                              uint32_t* stage, int64_t split_offset = 0) {
+                                              uint32_t* stage) {
   const int lane = threadIdx.x & 31;
   const int row = p.sorted_rows[slot];               // flat (token, k) index, < 0 for a pad slot
   // a warp whose 32 rows are all padding has nothing to store: it skips the tensor-memory reads too
@@ -271,7 +268,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ro
     }
   } else {
     const float w = p.sorted_weights[slot];
-    float* obase = reinterpret_cast<float*>(p.out) + split_offset + n_blk * kTileN;   // K unit's own partial rows
+    float* obase = reinterpret_cast<float*>(p.out) + n_blk * kTileN;
     uint32_t v[2][32];
     ptx::tmem_ld_32x32(t_row, v[0]);
 #pragma unroll
@@ -404,10 +401,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Work units: tiles, or (second GEMM of decode-sized batches) K slices of tiles, so that the
-  // units divide more evenly over the SMs than a hundred-odd whole tiles do.
-  const int splits = (kEpi == kEpiScaledSlots && p.k_splits > 1) ? p.k_splits : 1;
-  const int total_tiles = cum_s[p.num_experts] * p.n_blocks * splits;
+  const int total_tiles = cum_s[p.num_experts] * p.n_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -416,13 +410,11 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord tc = decode_tile(tile / splits, cum_s, p.num_experts, p.n_blocks);
-        const int ks = tile % splits;
-        const int k_begin = ks * p.k_iters / splits, k_end = (ks + 1) * p.k_iters / splits;
+        const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
         const int a_row = tc.m_blk * kBlockM;
         const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
         const int b_row1 = b_row0 + p.second_slab_offset;
-        for (int k = k_begin; k < k_end; ++k) {
+        for (int k = 0; k < p.k_iters; ++k) {
           if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -461,9 +453,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kTileN);
-        const int ks = tile % splits;
-        const int k_begin = ks * p.k_iters / splits, k_end = (ks + 1) * p.k_iters / splits;
-        for (int k = k_begin; k < k_end; ++k) {
+        for (int k = 0; k < p.k_iters; ++k) {
           if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
             ok = false;
             break;
@@ -476,7 +466,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           for (int kk = 0; kk < kStageKBytes / kUmmaKBytes; ++kk) {
             // advancing K inside the swizzle row = advancing the start address
             const uint64_t adv = static_cast<uint64_t>((kk * kUmmaKBytes) >> 4);
-            const uint32_t accum = (k > k_begin || kk) ? 1u : 0u;
+            const uint32_t accum = (k | kk) ? 1u : 0u;
             if (FMOE_DBG(p, 2u)) continue;
             if (kFp8) ptx::umma_f8(d_tmem, da + adv, db + adv, p.idesc, accum);
             else      ptx::umma_f16(d_tmem, da + adv, db + adv, p.idesc, accum);
@@ -498,7 +488,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const TileCoord tc = decode_tile(tile / splits, cum_s, p.num_experts, p.n_blocks);
+      const TileCoord tc = decode_tile(tile, cum_s, p.num_experts, p.n_blocks);
       const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
       // Per-output-channel scales of this tile's two slabs (same addresses for the whole
       // warp, so these are broadcast loads served by L1).
@@ -515,8 +505,7 @@ fmoe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                              static_cast<uint32_t>(acc * kTileN);
       if (!FMOE_DBG(p, 1u))
         epilogue_tile<kEpi>(p, t_row, slot, tc.n_blk, bs0, bs1, a_s,
-                            reinterpret_cast<uint32_t*>(misc + kSmemMisc) + quad * (kEpiStageBytesPerWarp / 4),
-                            static_cast<int64_t>(tile % splits) * p.split_stride);
+                            reinterpret_cast<uint32_t*>(misc + kSmemMisc) + quad * (kEpiStageBytesPerWarp / 4));
       ptx::tc_fence_before();
       ptx::mbar_arrive(ptx::smem_u32(&acc_empty_bar[acc]));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }

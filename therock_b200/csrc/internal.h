@@ -72,7 +72,7 @@ cudaError_t launch_decode_prologue(const int32_t* topk_ids, const float* topk_we
 // slots are f32, or bf16 when slots_bf16.
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
                            int H, void* out, cudaStream_t stream,
-                           const int32_t* num_tokens_dev = nullptr, int k_splits = 1);
+                           const int32_t* num_tokens_dev = nullptr);
 
 // out[t, :] = bf16( sum_k rows[index[t*K + k], :] ), f32 accumulation, index < 0 skipped;
 // rows are bf16 [*, H].
@@ -106,8 +106,6 @@ struct GemmLaunch {
   int done_count;
   void* out_scale;              // block flavours, first GEMM: when set, `out` receives e4m3 and this the
                                 // 1x128 scales of the intermediate (f32 [a_rows, ld_out/128] or UE8M0 bytes)
-  int k_splits;                 // > 1: cut every tile's K loop into this many work units (decode-sized second
-                                // GEMM, f32 rows); unit s writes to out + s * out_rows * ld_out
   int32_t* status;
   int max_m_blocks;             // upper bound on 128-row blocks (sizes the grid)
   bool b_tiled;                 // B is stored as contiguous 128-row x 128-byte tiles (see fmoe_weight_layout)

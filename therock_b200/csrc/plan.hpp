@@ -17,9 +17,7 @@ constexpr int kPlanSlabRows = 128;   // rows of one weight slab
 constexpr int kPlanTileN = 256;      // accumulator columns of one tile
 constexpr int kSortMultiCtaPairs = 8192;   // pairs from which moe_sorting spreads over several CTAs
 constexpr int kSortMaxCtasPlan = 64;
-constexpr bool kFusedBlockQuant = true;
-constexpr int kMaxKSplits = 16;            // K slices per tile of the decode-sized second GEMM (at most)
-   // 1x128 quantisation of the intermediate inside gemm1's epilogue
+constexpr bool kFusedBlockQuant = true;    // 1x128 quantisation of the intermediate inside gemm1's epilogue
 
 // Text of the last error on this thread (shared by every translation unit of the library).
 inline char* last_error_buf() {
@@ -114,27 +112,6 @@ inline bool quantise_once(const fmoe_traits_c* t, const fmoe_args_c* a) {
   return quant_is_fp8(t->quant) && a->K >= 2 && !fused_prologue(t, a) && a->H % 16 == 0;
 }
 
-// The second GEMM of a decode-sized batch (at most 32 routed rows, f32 partial rows kept in the
-// workspace) has a hundred-odd tiles for 148 SMs; cutting each tile's K loop into slices evens
-// the load out.  The slices' partial rows are added in slice order by the combine: deterministic.
-inline bool decode_k_split_allowed(const fmoe_traits_c* t, const fmoe_args_c* a) {
-  return static_cast<long long>(a->T) * a->K <= 32 && !quant_is_block(t->quant) &&
-         t->partial_dtype == FMOE_PARTIAL_F32 && a->partial_row_ptrs == nullptr && t->gemm_mode != 2;
-}
-// Number of K slices: the candidate with the fewest rounds of work per SM, smaller on ties.
-inline int decode_k_splits(long long tiles, int k_iters, int sms) {
-  int best = 1;
-  double best_cost = 1e30;
-  for (int s = 1; s <= kMaxKSplits; s *= 2) {
-    if (k_iters / s < 8) break;                      // keep slices long enough to fill the pipeline
-    const long long units = tiles * s;
-    const long long rounds = (units + sms - 1) / sms;
-    const double cost = static_cast<double>(rounds) / s + 0.004 * s;   // small charge per extra slice (epilogue, reduction)
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
-  }
-  return best;
-}
-
 inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
   const int64_t cap = sort_capacity(a->T, a->K, a->E, t->block_m);
   const bool fp8 = quant_is_fp8(t->quant);
@@ -161,9 +138,7 @@ inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
   if (!fp8) l.y_scale = take(0);
   else if (hw) l.y_scale = take(packed_scale_bytes(cap, a->I));
   else l.y_scale = take(static_cast<uint64_t>(cap) * 4 * (blk ? a->I / 128 : 1));
-  // decode-sized batches may cut the second GEMM's K loop into slices, each with its own f32 rows
-  const uint64_t slot_copies = decode_k_split_allowed(t, a) ? kMaxKSplits : 1;
-  l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * (t->partial_dtype == FMOE_PARTIAL_BF16 ? 2 : 4) * slot_copies);
+  l.slots = take(static_cast<uint64_t>(a->T) * a->K * a->H * (t->partial_dtype == FMOE_PARTIAL_BF16 ? 2 : 4));
   l.sort_scratch = take(static_cast<uint64_t>(2 * kSortMaxCtasPlan) * a->E * 4);
   // fp8 with several experts per token: the token rows are quantised once, then gathered as e4m3
   const bool once = quantise_once(t, a);

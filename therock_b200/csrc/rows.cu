@@ -182,8 +182,7 @@ gather_rows_kernel(const uint4* __restrict__ src, int n_src, int cols,
 template <bool kBf16Slots>
 __global__ void __launch_bounds__(kRowThreads)
 combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ topk_ids, int K, int E,
-               int H, void* __restrict__ out_v, const int32_t* __restrict__ num_tokens_dev, int k_splits,
-               int64_t split_stride) {
+               int H, void* __restrict__ out_v, const int32_t* __restrict__ num_tokens_dev) {
   ptx::pdl_wait();
   ptx::pdl_release();
   const int t = blockIdx.x;
@@ -224,18 +223,7 @@ combine_kernel(const void* __restrict__ slots_v, const int32_t* __restrict__ top
     for (int k = 0; k < K; ++k) {
       const int e = topk_ids[t * K + k];
       if (e < 0 || e >= E) continue;
-      // the K slices of a (token, k) row are added first, in slice order, then the rows in k order
-      const float4* base = slots + (static_cast<size_t>(t) * K + k) * nvec + i;
-      float4 v = base[0];
-      for (int s0 = 1; s0 < k_splits; s0 += 4) {           // four independent loads in flight, added in order
-        float4 u[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          u[j] = (s0 + j < k_splits) ? base[static_cast<size_t>(s0 + j) * (split_stride >> 2)] : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (s0 + j < k_splits) { v.x += u[j].x; v.y += u[j].y; v.z += u[j].z; v.w += u[j].w; }
-      }
+      const float4 v = slots[(static_cast<size_t>(t) * K + k) * nvec + i];
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
@@ -489,8 +477,7 @@ cudaError_t launch_decode_prologue(const int32_t* topk_ids, const float* topk_we
 }
 
 cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* topk_ids, int T, int K, int E,
-                           int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev, int k_splits) {
-  const int64_t split_stride = static_cast<int64_t>(T) * K * H;     // f32 elements between K slices
+                           int H, void* out, cudaStream_t stream, const int32_t* num_tokens_dev) {
   // few tokens: spread each row over several CTAs so the whole GPU takes part
   const int nvec = slots_bf16 ? H >> 3 : H >> 2;
   int gy = 1;
@@ -500,9 +487,9 @@ cudaError_t launch_combine(const void* slots, bool slots_bf16, const int32_t* to
   }
   if (slots_bf16)
     return launch_pdl(combine_kernel<true>, dim3(T, gy), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
-                      num_tokens_dev, 1, split_stride);
+                      num_tokens_dev);
   return launch_pdl(combine_kernel<false>, dim3(T, gy), dim3(kRowThreads), 0, stream, slots, topk_ids, K, E, H, out,
-                    num_tokens_dev, k_splits, split_stride);
+                    num_tokens_dev);
 }
 
 }  // namespace fmoe
