@@ -169,6 +169,20 @@ def test_hardware_scaled_down_gemm_with_224_column_tiles(T, H, I, E, K, partial)
     check(d, got, run_oracle(d, partial=partial))
 
 
+@pytest.mark.parametrize("quant", [0, 1, 3])
+def test_shared_expert_as_one_more_expert_every_token_selects(quant):
+    """A DeepSeek-style shared expert in the same call: expert E-1 holds its weights and
+    append_shared_expert gives every token one more (expert, weight 1) pair."""
+    T, H, I, E, K = 160, 512, 256, 9, 2
+    d = O.make_inputs(T, H, I, E, K, quant, "sigmoid", seed=77)
+    d["topk_ids"] = np.where(d["topk_ids"] == E - 1, (d["topk_ids"] + 1) % (E - 1), d["topk_ids"]).astype(np.int32)
+    ids, w = api.append_shared_expert(to_dev(d["topk_ids"]), to_dev(d["topk_w"]), E - 1)
+    d2 = dict(d, topk_ids=ids.cpu().numpy(), topk_w=w.cpu().numpy())
+    assert d2["topk_ids"].shape == (T, K + 1) and (d2["topk_ids"][:, K] == E - 1).all()
+    got, _ = run_gpu(d2)
+    check(d2, got, run_oracle(d2))
+
+
 def test_tiny_sigmoid_golden():
     cfg = dict(T=48, H=256, I=256, E=16, K=4, routing="sigmoid")
     g = np.load(os.path.join(GOLD, "tiny_sigmoid.npz"))

@@ -438,6 +438,20 @@ class HostPipeline:
         self.h2d.synchronize()
 
 
+def append_shared_expert(topk_ids: torch.Tensor, topk_weight: torch.Tensor, shared_expert_id: int,
+                         weight: float = 1.0):
+    """A shared expert (a dense FFN every token passes through, added to the routed experts'
+    output, as in DeepSeek-style layers) fused into the same operator call: store its weights as
+    expert `shared_expert_id` of W1 / W2 and give every token one more (expert, weight) pair.  The
+    shared expert's rows then run through the same grouped GEMMs as one large group and its
+    output is added in the same ordered combine (it is the last term of every token's sum).
+    Returns (topk_ids [T, K+1], topk_weight [T, K+1])."""
+    T = topk_ids.shape[0]
+    ids = torch.cat([topk_ids, torch.full((T, 1), shared_expert_id, dtype=topk_ids.dtype, device=topk_ids.device)], dim=1)
+    w = torch.cat([topk_weight, torch.full((T, 1), weight, dtype=topk_weight.dtype, device=topk_weight.device)], dim=1)
+    return ids.contiguous(), w.contiguous()
+
+
 def route(logits: torch.Tensor, topk: int, mode: str = "softmax", stream=None):
     """Router kernel: logits [T, E] f32 (CUDA) -> (topk_ids int32 [T, K], topk_weight f32 [T, K])."""
     if not (logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous()):
