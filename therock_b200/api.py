@@ -9,7 +9,10 @@ from typing import Optional
 
 import torch
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfmoe_b200.so")
+# FMOE_B200_LIBRARY selects another build of the library (the bounds-checked or the timing-switch
+# variant made by therock_b200.build); the default is the product library next to this file.
+LIB_PATH = os.environ.get("FMOE_B200_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                                                               "libfmoe_b200.so")
 
 QUANT = {"none": 0, "token_channel": 1, "block128": 2, "block128_ue8m0": 3}
 PARTIAL = {"f32": 0, "bf16": 1}
