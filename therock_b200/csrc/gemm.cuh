@@ -87,7 +87,7 @@ struct GemmParams {
 
 // Checked build (-DFMOE_BOUNDS_CHECKS): every computed output row is compared with its bound
 // before the store; a violation stores a code in the status word instead of writing.
-enum : int { kStatusBoundsGemm = 0x400, kStatusBoundsRows = 0x500 };
+enum : int { kStatusBoundsGemm = 0x400 };
 #ifdef FMOE_BOUNDS_CHECKS
 #define FMOE_ROW_OK(p, r) ((r) < (p).out_rows ? true : (atomicExch((p).status, kStatusBoundsGemm), false))
 #else
