@@ -275,3 +275,66 @@ def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
     # the context is healthy: a plain operator call still works
     from tests.util import run_gpu
     run_gpu(d)
+
+
+def _stress_worker(rank, world, port, quant, steps, ret):
+    """Many steps with fresh routing and activations every step, the fused step and the
+    single-purpose kernels side by side: both return bf16 partial rows and add them in k order,
+    so their outputs must agree bit for bit; a race between steps (a flag, a count or a row
+    arriving in the wrong epoch) would show up as a difference."""
+    import torch.distributed as dist
+    from therock_b200 import ep
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        T, H, I, E, K = 192 * world, 512, 256, 8, 2
+        d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=29)
+        e_local, t_local = E // world, T // world
+        lo = rank * e_local
+        if quant == 0:
+            w1, w2, s1, s2 = bf16_dev(d["w1"][lo:lo + e_local], dev), bf16_dev(d["w2"][lo:lo + e_local], dev), None, None
+        else:
+            w1, w2 = to_dev(d["w1"][lo:lo + e_local], device=dev), to_dev(d["w2"][lo:lo + e_local], device=dev)
+            s1, s2 = to_dev(d["w1_scale"][lo:lo + e_local], device=dev), to_dev(d["w2_scale"][lo:lo + e_local], device=dev)
+        mk = lambda fused: ep.PeerExpertParallelMoE(E, world, rank, traits_for(quant), w1, w2, s1, s2,
+                                                    tokens_per_rank=t_local, topk=K, hidden=H, fused=fused)
+        fused, plain = mk(True), mk(False)
+        g = torch.Generator(device=dev)
+        g.manual_seed(1000 + rank)
+        bad = 0
+        for step in range(steps):
+            x = torch.randn(t_local, H, generator=g, device=dev).to(torch.bfloat16)
+            logits = torch.randn(t_local, E, generator=g, device=dev)
+            if step % 5 == 4:
+                logits[:, : E // 2] += 4.0          # skewed routing: one half of the ranks gets almost everything
+            w, ids = torch.topk(torch.softmax(logits, -1), K, dim=-1)
+            ids = ids.to(torch.int32).contiguous()
+            if step % 7 == 3:
+                ids[::11, 0] = -1                   # dropped pairs
+            w = (w / w.sum(-1, keepdim=True)).float().contiguous()
+            a = fused.forward(x, ids, w).clone()
+            b = plain.forward(x, ids, w).clone()
+            bad += int((a.view(torch.int16) != b.view(torch.int16)).sum().item())
+        ok = bad == 0 and fused.check_status() == 0 and plain.check_status() == 0
+        ret[rank] = bool(ok) if ok else f"{bad} differing elements, status {fused.check_status()} / {plain.check_status()}"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("quant", [0, 1])
+def test_fused_and_single_purpose_steps_agree_bit_for_bit_over_many_random_steps(quant):
+    world = 2 if torch.cuda.device_count() >= 2 else 1
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_stress_worker, args=(r, world, port, quant, 60, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert p.exitcode == 0
+    assert all(ret.get(r) is True for r in range(world)), dict(ret)
