@@ -688,7 +688,7 @@ def measure_ep(env, a, c, sampler):
     ids_h = d["ids"].cpu().pin_memory()
     w_h = d["w"].cpu().pin_memory()
     out_h = torch.empty(T_local, H, dtype=torch.bfloat16).pin_memory()
-    if ep_transport == "peer_memory":
+    if ep_transport == "peer_memory" and a.e2e_pipeline == "graph":
         # the whole expert-parallel step has no host synchronisation inside, so it is captured,
         # with the copies of the neighbouring batches, in one graph per pipeline slot
         ep_out = [torch.empty_like(d["x"]) for _ in range(2)]
@@ -697,6 +697,23 @@ def measure_ep(env, a, c, sampler):
             return moe.forward(x, ids, w, out=ep_out[slot])
         pipe = api.GraphPipeline(pipe_step, x_h, ids_h, w_h, out_h, dev)
         submit, finish = pipe.submit, pipe.flush
+    elif ep_transport == "peer_memory":
+        # three streams driven from the host; the step itself is one captured graph per slot
+        ep_out = [torch.empty_like(d["x"]) for _ in range(2)]
+        ep_graphs = [None, None]
+
+        def pipe_step(x, ids, w, slot):
+            if ep_graphs[slot] is None:
+                moe.forward(x, ids, w, out=ep_out[slot])          # warm-up outside capture
+                torch.cuda.current_stream().synchronize()
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_, stream=torch.cuda.current_stream()):
+                    moe.forward(x, ids, w, out=ep_out[slot])
+                ep_graphs[slot] = g_
+            ep_graphs[slot].replay()
+            return ep_out[slot]
+        pipe = api.HostPipeline(pipe_step, T_local, H, c["K"], dev, depth=2)
+        submit, finish = (lambda: pipe.submit(x_h, ids_h, w_h, out_h)), pipe.drain
     else:
         def pipe_step(x, ids, w, slot):
             return moe.forward(x, ids, w)
@@ -813,6 +830,9 @@ def main():
                     help="N > 1, peer memory: the fused step (send / recv_ready / wait_combine) or the single-purpose kernels")
     ap.add_argument("--gemm-mode", type=int, choices=[0, 1, 2], default=0,
                     help="0 = the library's per-GEMM choice, 1 = single-CTA kernel, 2 = CTA-pair kernel (profiling)")
+    ap.add_argument("--e2e-pipeline", choices=["graph", "streams"], default="graph",
+                    help="N > 1 end-to-end loop: one CUDA graph per step that also holds the copies, or three "
+                         "streams driven from the host around a graph of the step")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-resident timed loop: no stage profile, e2e or CPU baseline")
     a = ap.parse_args()

@@ -320,7 +320,9 @@ FMOE_API int fmoe_ep_return(const void* out_rows, int32_t H, const int32_t* n_re
  * rank's received-row count to n_recv_dev and finally tells every rank that its rows are complete.
  * The kernel's CTAs meet at a barrier of their own: it must run with the GPU otherwise idle (it is
  * launched without programmatic overlap, after everything earlier on the stream).
- * scratch: int32[fmoe_ep_send_scratch_words(T, K, G)], zero-initialised once. */
+ * scratch: int32[fmoe_ep_send_scratch_words(T, K, G)], zero-initialised once; the same array is
+ * passed to all three kernels of the step (it also holds the words through which the CTAs of a
+ * kernel share the outcome of a wait, so that only two of them poll memory the peers write). */
 FMOE_API int64_t fmoe_ep_send_scratch_words(int32_t T, int32_t K, int32_t G);
 FMOE_API int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
                           int32_t H, int32_t experts_per_rank, const uint64_t* peer_base,
@@ -332,14 +334,15 @@ FMOE_API int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* t
  * partial_row_ptrs of the local fmoe_run. */
 FMOE_API int fmoe_ep_recv_ready(int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base,
                                 const fmoe_ep_layout_c* lay, int32_t me, int32_t G, const int32_t* epoch_dev,
-                                uint64_t* row_ptrs, int32_t* status, int32_t timeout_ms, void* stream);
+                                uint64_t* row_ptrs, int32_t* scratch, int32_t* status, int32_t timeout_ms,
+                                void* stream);
 /* Waits until every rank has returned this rank's rows (the done_flag_* signal of their local
  * fmoe_run, aimed at flags_return) and adds them up: out[t] = bf16(sum over k ascending of
  * back[t*K + k]) in f32, pairs with an expert id outside [0, num_experts) skipped.  Advances the
- * epoch.  sync_counter: one zero-initialised device int32. */
+ * epoch.  scratch: the step's scratch array (see fmoe_ep_send). */
 FMOE_API int fmoe_ep_wait_combine(const int32_t* topk_ids, int32_t T, int32_t K, int32_t H, int32_t num_experts,
                                   const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
-                                  int32_t* epoch_dev, int32_t* sync_counter, void* out, int32_t* status,
+                                  int32_t* epoch_dev, int32_t* scratch, void* out, int32_t* status,
                                   int32_t timeout_ms, void* stream);
 
 /* What one fmoe_run with these traits and dimensions will launch on the current device: the

@@ -116,7 +116,7 @@ def lib() -> ctypes.CDLL:
         l.fmoe_ep_send_scratch_words.argtypes = [i32, i32, i32]
         l.fmoe_ep_send.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp,
                                    vp, vp, i32, vp]
-        l.fmoe_ep_recv_ready.argtypes = [i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp, i32, vp]
+        l.fmoe_ep_recv_ready.argtypes = [i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp, vp, i32, vp]
         l.fmoe_ep_wait_combine.argtypes = [vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp,
                                            vp, i32, vp]
         _lib = l

@@ -131,17 +131,48 @@ __device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
 __device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Thread p < G waits until flags[p] >= epoch; gives up after limit cycles and reports the rank.
-__device__ __forceinline__ void wait_flags(const int32_t* flags, int G, int epoch, long long limit, int32_t* status) {
-  const int p = threadIdx.x;
-  if (p < G) {
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int32_t* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// All CTAs of a kernel wait until flags[p] >= epoch for every rank p.  Only the first two CTAs
+// poll the flags the peers write (system scope); the one that sees them complete publishes the
+// epoch in a local word the other CTAs poll at device scope with a growing back-off, so a
+// thousand waiting CTAs do not hammer one line of memory with system-scope loads while copies
+// and peer stores are in flight.  Gives up after `limit` cycles and reports the missing rank.
+// Layout of the step's scratch words (int32): [0] grid barrier of the send kernel, [1] its
+// finished CTAs, [2] / [3] / [4] the local "complete" words of the three waits, [5] finished CTAs
+// of wait_combine, [8 ...] per-CTA counts of the send kernel.
+__device__ __forceinline__ void wait_flags(const int32_t* flags, int32_t* ready, int G, int epoch, long long limit,
+                                           int32_t* status) {
+  if (threadIdx.x == 0) {
     const long long t0 = clock64();
-    while (ld_acquire_sys(flags + p) < epoch) {
-      if (clock64() - t0 > limit) {
-        atomicExch(status, 0x300 | p);
+    unsigned backoff = 32;
+    for (;;) {
+      if (ld_acquire_gpu(ready) >= epoch) break;
+      if (blockIdx.x < 2) {
+        int missing = -1;
+        for (int p = 0; p < G; ++p)
+          if (ld_acquire_sys(flags + p) < epoch) { missing = p; break; }
+        if (missing < 0) {
+          st_release_gpu(ready, epoch);
+          break;
+        }
+        if (clock64() - t0 > limit) {
+          atomicExch(status, 0x300 | missing);
+          st_release_gpu(ready, epoch);          // let the other CTAs go on too: the step is lost anyway
+          break;
+        }
+      } else if (clock64() - t0 > 2 * limit) {   // the polling CTAs never reported: do not wait for ever
+        atomicExch(status, 0x330);
         break;
       }
-      __nanosleep(64);
+      __nanosleep(backoff);
+      if (backoff < 1024) backoff <<= 1;
     }
   }
   __syncthreads();
@@ -237,7 +268,7 @@ ep_send_kernel(const EpSendParams p) {
     if (tid < G) st_release_sys(peer_ptr<int32_t>(p.peer_base, tid, p.lay.flags) + p.me, epoch);
   }
   // 4. everybody's counts
-  wait_flags(peer_ptr<int32_t>(p.peer_base, p.me, p.lay.flags), G, epoch, p.limit, p.status);
+  wait_flags(peer_ptr<int32_t>(p.peer_base, p.me, p.lay.flags), p.sync + 2, G, epoch, p.limit, p.status);
   const int32_t* matrix = peer_ptr<int32_t>(p.peer_base, p.me, p.lay.matrix);
   if (tid < G) {
     int base = 0;
@@ -295,8 +326,9 @@ ep_send_kernel(const EpSendParams p) {
 __global__ void __launch_bounds__(256)
 ep_recv_ready_kernel(int H, const int32_t* __restrict__ n_recv_dev, const uint64_t* __restrict__ peer_base,
                      fmoe_ep_layout_c lay, int me, int G, const int32_t* __restrict__ epoch,
-                     uint64_t* __restrict__ row_ptrs, int32_t* __restrict__ status, long long limit) {
-  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_dispatch), G, *epoch, limit, status);
+                     uint64_t* __restrict__ row_ptrs, int32_t* __restrict__ scratch, int32_t* __restrict__ status,
+                     long long limit) {
+  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_dispatch), scratch + 3, G, *epoch, limit, status);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= *n_recv_dev || i >= lay.recv_cap) return;
   const int2 s = __ldcg(peer_ptr<int2>(peer_base, me, lay.src) + i);
@@ -310,9 +342,10 @@ ep_recv_ready_kernel(int H, const int32_t* __restrict__ n_recv_dev, const uint64
 __global__ void __launch_bounds__(128)
 ep_wait_combine_kernel(const int32_t* __restrict__ topk_ids, int K, int H, int E,
                        const uint64_t* __restrict__ peer_base, fmoe_ep_layout_c lay, int me, int G,
-                       int32_t* __restrict__ epoch, int32_t* __restrict__ sync_counter, uint4* __restrict__ out,
+                       int32_t* __restrict__ epoch, int32_t* __restrict__ scratch, uint4* __restrict__ out,
                        int32_t* __restrict__ status, long long limit) {
-  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_return), G, *epoch, limit, status);
+  int32_t* sync_counter = scratch + 5;
+  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_return), scratch + 4, G, *epoch, limit, status);
   const int t = blockIdx.x;
   const int nvec = H >> 3;
   const uint4* back = peer_ptr<uint4>(peer_base, me, lay.back);
@@ -434,7 +467,7 @@ static int ep_send_grid(int32_t T, int32_t K) {
 
 int64_t fmoe_ep_send_scratch_words(int32_t T, int32_t K, int32_t G) {
   (void)T; (void)K;
-  return 4 + 256LL * (G > 0 ? G : 1);      // two counters + per-CTA counts for up to 256 CTAs
+  return 8 + 256LL * (G > 0 ? G : 1);      // counters and wait words + per-CTA counts for up to 256 CTAs
 }
 
 int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K, int32_t H,
@@ -456,7 +489,7 @@ int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weigh
   p.topk_ids = topk_ids; p.topk_w = topk_weight;
   p.T = T; p.K = K; p.H = H; p.e_local = experts_per_rank;
   p.peer_base = peer_base; p.lay = *lay; p.me = me; p.G = G;
-  p.sync = scratch; p.cta_counts = scratch + 4;
+  p.sync = scratch; p.cta_counts = scratch + 8;
   p.epoch = epoch_dev; p.n_recv_dev = n_recv_dev; p.status = status;
   p.limit = wait_limit_cycles(timeout_ms);
   fmoe::ep_send_kernel<<<grid, fmoe::kSendThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
@@ -464,30 +497,30 @@ int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weigh
 }
 
 int fmoe_ep_recv_ready(int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,
-                       int32_t me, int32_t G, const int32_t* epoch_dev, uint64_t* row_ptrs, int32_t* status,
-                       int32_t timeout_ms, void* stream) {
-  if (!n_recv_dev || !peer_base || !lay || !epoch_dev || !row_ptrs || !status)
+                       int32_t me, int32_t G, const int32_t* epoch_dev, uint64_t* row_ptrs, int32_t* scratch,
+                       int32_t* status, int32_t timeout_ms, void* stream) {
+  if (!n_recv_dev || !peer_base || !lay || !epoch_dev || !row_ptrs || !scratch || !status)
     return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_recv_ready: a required pointer is null");
   if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G || H <= 0 || timeout_ms < 0)
     return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_recv_ready: bad arguments (rank %d, world %d, H %d)", me, G, H);
   if (lay->recv_cap <= 0) return FMOE_OK;
   const unsigned grid = static_cast<unsigned>((lay->recv_cap + 255) / 256);
   fmoe::ep_recv_ready_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      H, n_recv_dev, peer_base, *lay, me, G, epoch_dev, row_ptrs, status, wait_limit_cycles(timeout_ms));
+      H, n_recv_dev, peer_base, *lay, me, G, epoch_dev, row_ptrs, scratch, status, wait_limit_cycles(timeout_ms));
   return fmoe::launch_status("fmoe_ep_recv_ready");
 }
 
 int fmoe_ep_wait_combine(const int32_t* topk_ids, int32_t T, int32_t K, int32_t H, int32_t num_experts,
                          const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me, int32_t G,
-                         int32_t* epoch_dev, int32_t* sync_counter, void* out, int32_t* status, int32_t timeout_ms,
+                         int32_t* epoch_dev, int32_t* scratch, void* out, int32_t* status, int32_t timeout_ms,
                          void* stream) {
-  if (!topk_ids || !peer_base || !lay || !epoch_dev || !sync_counter || !out || !status)
+  if (!topk_ids || !peer_base || !lay || !epoch_dev || !scratch || !out || !status)
     return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_wait_combine: a required pointer is null");
   if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G || T <= 0 || K <= 0 || H <= 0 || H % 8 || timeout_ms < 0)
     return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_wait_combine: bad arguments (rank %d, world %d, T %d, K %d, H %d)", me,
                       G, T, K, H);
   fmoe::ep_wait_combine_kernel<<<T, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      topk_ids, K, H, num_experts, peer_base, *lay, me, G, epoch_dev, sync_counter, reinterpret_cast<uint4*>(out),
+      topk_ids, K, H, num_experts, peer_base, *lay, me, G, epoch_dev, scratch, reinterpret_cast<uint4*>(out),
       status, wait_limit_cycles(timeout_ms));
   return fmoe::launch_status("fmoe_ep_wait_combine");
 }

@@ -346,7 +346,6 @@ class PeerExpertParallelMoE:
             self.send_scratch = torch.zeros(int(api.lib().fmoe_ep_send_scratch_words(tokens_per_rank, topk, world)),
                                             dtype=torch.int32, device=dev)
             self.row_ptrs = torch.zeros(recv_cap, dtype=torch.int64, device=dev)
-            self.sync_counter = torch.zeros(1, dtype=torch.int32, device=dev)
             self.args.partial_row_ptrs = self.row_ptrs
             self.args.done_flag_addrs = (self.peer_base + (lay.flags_return + 4 * rank)).contiguous()
             self.args.done_flag_value = self.epoch_dev
@@ -381,13 +380,14 @@ class PeerExpertParallelMoE:
                                     self.barrier_timeout_ms, st))
         self._mark("send")
         api._check(lib.fmoe_ep_recv_ready(H, self.n_recv.data_ptr(), pb, by(self.lay), self.rank, G,
-                                          self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(), self.status.data_ptr(),
+                                          self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(),
+                                          self.send_scratch.data_ptr(), self.status.data_ptr(),
                                           self.barrier_timeout_ms, st))
         self._mark("recv_ready")
         api.fused_moe(self.traits, self.args)
         self._mark("local_moe")
         api._check(lib.fmoe_ep_wait_combine(topk_ids.data_ptr(), T, K, H, self.E, pb, by(self.lay), self.rank, G,
-                                            self.epoch_dev.data_ptr(), self.sync_counter.data_ptr(), out.data_ptr(),
+                                            self.epoch_dev.data_ptr(), self.send_scratch.data_ptr(), out.data_ptr(),
                                             self.status.data_ptr(), self.barrier_timeout_ms, st))
         self._mark("wait_combine")
         return out
