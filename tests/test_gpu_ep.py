@@ -266,6 +266,8 @@ def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
     assert rc == 0 and int(status.item()) == (0x300 | 1)
     status.zero_()
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    # this rank's own operator would have signalled its returns; rank 1 never does
+    mine[lay.flags_return:lay.flags_return + 4].view(torch.int32)[0] = 1
     rc = lib.fmoe_ep_wait_combine(ids.data_ptr(), T, K, H, 2 * e_local, peer_base.data_ptr(), by(lay), 0, 2,
                                   epoch.data_ptr(), scratch.data_ptr(), out.data_ptr(), status.data_ptr(), 50, st)
     torch.cuda.synchronize()
