@@ -131,6 +131,10 @@ __device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
 __device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// After one system-scope fence: fence + relaxed store is a release, without a fence per flag.
+__device__ __forceinline__ void st_relaxed_sys(int32_t* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -263,8 +267,7 @@ ep_send_kernel(const EpSendParams p) {
       const int peer = i / G, d = i % G;
       peer_ptr<int32_t>(p.peer_base, peer, p.lay.matrix)[p.me * G + d] = total[d];
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();          // the release store below orders the CTA's count stores before the flag
     if (tid < G) st_release_sys(peer_ptr<int32_t>(p.peer_base, tid, p.lay.flags) + p.me, epoch);
   }
   // 4. everybody's counts
@@ -308,17 +311,18 @@ ep_send_kernel(const EpSendParams p) {
     peer_ptr<float>(p.peer_base, d, p.lay.weights)[dst] = p.topk_w[r];
     peer_ptr<int2>(p.peer_base, d, p.lay.src)[dst] = make_int2(p.me, r);
   }
-  // 7. the last CTA to finish tells every rank that this rank's rows are complete
-  __threadfence_system();
+  // 7. the last CTA to finish tells every rank that this rank's rows are complete (one
+  //    system-scope fence for the whole grid: the last CTA's, after it has seen every count)
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     const int prev = atomicAdd(&p.sync[1], 1);
     if (prev == C - 1) {
       p.sync[0] = 0;
       p.sync[1] = 0;
       __threadfence_system();
       for (int peer = 0; peer < G; ++peer)
-        st_release_sys(peer_ptr<int32_t>(p.peer_base, peer, p.lay.flags_dispatch) + p.me, epoch);
+        st_relaxed_sys(peer_ptr<int32_t>(p.peer_base, peer, p.lay.flags_dispatch) + p.me, epoch);
     }
   }
 }

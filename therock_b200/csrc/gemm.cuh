@@ -123,13 +123,15 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, const int* cum, int E
 // rows without a further launch.
 __device__ __forceinline__ void grid_done_signal(const GemmParams& p) {
   if (p.done_addrs == nullptr || threadIdx.x != 0) return;
-  __threadfence_system();                         // this CTA's stores (seen through the barrier) first
+  // This CTA's stores (seen through the barrier) are ordered before its count at device scope;
+  // the one system-scope fence of the grid is the last CTA's, which has observed every count.
+  __threadfence();
   const int prev = atomicAdd(p.done_counter, 1);
   if (prev != static_cast<int>(gridDim.x) - 1) return;
   __threadfence_system();
   const int v = *p.done_value;
   for (int i = 0; i < p.done_count; ++i)
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.done_addrs[i]), "r"(v) : "memory");
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.done_addrs[i]), "r"(v) : "memory");
   *p.done_counter = 0;                            // ready for the next launch
 }
 
