@@ -72,7 +72,9 @@ enum fmoe_gemm_kernel {
   FMOE_KERNEL_PAIR = 2,          /* fmoe_grouped_gemm_pair_kernel: CTA pair, cta_group::2, 256 x 256 tile */
   FMOE_KERNEL_BLOCK_PROMOTE = 3, /* fmoe_grouped_gemm_block_kernel<.., false>: per-128 partials promoted in registers */
   FMOE_KERNEL_BLOCK_HW_SCALE = 4,/* fmoe_grouped_gemm_block_kernel<.., true>: block_scale MMA, UE8M0 scales */
-  FMOE_KERNEL_SINGLE_DECODE = 5  /* fmoe_grouped_gemm_kernel staging 32 activation rows (at most 32 routed rows) */
+  FMOE_KERNEL_SINGLE_DECODE = 5, /* fmoe_grouped_gemm_kernel staging 32 activation rows (at most 32 routed rows) */
+  FMOE_KERNEL_BLOCK_HW_TOKENS_N = 6 /* fmoe_grouped_gemm_tokn_kernel: block_scale MMA with the weights on M and
+                                       the tokens on N in steps of 16, so padding rows are not multiplied */
 };
 
 enum fmoe_activation { FMOE_ACT_SILU = 0 };
@@ -93,7 +95,9 @@ typedef struct fmoe_traits_c {
                            1: W1 is [E,I,H] and y = SiLU(gate) (I a multiple of 256; not with block128) */
   int32_t block_m;      /* rows per sorted block; 128 */
   int32_t gemm_mode;    /* 0 = chosen per GEMM from the expected tile counts, 1 = single-CTA
-                           kernel, 2 = CTA-pair kernel (cta_group::2) */
+                           kernel, 2 = CTA-pair kernel (cta_group::2); with block128_ue8m0:
+                           0 and 1 = tokens on M (128-row blocks), 2 = tokens on N (steps of 16;
+                           measured slower on the shapes benchmarked, kept selectable) */
   int32_t weight_layout; /* fmoe_weight_layout of w1 and w2 */
   int32_t partial_dtype; /* fmoe_partial_dtype */
 } fmoe_traits_c;

@@ -86,9 +86,15 @@ int main() {
         fmoe_run_info_c info;
         std::memset(&info, 0, sizeof(info));
         EXPECT(describe_run(&tq, &aq, 148, 0, &info) == FMOE_OK);
-        EXPECT(info.gemm1_kernel >= FMOE_KERNEL_SINGLE && info.gemm1_kernel <= FMOE_KERNEL_SINGLE_DECODE);
+        EXPECT(info.gemm1_kernel >= FMOE_KERNEL_SINGLE && info.gemm1_kernel <= FMOE_KERNEL_BLOCK_HW_TOKENS_N);
         EXPECT(info.launches >= 4 && info.launches <= 9);   // decode prologue (one launch for sort + gather) up to multi-CTA sort + quantise-once + quantised intermediate
-        if (q == FMOE_QUANT_BLOCK128_UE8M0) EXPECT(info.gemm1_kernel == FMOE_KERNEL_BLOCK_HW_SCALE);
+        if (q == FMOE_QUANT_BLOCK128_UE8M0) {
+          EXPECT(info.gemm1_kernel == FMOE_KERNEL_BLOCK_HW_SCALE);
+          fmoe_run_info_c forced;
+          std::memset(&forced, 0, sizeof(forced));
+          EXPECT(describe_run(&tq, &aq, 148, 1, &forced) == FMOE_OK && forced.gemm1_kernel == FMOE_KERNEL_BLOCK_HW_SCALE);
+          EXPECT(describe_run(&tq, &aq, 148, 2, &forced) == FMOE_OK && forced.gemm2_kernel == FMOE_KERNEL_BLOCK_HW_TOKENS_N);
+        }
       }
     }
   }

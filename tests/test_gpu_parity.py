@@ -165,8 +165,36 @@ def test_hardware_scaled_down_gemm_with_224_column_tiles(T, H, I, E, K, partial)
     with two 224-column accumulators in tensor memory; the tile's 32-row scale groups then cut
     across the 128-row weight-scale blocks."""
     d = O.make_inputs(T, H, I, E, K, 3, "softmax", seed=H + T)
-    got, _ = run_gpu(d, partial)
+    got, _ = run_gpu(d, partial, gemm_mode=1)      # tokens on M: the kernel with the 224-column tiles
     check(d, got, run_oracle(d, partial=partial))
+
+
+TOKENS_ON_N_CASES = [
+    (300, 512, 384, 6, 2, "spread"),      # ~100 rows per expert: one chunk each
+    (1500, 512, 256, 4, 2, "spread"),     # ~750 rows per expert: four chunks of unequal size
+    (40, 256, 128, 16, 1, "spread"),      # most experts hold 0..5 rows, some none
+    (700, 1792, 256, 3, 1, "spread"),     # ~233 rows per expert: around the 224-token chunk limit
+    (1024, 256, 256, 8, 1, "one"),        # every row on one expert: five chunks, seven experts empty
+    (449, 256, 128, 2, 1, "one"),         # 449 rows: three chunks of 160 + 144 + 160 after rounding to 464
+]
+
+
+@pytest.mark.parametrize("partial", ["f32", "bf16"])
+@pytest.mark.parametrize("T,H,I,E,K,routing", TOKENS_ON_N_CASES)
+def test_ue8m0_tokens_on_n_kernel_matches_oracle_and_tokens_on_m(T, H, I, E, K, routing, partial):
+    """The UE8M0 mode has two GEMM kernels: tokens as 128-row blocks on M, or weights on M and an
+    expert's live tokens, in steps of 16, on N.  Both are checked against the oracle on ragged
+    expert loads and against each other (same products, same K order: the results agree to well
+    inside one bf16 rounding of the output)."""
+    d = O.make_inputs(T, H, I, E, K, 3, "softmax", seed=3 * T + E)
+    if routing == "one":
+        d["topk_ids"][:] = E - 1
+    ref = run_oracle(d, partial=partial)
+    on_n, _ = run_gpu(d, partial, gemm_mode=2)
+    check(d, on_n, ref)
+    on_m, _ = run_gpu(d, partial, gemm_mode=1)
+    check(d, on_m, ref)
+    assert rel_l2(on_n, on_m) <= 2e-3
 
 
 @pytest.mark.parametrize("quant", [0, 1, 3])
@@ -476,8 +504,6 @@ def test_tiled_weight_layout_gives_identical_results(quant, gemm_mode):
     from therock_b200 import weights as W
     d = O.make_inputs(300, 512, 384, 6, 2, quant, "softmax", seed=51)
     base = args_for(d)
-    if quant == 3 and gemm_mode == 2:
-        pytest.skip("the block-scaled modes have one kernel flavour")
     tr = traits_for(quant)
     tr.gemm_mode = gemm_mode
     ref = out_bits(M.fused_moe(tr, base)).copy()

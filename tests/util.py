@@ -19,8 +19,9 @@ def bf16_dev(bits, device="cuda:0"):
     return to_dev(bits.view(np.int16), torch.bfloat16, device)
 
 
-def traits_for(quant, partial="f32"):
-    return M.FusedMoeTraits(prec_w="bf16" if quant == 0 else "fp8", quant=QUANT_NAME[quant], partial_dtype=partial)
+def traits_for(quant, partial="f32", gemm_mode=0):
+    return M.FusedMoeTraits(prec_w="bf16" if quant == 0 else "fp8", quant=QUANT_NAME[quant], partial_dtype=partial,
+                            gemm_mode=gemm_mode)
 
 
 def args_for(d, device="cuda:0"):
@@ -41,13 +42,13 @@ def out_bits(t):
 CANARY = 0xA5
 
 
-def run_gpu(d, partial="f32"):
+def run_gpu(d, partial="f32", gemm_mode=0):
     """One fused_moe call through the C-ABI.  The output and the workspace are allocated with
     64 KiB of canary bytes on either side; the bytes are checked after the run, so a kernel that
     writes outside the buffers it was given fails the test even if the results look right."""
     from therock_b200 import api
     args = args_for(d)
-    traits = traits_for(d["quant"], partial)
+    traits = traits_for(d["quant"], partial, gemm_mode)
     pad = 65536
     T, H = args.a.shape
     need = M.fused_moe_workspace_size(traits, args)

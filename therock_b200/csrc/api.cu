@@ -142,6 +142,7 @@ const char* fmoe_gemm_kernel_name(int32_t kernel) {
     case FMOE_KERNEL_BLOCK_PROMOTE: return "fmoe_grouped_gemm_block_kernel<promote>";
     case FMOE_KERNEL_BLOCK_HW_SCALE: return "fmoe_grouped_gemm_block_kernel<block_scale MMA>";
     case FMOE_KERNEL_SINGLE_DECODE: return "fmoe_grouped_gemm_kernel<32 activation rows>";
+    case FMOE_KERNEL_BLOCK_HW_TOKENS_N: return "fmoe_grouped_gemm_tokn_kernel";
     default: return "";
   }
 }

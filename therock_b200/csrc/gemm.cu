@@ -6,7 +6,7 @@
 #include <mutex>
 
 #include "../../include/fused_moe_c.h"
-#include "gemm_block.cuh"
+#include "gemm_tokn.cuh"
 #include "internal.h"
 
 namespace fmoe {
@@ -141,9 +141,25 @@ cudaError_t launch_block_variant(const CUtensorMap& ta, const CUtensorMap& tb, c
                     kBlockSmemBytes, stream, ta, tb, bp);
 }
 
+template <int kEpi>
+cudaError_t launch_tokn_variant(const CUtensorMap& tw, const CUtensorMap (&tt)[4], const BlockGemmParams& bp, int grid,
+                                cudaStream_t stream) {
+  static bool configured[kMaxDevices] = {false};
+  const int dev = current_device();
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fmoe_grouped_gemm_tokn_kernel<kEpi>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kToknSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  return launch_pdl(fmoe_grouped_gemm_tokn_kernel<kEpi>, dim3(grid), dim3(kToknThreads), kToknSmemBytes, stream, tw,
+                    tt[0], tt[1], tt[2], tt[3], bp);
+}
+
 cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* drv_err) {
   CUtensorMap ta, tb;
-  const bool block = g.flavour == FMOE_KERNEL_BLOCK_PROMOTE || g.flavour == FMOE_KERNEL_BLOCK_HW_SCALE;
+  const bool tokn = g.flavour == FMOE_KERNEL_BLOCK_HW_TOKENS_N;
+  const bool block = g.flavour == FMOE_KERNEL_BLOCK_PROMOTE || g.flavour == FMOE_KERNEL_BLOCK_HW_SCALE || tokn;
   const bool pair = g.flavour == FMOE_KERNEL_PAIR;
   // decode-sized batches: only the first kDecodeARows rows of a block can be real
   const bool few_rows = g.flavour == FMOE_KERNEL_SINGLE_DECODE;
@@ -203,7 +219,29 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     bp.a_scale = g.a_scale;
     bp.b_scale = g.b_scale;
     bp.k_blocks = p.k_iters;
+    bp.a_rows = g.a_rows;
     bp.out_scale = g.out_scale;
+    if (tokn) {
+      if (g.epilogue == kEpiSilu) return cudaErrorInvalidValue;
+      if (g.epilogue == kEpiSiluMul && g.out_scale == nullptr) return cudaErrorInvalidValue;
+      // token boxes of 128, 64, 32 and 16 rows: every chunk (a multiple of 16 rows) is at most three loads
+      CUtensorMap tt[4];
+      const int box_rows[4] = {128, 64, 32, 16};
+      for (int i = 0; i < 4; ++i) {
+        CUresult r2 = make_map(&tt[i], g.a, true, g.a_rows, g.k_elems, box_rows[i]);
+        if (r2 != CUDA_SUCCESS) {
+          if (drv_err) *drv_err = static_cast<int>(r2);
+          return cudaErrorInvalidValue;
+        }
+      }
+      // upper bound on chunks: one per expert that is hit, plus one per full 224 rows
+      const long long rows_bound = static_cast<long long>(g.max_m_blocks) * kBlockM;
+      const long long chunk_bound = rows_bound / kToknMaxN + g.num_experts;
+      const long long tile_bound = chunk_bound * g.n_blocks;
+      const int tgrid = static_cast<int>(tile_bound < sm_count() ? (tile_bound > 0 ? tile_bound : 1) : sm_count());
+      return g.epilogue == kEpiSiluMul ? launch_tokn_variant<kEpiSiluMul>(tb, tt, bp, tgrid, stream)
+                                       : launch_tokn_variant<kEpiScaledSlots>(tb, tt, bp, tgrid, stream);
+    }
     const bool hw = g.flavour == FMOE_KERNEL_BLOCK_HW_SCALE;
     if (hw && g.epilogue == kEpiScaledSlots && !g.b_tiled && g.ld_out % 224 == 0 && g.n_stride == kTileN) {
       // Output width tiles by 224: two 224-column accumulators fit tensor memory beside the scale

@@ -58,6 +58,7 @@ struct BlockGemmParams {
   const void* a_scale;          // f32 [cap, k_blocks], or UE8M0 bytes [cap, scale_pitch(k_blocks)] (kHw)
   const float* b_scale;         // [E * b_rows_per_expert / 128, k_blocks]
   int k_blocks;                 // K / 128 (== g.k_iters)
+  int64_t a_rows;               // rows of the activation matrix and of a_scale
   void* out_scale;              // first GEMM: scales of the quantised intermediate, f32 [cap, ld_out/128]
                                 // or UE8M0 bytes [cap, scale_pitch(ld_out/128)] (kHw); `g.out` then receives e4m3
 };

@@ -156,8 +156,16 @@ inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {
 // persistent waves of both flavours from the expected number of routed rows.
 inline int pick_gemm_flavour(const fmoe_traits_c* t, const fmoe_args_c* a, int n_blocks, int sms, int forced) {
   if (t->quant == FMOE_QUANT_BLOCK128) return FMOE_KERNEL_BLOCK_PROMOTE;
-  if (t->quant == FMOE_QUANT_BLOCK128_UE8M0) return FMOE_KERNEL_BLOCK_HW_SCALE;
   const long long rows = static_cast<long long>(a->T) * a->K;
+  if (t->quant == FMOE_QUANT_BLOCK128_UE8M0) {
+    // Tokens on N (gemm_mode 2) multiplies only live rows, rounded up to 16 per expert, where
+    // tokens on M pads every expert to 128-row blocks.  It is never chosen automatically: with two
+    // N <= 224 MMAs per K step that both re-read the token tile, its operand reads from shared
+    // memory per multiply-add are a third higher at 128 tokens per chunk, which on the
+    // DeepSeek-V3 shape (256 rows per expert) cancels the quarter of the rows it saves (first GEMM
+    // 2.20 ms against 2.24 ms), and its second GEMM does not overlap the epilogue (2.42 against 1.54 ms).
+    return forced == 2 ? FMOE_KERNEL_BLOCK_HW_TOKENS_N : FMOE_KERNEL_BLOCK_HW_SCALE;
+  }
   if (forced == 2) return FMOE_KERNEL_PAIR;
   const bool decode = rows <= 32;
   if (forced == 1) return decode ? FMOE_KERNEL_SINGLE_DECODE : FMOE_KERNEL_SINGLE;
