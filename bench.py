@@ -633,7 +633,8 @@ def measure_ep(env, a, c, sampler):
     if os.environ.get("FMOE_EP_MODE", "peer") != "nccl":
         try:
             moe = ep.PeerExpertParallelMoE(c["E"], world, rank, traits, d["w1"], d["w2"], d["s1"], d["s2"],
-                                           tokens_per_rank=T_local, topk=c["K"], hidden=H, fused=a.ep_fused == "on")
+                                           tokens_per_rank=T_local, topk=c["K"], hidden=H, fused=a.ep_fused == "on",
+                                           fp8_wire=a.ep_fp8_wire == "on")
             ep_transport = "peer_memory"
         except Exception as exc:  # noqa: BLE001
             if rank == 0:
@@ -665,6 +666,7 @@ def measure_ep(env, a, c, sampler):
     res["config"]["weight_layout"] = a.weight_layout
     res["config"]["ep_transport"] = ep_transport
     res["config"]["ep_step"] = "fused kernels" if getattr(moe, "fused", False) else "single-purpose kernels"
+    res["config"]["ep_wire"] = "e4m3 rows + scales" if getattr(moe, "fp8_wire", False) else "bf16 rows"
     if a.kernel_only:
         return res, None
 
@@ -826,6 +828,8 @@ def main():
                     help="how the K weighted expert outputs are held before the ordered sum")
     ap.add_argument("--per-config", choices=["on", "off"], default="on",
                     help="single GPU, default workload: also measure C2, C3, C4 and attach them as per_config")
+    ap.add_argument("--ep-fp8-wire", choices=["on", "off"], default="on",
+                    help="N>1, fp8 configurations, fused step: token rows cross NVLink as e4m3 + scales (on) or bf16 (off)")
     ap.add_argument("--ep-fused", choices=["on", "off"], default="on",
                     help="N > 1, peer memory: the fused step (send / recv_ready / wait_combine) or the single-purpose kernels")
     ap.add_argument("--gemm-mode", type=int, choices=[0, 1, 2], default=0,

@@ -49,6 +49,7 @@ struct fused_moe_args {
   const int32_t* num_tokens_dev_ptr = nullptr;  // optional device-side token count (<= num_tokens)
   int expected_tokens = 0;                      // its typical value (kernel choice hint), 0 = num_tokens
   const uint64_t* partial_row_ptrs = nullptr;   // optional [T*K] destinations of the weighted partial rows (bf16)
+  const void* a_scale_ptr = nullptr;            // optional: a_ptr holds e4m3 rows and this their scales (fmoe_quantise_rows)
 };
 
 struct stream_config {
@@ -92,6 +93,7 @@ inline void to_c(const fused_moe_args& a, fmoe_args_c* c) {
   c->num_tokens_dev = a.num_tokens_dev_ptr;
   c->expected_tokens = a.expected_tokens;
   c->partial_row_ptrs = a.partial_row_ptrs;
+  c->x_scale = a.a_scale_ptr;
 }
 }  // namespace fmoe_detail
 

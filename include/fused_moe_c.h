@@ -104,7 +104,7 @@ typedef struct fmoe_traits_c {
 
 /* Run-time arguments (ck_tile's fused_moe_args role).  All pointers are device pointers. */
 typedef struct fmoe_args_c {
-  const void* x;            /* [T, H] bf16 activations */
+  const void* x;            /* [T, H] bf16 activations ([T, H] e4m3 when x_scale is set) */
   const void* w1;           /* [E, 2I, H] gate rows then up rows ([E, I, H] when gate_only); bf16 or e4m3 */
   const void* w2;           /* [E, H, I]; bf16 or e4m3 */
   const float* w1_scale;    /* quant 1: [E, 2I]; quant 2, 3: [E, 2I/128, H/128]; else NULL */
@@ -139,6 +139,12 @@ typedef struct fmoe_args_c {
   int32_t* done_counter;
   int32_t done_flag_count;
   int32_t reserved2;
+  /* Activations that are already quantised (optional; fp8 quant modes only).  When set, x holds
+   * e4m3 rows and x_scale their scales exactly as fmoe_quantise_rows writes them for traits.quant
+   * (f32 [T], f32 [T, H/128] or UE8M0 bytes [T, roundup(H/128, 4)]); the operator skips its own
+   * quantisation of x and the result is bit-identical to passing the bf16 rows.  Used on the
+   * receiving side of an expert-parallel dispatch that sends e4m3 rows. */
+  const void* x_scale;
 } fmoe_args_c;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -254,6 +260,14 @@ FMOE_API int fmoe_profile_destroy(void* handle);
 FMOE_API int fmoe_gather_rows(const void* src, int32_t n_src, int32_t cols, const int32_t* row_ids,
                               int32_t n_rows, const int32_t* n_rows_dev, void* dst, void* stream);
 
+/* The operator's dynamic quantisation of activation rows as a call of its own: q[t, :] =
+ * e4m3(x[t, :] / scale) with one scale per row (quant = token_channel: scales f32 [T]) or per
+ * 128 columns (block128: f32 [T, H/128]; block128_ue8m0: power-of-two scales as bytes
+ * [T, roundup(H/128, 4)]).  H a multiple of 16 (128 for the block modes).  No counterpart in the
+ * reference operator, which quantises inside the call. */
+FMOE_API int fmoe_quantise_rows(const void* x, int32_t T, int32_t H, int32_t quant, void* q, void* scales,
+                                void* stream);
+
 /* Expert-parallel combine: out[t, :] = bf16( sum over k ascending of rows[index[t*K+k], :] )
  * with f32 accumulation; index < 0 skips the term.  rows are the bf16 partial results that
  * came back through the all-to-all.  No counterpart in the single-GPU reference. */
@@ -277,6 +291,8 @@ typedef struct fmoe_ep_layout_c {
   int64_t send_cap;  /* rows of `back` (>= T*K of this rank) */
   uint64_t flags_dispatch; /* int32[G]: epoch at which each peer finished writing its rows here (fused path) */
   uint64_t flags_return;   /* int32[G]: epoch at which each peer finished returning this rank's rows (fused path) */
+  uint64_t row_scales;     /* bytes [recv_cap, scale_row_bytes]: scales of the received rows when they travel as
+                              e4m3 (fmoe_ep_send_rows); unused otherwise */
 } fmoe_ep_layout_c;
 
 /* Groups this rank's T*K routed pairs by the rank that owns the expert (stable):
@@ -333,6 +349,17 @@ FMOE_API int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* t
                           const fmoe_ep_layout_c* lay, int32_t me, int32_t G, int32_t* scratch,
                           const int32_t* epoch_dev, int32_t* n_recv_dev, int32_t* status, int32_t timeout_ms,
                           void* stream);
+/* The same step with the token rows in any fixed-size encoding: row_bytes per row (a multiple of
+ * 16), stored at lay->rows + slot * row_bytes on the owner, plus optional per-row scales
+ * (scale_row_bytes, a multiple of 4, stored at lay->row_scales + slot * scale_row_bytes).  With rows
+ * and scales from fmoe_quantise_rows the dispatch moves e4m3 instead of bf16 (half the bytes) and
+ * the owner passes them to the operator as x / x_scale; results are bit-identical to sending bf16.
+ * fmoe_ep_send(x, ..., H, ...) is this call with row_bytes = 2 * H and no scales. */
+FMOE_API int fmoe_ep_send_rows(const void* rows, int32_t row_bytes, const void* row_scales, int32_t scale_row_bytes,
+                               const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                               int32_t experts_per_rank, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,
+                               int32_t me, int32_t G, int32_t* scratch, const int32_t* epoch_dev,
+                               int32_t* n_recv_dev, int32_t* status, int32_t timeout_ms, void* stream);
 /* Waits until every rank's rows have arrived and fills row_ptrs[i] (i < *n_recv_dev) with the
  * address, in the source rank's `back` array, where the result of received row i belongs: the
  * partial_row_ptrs of the local fmoe_run. */

@@ -169,6 +169,30 @@ def test_hardware_scaled_down_gemm_with_224_column_tiles(T, H, I, E, K, partial)
     check(d, got, run_oracle(d, partial=partial))
 
 
+@pytest.mark.parametrize("quant", [1, 2, 3])
+@pytest.mark.parametrize("T,H,I,E,K", [(200, 512, 256, 8, 2), (77, 256, 384, 5, 1), (16, 1024, 128, 8, 2)])
+def test_prequantised_activations_give_identical_bits(quant, T, H, I, E, K):
+    """Activations quantised by fmoe_quantise_rows and passed as e4m3 rows + scales (what the
+    receiving side of an e4m3 expert-parallel dispatch does) give the bits of the bf16 call."""
+    d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=7 * T + quant)
+    ref, _ = run_gpu(d)
+    args = args_for(d)
+    q, s = api.quantise_rows(args.a, QUANT_NAME[quant])
+    args.a, args.a_scale = q, s
+    got = out_bits(M.fused_moe(traits_for(quant), args))
+    torch.cuda.synchronize()
+    assert api.check_status(args.workspace) == 0
+    assert (got == ref).all()
+    # the stand-alone quantisation against the oracle's, bit for bit (bytes and scales)
+    q_ref, s_ref = O.quant_rows_e4m3(O.bf16_to_f32(d["x"]), None if quant == 1 else 128, pow2=(quant == 3))
+    assert (q.cpu().numpy() == q_ref).all()
+    if quant == 3:
+        s_got = s.cpu().numpy()[:, :H // 128]
+        assert (s_got == ((s_ref.view(np.uint32) >> 23) & 0xff).astype(np.uint8)).all()
+    else:
+        assert (s.cpu().numpy().view(np.float32).reshape(s_ref.shape) == s_ref).all()
+
+
 TOKENS_ON_N_CASES = [
     (300, 512, 384, 6, 2, "spread"),      # ~100 rows per expert: one chunk each
     (1500, 512, 256, 4, 2, "spread"),     # ~750 rows per expert: four chunks of unequal size

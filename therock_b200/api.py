@@ -48,7 +48,7 @@ class _Args(ctypes.Structure):
                 ("reserved", ctypes.c_int32 * 2), ("num_tokens_dev", ctypes.c_void_p),
                 ("partial_row_ptrs", ctypes.c_void_p), ("done_flag_addrs", ctypes.c_void_p),
                 ("done_flag_value", ctypes.c_void_p), ("done_counter", ctypes.c_void_p),
-                ("done_flag_count", ctypes.c_int32), ("reserved2", ctypes.c_int32)]
+                ("done_flag_count", ctypes.c_int32), ("reserved2", ctypes.c_int32), ("x_scale", ctypes.c_void_p)]
 
 
 class _Layout(ctypes.Structure):
@@ -62,7 +62,7 @@ class EpLayout(ctypes.Structure):
     """Byte offsets inside the per-rank peer-addressable buffer (fmoe_ep_layout_c)."""
     _fields_ = [(n, ctypes.c_uint64) for n in ("flags", "matrix", "rows", "ids", "weights", "src", "back")] + \
                [("recv_cap", ctypes.c_int64), ("send_cap", ctypes.c_int64),
-                ("flags_dispatch", ctypes.c_uint64), ("flags_return", ctypes.c_uint64)]
+                ("flags_dispatch", ctypes.c_uint64), ("flags_return", ctypes.c_uint64), ("row_scales", ctypes.c_uint64)]
 
 
 _lib: Optional[ctypes.CDLL] = None
@@ -116,6 +116,9 @@ def lib() -> ctypes.CDLL:
         l.fmoe_ep_send_scratch_words.argtypes = [i32, i32, i32]
         l.fmoe_ep_send.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp,
                                    vp, vp, i32, vp]
+        l.fmoe_ep_send_rows.argtypes = [vp, i32, vp, i32, vp, vp, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32,
+                                        vp, vp, vp, vp, i32, vp]
+        l.fmoe_quantise_rows.argtypes = [vp, i32, i32, i32, vp, vp, vp]
         l.fmoe_ep_recv_ready.argtypes = [i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp, vp, i32, vp]
         l.fmoe_ep_wait_combine.argtypes = [vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp,
                                            vp, i32, vp]
@@ -185,13 +188,17 @@ class FusedMoeArgs:
     done_flag_addrs: Optional[torch.Tensor] = None   # int64 [n]: addresses that receive done_flag_value[0] at the end
     done_flag_value: Optional[torch.Tensor] = None   # int32 [1] on the device
     done_counter: Optional[torch.Tensor] = None      # int32 [1] on the device, zero
+    a_scale: Optional[torch.Tensor] = None           # scales of `a` when `a` already holds e4m3 rows (quantise_rows)
 
     def to_c(self, gate_only: bool = False) -> _Args:
         for name in ("a", "g", "d", "topk_ids", "topk_weight"):
             t = getattr(self, name)
             if not (t.is_cuda and t.is_contiguous()):
                 raise FmoeError(-1, f"{name} must be a contiguous CUDA tensor")
-        if self.a.dtype != torch.bfloat16:
+        if self.a_scale is not None:
+            if self.a.element_size() != 1:
+                raise FmoeError(-1, "a must hold e4m3 bytes when a_scale is given")
+        elif self.a.dtype != torch.bfloat16:
             raise FmoeError(-1, "a must be bf16")
         if self.topk_ids.dtype != torch.int32 or self.topk_weight.dtype != torch.float32:
             raise FmoeError(-1, "topk_ids must be int32 and topk_weight float32")
@@ -214,6 +221,8 @@ class FusedMoeArgs:
         c.T, c.H, c.I, c.E, c.K = T, H, I, E, self.topk_ids.shape[1]
         c.num_tokens_dev = self.num_tokens_dev.data_ptr() if self.num_tokens_dev is not None else None
         c.expected_tokens = int(self.expected_tokens)
+        if self.a_scale is not None:
+            c.x_scale = self.a_scale.data_ptr()
         if self.partial_row_ptrs is not None:
             c.partial_row_ptrs = self.partial_row_ptrs.data_ptr()
         if self.done_flag_addrs is not None:
@@ -267,7 +276,7 @@ def fused_moe(traits: FusedMoeTraits, args: FusedMoeArgs, stream=None, time_kern
     output / workspace tensors are allocated here with torch (callers on a hot loop pass
     their own)."""
     if args.o is None:
-        args.o = torch.empty_like(args.a)
+        args.o = torch.empty(args.a.shape, dtype=torch.bfloat16, device=args.a.device)
     if args.workspace is None:
         args.workspace = torch.empty(fused_moe_workspace_size(traits, args), dtype=torch.uint8,
                                      device=args.a.device)
@@ -349,6 +358,32 @@ def gather_rows(src: torch.Tensor, row_ids: torch.Tensor, n_rows_dev: torch.Tens
     _check(lib().fmoe_gather_rows(src.data_ptr(), src.shape[0], src.shape[1], row_ids.data_ptr(), n,
                                   n_rows_dev.data_ptr(), out.data_ptr(), _stream_ptr(stream)))
     return out
+
+
+def quant_scale_row_bytes(quant: str, hidden: int) -> int:
+    """Bytes of one row of activation scales in the given fp8 quant mode."""
+    if quant == "token_channel":
+        return 4
+    if quant == "block128":
+        return 4 * (hidden // 128)
+    if quant == "block128_ue8m0":
+        return (hidden // 128 + 3) // 4 * 4
+    raise FmoeError(-1, f"{quant!r} is not an fp8 quant mode")
+
+
+def quantise_rows(x: torch.Tensor, quant: str, q: Optional[torch.Tensor] = None,
+                  scales: Optional[torch.Tensor] = None, stream=None):
+    """The operator's dynamic e4m3 quantisation of activation rows as a call of its own.
+    Returns (q uint8 [T, H], scales uint8 [T, quant_scale_row_bytes]); pass them as
+    FusedMoeArgs.a / a_scale and the operator's result is bit-identical to passing x."""
+    T, H = x.shape
+    if q is None:
+        q = torch.empty(T, H, dtype=torch.uint8, device=x.device)
+    if scales is None:
+        scales = torch.empty(T, quant_scale_row_bytes(quant, H), dtype=torch.uint8, device=x.device)
+    _check(lib().fmoe_quantise_rows(x.data_ptr(), T, H, QUANT[quant], q.data_ptr(), scales.data_ptr(),
+                                    _stream_ptr(stream)))
+    return q, scales
 
 
 def combine_rows(rows: torch.Tensor, index: torch.Tensor, T: int, K: int,

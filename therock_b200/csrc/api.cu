@@ -214,7 +214,7 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
   const bool blk = fmoe::quant_is_block(traits->quant);
   const bool hw = traits->quant == FMOE_QUANT_BLOCK128_UE8M0;
   const int qmode = !fp8 ? 0 : (hw ? 3 : (blk ? 2 : 1));
-  if (fmoe::decode_prologue_applies(a.T, a.K, qmode)) {
+  if (a.x_scale == nullptr && fmoe::decode_prologue_applies(a.T, a.K, qmode)) {
     // decode-sized batch: sorting and gather (+ quantisation) are one launch
     NvtxRange r("decode_prologue");
     FMOE_CUDA(fmoe::launch_decode_prologue(a.topk_ids, a.topk_weight, a.T, a.K, a.E, plan.cap, a.x, a.H, qmode,
@@ -231,7 +231,11 @@ static int run_impl(const fmoe_traits_c* traits, const fmoe_args_c* args, void* 
     }
     FMOE_STAGE(1);
     NvtxRange r("gather_quant");
-    if (fmoe::quantise_once(traits, args)) {
+    if (a.x_scale != nullptr) {
+      // the caller's rows are e4m3 with their scales already: the routed pairs copy them
+      FMOE_CUDA(fmoe::launch_gather_quantised(a.x, a.x_scale, a.T, a.H, sorted_ids, num_post_pad, plan.cap, qmode,
+                                              a_sorted, a_scale, stream));
+    } else if (fmoe::quantise_once(traits, args)) {
       // every token row is quantised once; the routed pairs then copy e4m3 rows and scales
       void* xq = ws + l.x_quant;
       void* xq_scale = ws + l.x_quant_scale;
@@ -464,6 +468,20 @@ int fmoe_gather_rows(const void* src, int32_t n_src, int32_t cols, const int32_t
   if (guard.rc() != FMOE_OK) return guard.rc();
   FMOE_CUDA(fmoe::launch_gather_rows(src, n_src, cols, row_ids, n_rows_dev, n_rows, 0, dst, nullptr,
                                      static_cast<cudaStream_t>(stream)));
+  return FMOE_OK;
+}
+
+int fmoe_quantise_rows(const void* x, int32_t T, int32_t H, int32_t quant, void* q, void* scales, void* stream) {
+  if (!x || !q || !scales) return fail(FMOE_ERR_INVALID_ARG, "x, q and scales are required");
+  if (quant != FMOE_QUANT_TOKEN_CHANNEL && quant != FMOE_QUANT_BLOCK128 && quant != FMOE_QUANT_BLOCK128_UE8M0)
+    return fail(FMOE_ERR_INVALID_ARG, "quant must be an fp8 mode");
+  if (H <= 0 || H % 16 || (quant != FMOE_QUANT_TOKEN_CHANNEL && H % 128))
+    return fail(FMOE_ERR_UNSUPPORTED, "H must be a multiple of 16 (128 for the block modes)");
+  if (T <= 0) return FMOE_OK;
+  DeviceGuard guard(x);
+  if (guard.rc() != FMOE_OK) return guard.rc();
+  const int qmode = quant == FMOE_QUANT_TOKEN_CHANNEL ? 1 : (quant == FMOE_QUANT_BLOCK128 ? 2 : 3);
+  FMOE_CUDA(fmoe::launch_gather_rows(x, T, H, nullptr, nullptr, T, qmode, q, scales, static_cast<cudaStream_t>(stream)));
   return FMOE_OK;
 }
 

@@ -183,10 +183,12 @@ __device__ __forceinline__ void wait_flags(const int32_t* flags, int32_t* ready,
 }
 
 struct EpSendParams {
-  const uint4* x;
+  const uint4* x;            // [T] rows of row_vecs 16-byte vectors
+  const uint32_t* x_scale;   // [T] rows of scale_words 32-bit words, or nullptr
+  int row_vecs, scale_words;
   const int32_t* topk_ids;
   const float* topk_w;
-  int T, K, H, e_local;
+  int T, K, e_local;
   const uint64_t* peer_base;
   fmoe_ep_layout_c lay;
   int me, G;
@@ -294,7 +296,7 @@ ep_send_kernel(const EpSendParams p) {
   }
   __syncthreads();
   // 6. rows and their metadata into the owners' receive arrays (plain peer stores)
-  const int nvec = p.H >> 3;
+  const int nvec = p.row_vecs;
   for (int idx = tid; idx < n * nvec; idx += kSendThreads) {
     const int i = idx / nvec, v = idx - i * nvec;
     const int d = dest_rank[i], dst = dest_slot[i];
@@ -307,6 +309,9 @@ ep_send_kernel(const EpSendParams p) {
     const int d = dest_rank[i], dst = dest_slot[i];
     if (d < 0 || dst >= p.lay.recv_cap) continue;
     const int r = r0 + i;
+    for (int w = 0; w < p.scale_words; ++w)
+      peer_ptr<uint32_t>(p.peer_base, d, p.lay.row_scales)[static_cast<size_t>(dst) * p.scale_words + w] =
+          p.x_scale[static_cast<size_t>(r / p.K) * p.scale_words + w];
     peer_ptr<int32_t>(p.peer_base, d, p.lay.ids)[dst] = p.topk_ids[r] % p.e_local;
     peer_ptr<float>(p.peer_base, d, p.lay.weights)[dst] = p.topk_w[r];
     peer_ptr<int2>(p.peer_base, d, p.lay.src)[dst] = make_int2(p.me, r);
@@ -478,20 +483,34 @@ int fmoe_ep_send(const void* x, const int32_t* topk_ids, const float* topk_weigh
                  int32_t experts_per_rank, const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
                  int32_t G, int32_t* scratch, const int32_t* epoch_dev, int32_t* n_recv_dev, int32_t* status,
                  int32_t timeout_ms, void* stream) {
+  if (H <= 0 || H % 8) return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send: H must be a positive multiple of 8");
+  return fmoe_ep_send_rows(x, 2 * H, nullptr, 0, topk_ids, topk_weight, T, K, experts_per_rank, peer_base, lay, me, G,
+                           scratch, epoch_dev, n_recv_dev, status, timeout_ms, stream);
+}
+
+int fmoe_ep_send_rows(const void* x, int32_t row_bytes, const void* row_scales, int32_t scale_row_bytes,
+                      const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                      int32_t experts_per_rank, const uint64_t* peer_base, const fmoe_ep_layout_c* lay, int32_t me,
+                      int32_t G, int32_t* scratch, const int32_t* epoch_dev, int32_t* n_recv_dev, int32_t* status,
+                      int32_t timeout_ms, void* stream) {
   if (!x || !topk_ids || !topk_weight || !peer_base || !lay || !scratch || !epoch_dev || !n_recv_dev || !status)
     return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send: a required pointer is null");
   if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G)
     return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send: rank %d / world %d out of range (at most %d ranks)", me, G,
                       fmoe::kSendMaxRanks);
-  if (H <= 0 || H % 8 || T <= 0 || K <= 0 || experts_per_rank <= 0 || timeout_ms < 0)
-    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send: H must be a positive multiple of 8; T, K, experts_per_rank positive");
+  if (row_bytes <= 0 || row_bytes % 16 || T <= 0 || K <= 0 || experts_per_rank <= 0 || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send: row bytes must be a positive multiple of 16; T, K, experts_per_rank positive");
+  if (scale_row_bytes < 0 || scale_row_bytes % 4 || (scale_row_bytes > 0 && !row_scales))
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send: scale row bytes must be a multiple of 4 and come with row_scales");
   const int grid = ep_send_grid(T, K);
   if ((static_cast<long long>(T) * K + grid - 1) / grid > fmoe::kSendMaxChunk)
     return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send: at most %d routed pairs per rank", grid * fmoe::kSendMaxChunk);
   fmoe::EpSendParams p;
   p.x = reinterpret_cast<const uint4*>(x);
+  p.x_scale = reinterpret_cast<const uint32_t*>(row_scales);
+  p.row_vecs = row_bytes / 16; p.scale_words = scale_row_bytes / 4;
   p.topk_ids = topk_ids; p.topk_w = topk_weight;
-  p.T = T; p.K = K; p.H = H; p.e_local = experts_per_rank;
+  p.T = T; p.K = K; p.e_local = experts_per_rank;
   p.peer_base = peer_base; p.lay = *lay; p.me = me; p.G = G;
   p.sync = scratch; p.cta_counts = scratch + 8;
   p.epoch = epoch_dev; p.n_recv_dev = n_recv_dev; p.status = status;

@@ -86,6 +86,8 @@ inline int validate_dims(const fmoe_traits_c* t, const fmoe_args_c* a) {
   }
   if (quant_is_block(t->quant) && (a->H % 128 || a->I % 128))
     return fail(FMOE_ERR_UNSUPPORTED, "block scales need hidden and intermediate sizes that are multiples of 128");
+  if (a->x_scale && (!quant_is_fp8(t->quant) || a->H % 16))
+    return fail(FMOE_ERR_INVALID_ARG, "x_scale (pre-quantised activations) needs an fp8 quant mode and H a multiple of 16");
   return FMOE_OK;
 }
 
@@ -104,12 +106,12 @@ inline uint64_t packed_scale_bytes(int64_t cap, int k_elems) {
 
 // Decode-sized batches without block scales run sorting + gather (+ quantisation) as one kernel.
 inline bool fused_prologue(const fmoe_traits_c* t, const fmoe_args_c* a) {
-  return static_cast<long long>(a->T) * a->K <= 128 &&
+  return static_cast<long long>(a->T) * a->K <= 128 && a->x_scale == nullptr &&
          (t->quant == FMOE_QUANT_NONE || t->quant == FMOE_QUANT_TOKEN_CHANNEL);
 }
 // fp8, K >= 2 and not decode-sized: quantise the T token rows once, then gather e4m3 rows.
 inline bool quantise_once(const fmoe_traits_c* t, const fmoe_args_c* a) {
-  return quant_is_fp8(t->quant) && a->K >= 2 && !fused_prologue(t, a) && a->H % 16 == 0;
+  return quant_is_fp8(t->quant) && a->K >= 2 && !fused_prologue(t, a) && a->H % 16 == 0 && a->x_scale == nullptr;
 }
 
 inline int make_plan(const fmoe_traits_c* t, const fmoe_args_c* a, Plan* p) {

@@ -273,6 +273,11 @@ class PeerExpertParallelMoE:
     fused=False: the same step from single-purpose kernels (plan, publish, barrier, dispatch,
         barrier, local operator, return, barrier, combine), thirteen launches.
 
+    fp8_wire (fused step with an fp8 quant mode; default on): the token rows are quantised once on
+        the sending rank (the operator's own quantisation, as a call of its own) and cross NVLink as
+        e4m3 rows + scales, half the bytes of bf16; the owner hands them to the operator as
+        pre-quantised activations.  Bit-identical to sending bf16 rows; one more launch.
+
     Arithmetic in both: each (token, k) partial row crosses NVLink as bf16 and the k-sum is f32 with
     one more rounding -- the operator's partial_dtype = bf16 contract.
     Every wait is a bounded spin; a rank that never arrives shows up in `status` instead of
@@ -281,7 +286,7 @@ class PeerExpertParallelMoE:
 
     def __init__(self, num_experts: int, world: int, rank: int, traits, w1_local, w2_local,
                  w1_scale=None, w2_scale=None, *, tokens_per_rank: int, topk: int, hidden: int, group=None,
-                 fused: bool = True):
+                 fused: bool = True, fp8_wire: Optional[bool] = None):
         import copy
         import ctypes
         import os
@@ -295,6 +300,8 @@ class PeerExpertParallelMoE:
         self.traits = copy.copy(traits)
         if self.fused:
             self.traits.partial_dtype = "bf16"
+        is_fp8 = self.traits.quant != "none"
+        self.fp8_wire = self.fused and is_fp8 and hidden % 16 == 0 and (fp8_wire is None or bool(fp8_wire))
         self.E, self.world, self.rank = num_experts, world, rank
         self.e_local = num_experts // world
         self.T, self.K, self.H = tokens_per_rank, topk, hidden
@@ -306,9 +313,13 @@ class PeerExpertParallelMoE:
             return (n + 255) // 256 * 256
         lay = api.EpLayout()
         off = 0
+        row_bytes = hidden if self.fp8_wire else hidden * 2
+        scale_bytes = api.quant_scale_row_bytes(self.traits.quant, hidden) if self.fp8_wire else 0
+        self.row_bytes, self.scale_row_bytes = row_bytes, scale_bytes
         for name, nbytes in (("flags", world * 4), ("flags_dispatch", world * 4), ("flags_return", world * 4),
                              ("matrix", world * world * 4),
-                             ("rows", recv_cap * hidden * 2), ("ids", recv_cap * 4), ("weights", recv_cap * 4),
+                             ("rows", recv_cap * row_bytes), ("row_scales", recv_cap * scale_bytes),
+                             ("ids", recv_cap * 4), ("weights", recv_cap * 4),
                              ("src", recv_cap * 8), ("back", R * hidden * 2)):
             setattr(lay, name, off)
             off = al(off + nbytes)
@@ -325,7 +336,14 @@ class PeerExpertParallelMoE:
         def view(name, n, dt):
             o = getattr(lay, name)
             return self.buf[o:o + n * torch.empty((), dtype=dt).element_size()].view(dt)
-        self.rows = view("rows", recv_cap * hidden, torch.bfloat16).view(recv_cap, hidden)
+        if self.fp8_wire:
+            self.rows = view("rows", recv_cap * hidden, torch.uint8).view(recv_cap, hidden)
+            self.row_scales = view("row_scales", recv_cap * scale_bytes, torch.uint8).view(recv_cap, scale_bytes)
+            self.xq = torch.empty(tokens_per_rank, hidden, dtype=torch.uint8, device=dev)
+            self.xq_scale = torch.empty(tokens_per_rank, scale_bytes, dtype=torch.uint8, device=dev)
+        else:
+            self.rows = view("rows", recv_cap * hidden, torch.bfloat16).view(recv_cap, hidden)
+            self.row_scales = None
         self.ids = view("ids", recv_cap, torch.int32).view(recv_cap, 1)
         self.wts = view("weights", recv_cap, torch.float32).view(recv_cap, 1)
         self.back = view("back", R * hidden, torch.bfloat16).view(R, hidden)
@@ -338,7 +356,8 @@ class PeerExpertParallelMoE:
         self.out_rows = torch.empty(recv_cap, hidden, dtype=torch.bfloat16, device=dev)
         self.args = api.FusedMoeArgs(a=self.rows, g=w1_local, d=w2_local, topk_ids=self.ids,
                                      topk_weight=self.wts, o=self.out_rows, g_scale=w1_scale,
-                                     d_scale=w2_scale, num_tokens_dev=self.n_recv, expected_tokens=R)
+                                     d_scale=w2_scale, num_tokens_dev=self.n_recv, expected_tokens=R,
+                                     a_scale=self.row_scales)
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         if self.fused:
             # fused step: the epoch starts at 1 and is advanced on the device by wait_combine
@@ -356,7 +375,7 @@ class PeerExpertParallelMoE:
         self.trace = None                    # set to [] to collect (phase, cuda event) marks
         self._ctypes = ctypes
         ops = api.launches_per_run(self.traits, self.args)
-        self.launches_per_step = (3 + ops) if self.fused else (8 + ops)
+        self.launches_per_step = (3 + ops + (1 if self.fp8_wire else 0)) if self.fused else (8 + ops)
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
@@ -374,10 +393,19 @@ class PeerExpertParallelMoE:
         if out is None:
             out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         self._mark("start")
-        api._check(lib.fmoe_ep_send(x.data_ptr(), topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, H, self.e_local,
-                                    pb, by(self.lay), self.rank, G, self.send_scratch.data_ptr(),
-                                    self.epoch_dev.data_ptr(), self.n_recv.data_ptr(), self.status.data_ptr(),
-                                    self.barrier_timeout_ms, st))
+        if self.fp8_wire:
+            api.quantise_rows(x, self.traits.quant, self.xq, self.xq_scale)
+            api._check(lib.fmoe_ep_send_rows(self.xq.data_ptr(), self.row_bytes, self.xq_scale.data_ptr(),
+                                             self.scale_row_bytes, topk_ids.data_ptr(), topk_weight.data_ptr(), T, K,
+                                             self.e_local, pb, by(self.lay), self.rank, G,
+                                             self.send_scratch.data_ptr(), self.epoch_dev.data_ptr(),
+                                             self.n_recv.data_ptr(), self.status.data_ptr(),
+                                             self.barrier_timeout_ms, st))
+        else:
+            api._check(lib.fmoe_ep_send(x.data_ptr(), topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, H,
+                                        self.e_local, pb, by(self.lay), self.rank, G, self.send_scratch.data_ptr(),
+                                        self.epoch_dev.data_ptr(), self.n_recv.data_ptr(), self.status.data_ptr(),
+                                        self.barrier_timeout_ms, st))
         self._mark("send")
         api._check(lib.fmoe_ep_recv_ready(H, self.n_recv.data_ptr(), pb, by(self.lay), self.rank, G,
                                           self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(),
