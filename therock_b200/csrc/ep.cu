@@ -50,7 +50,8 @@ __global__ void ep_barrier_kernel(const uint64_t* __restrict__ peer_base, uint64
     epoch = next;
   }
   if (p >= G) return;
-  __threadfence_system();   // everything this rank wrote before the barrier is visible first
+  // the release store orders everything this rank wrote before the barrier (earlier kernels on the
+  // stream included: the release is cumulative) before the flag
   volatile int32_t* theirs = peer_ptr<int32_t>(peer_base, p, flags_off) + me;
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
   const int32_t* mine = peer_ptr<int32_t>(peer_base, me, flags_off) + p;
@@ -131,6 +132,9 @@ __device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
 __device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Release fence at system scope, the acquire/release form (not the sequentially consistent
+// membar.sys of __threadfence_system()).
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 // After one system-scope fence: fence + relaxed store is a release, without a fence per flag.
 __device__ __forceinline__ void st_relaxed_sys(int32_t* p, int v) {
   asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -325,7 +329,7 @@ ep_send_kernel(const EpSendParams p) {
     if (prev == C - 1) {
       p.sync[0] = 0;
       p.sync[1] = 0;
-      __threadfence_system();
+      fence_acq_rel_sys();
       for (int peer = 0; peer < G; ++peer)
         st_relaxed_sys(peer_ptr<int32_t>(p.peer_base, peer, p.lay.flags_dispatch) + p.me, epoch);
     }

@@ -128,7 +128,7 @@ __device__ __forceinline__ void grid_done_signal(const GemmParams& p) {
   __threadfence();
   const int prev = atomicAdd(p.done_counter, 1);
   if (prev != static_cast<int>(gridDim.x) - 1) return;
-  __threadfence_system();
+  ptx::fence_acq_rel_sys();
   const int v = *p.done_value;
   for (int i = 0; i < p.done_count; ++i)
     asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.done_addrs[i]), "r"(v) : "memory");

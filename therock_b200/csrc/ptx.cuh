@@ -86,6 +86,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
+// Release fence at system scope (the acquire/release form, not the sequentially consistent
+// membar.sys that __threadfence_system() emits): with a relaxed system-scope store after it this
+// is a release that is cumulative over everything the thread has observed.
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
 // Hint: bring one box of a tiled tensor into L2 (no shared memory, no barrier).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tm, int32_t x, int32_t y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
