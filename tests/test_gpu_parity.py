@@ -11,7 +11,7 @@ import torch
 from oracle import oracle as O
 import therock_b200 as M
 from therock_b200 import api
-from tests.util import (args_for, bf16_dev, out_bits, rel_l2, run_gpu, run_oracle, to_dev, traits_for)
+from tests.util import (QUANT_NAME, args_for, bf16_dev, out_bits, rel_l2, run_gpu, run_oracle, to_dev, traits_for)
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")

@@ -117,18 +117,6 @@ int gemm_mode_override() {
 
 int device_sm_count() { return sm_count(); }
 
-// K stages by which the block-scaled kernels prefetch weight slabs into L2.  A library built with
-// -DFMOE_TIMING_SWITCHES honours FMOE_L2_AHEAD (used to compare settings in one call).
-static int block_l2_ahead() {
-#ifdef FMOE_TIMING_SWITCHES
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("FMOE_L2_AHEAD"); v = e ? atoi(e) : kBlockL2Ahead; }
-  return v;
-#else
-  return kBlockL2Ahead;
-#endif
-}
-
 bool pdl_enabled() {
   static int on = -1;
   if (on < 0) {
@@ -232,7 +220,6 @@ cudaError_t launch_grouped_gemm(const GemmLaunch& g, cudaStream_t stream, int* d
     bp.b_scale = g.b_scale;
     bp.k_blocks = p.k_iters;
     bp.a_rows = g.a_rows;
-    bp.l2_ahead = block_l2_ahead();
     bp.out_scale = g.out_scale;
     if (tokn) {
       if (g.epilogue == kEpiSilu) return cudaErrorInvalidValue;

@@ -38,7 +38,6 @@ namespace fmoe {
 constexpr int kBlockGemmThreads = 384;   // warpgroup 0: producer, MMA, scale loader; warpgroups 1, 2: epilogue
 constexpr int kBlockStages = 4;
 constexpr int kScaleAhead = 4;           // K blocks between the load of an f32 scale and its use
-constexpr int kBlockL2Ahead = 0;         // K stages of L2 prefetch of the weight slabs (0 = none)
 // setmaxnreg only redistributes what the CTA was given at launch (384 threads x 168 registers):
 // the per-role counts must add up to no more than that, or setmaxnreg.inc never returns.
 constexpr int kBlockThinRegs = 40;       // registers per thread kept by warpgroup 0
@@ -60,7 +59,6 @@ struct BlockGemmParams {
   const float* b_scale;         // [E * b_rows_per_expert / 128, k_blocks]
   int k_blocks;                 // K / 128 (== g.k_iters)
   int64_t a_rows;               // rows of the activation matrix and of a_scale
-  int l2_ahead;                 // K stages by which the producer prefetches the weight slabs into L2 (0 = off)
   void* out_scale;              // first GEMM: scales of the quantised intermediate, f32 [cap, ld_out/128]
                                 // or UE8M0 bytes [cap, scale_pitch(ld_out/128)] (kHw); `g.out` then receives e4m3
 };
@@ -148,28 +146,7 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
         const int a_row = tc.m_blk * kBlockM;
         const int b_row0 = tc.expert * p.b_rows_per_expert + tc.n_blk * p.n_stride;
         const int b_row1 = b_row0 + p.second_slab_offset;
-        // the weight slabs of the next tile of this CTA, for the prefetch that runs past this tile's end
-        int nb_row0 = -1, nb_row1 = -1;
-        if (bp.l2_ahead > 0 && tile + static_cast<int>(gridDim.x) < total_tiles) {
-          const TileCoord tn = decode_tile(tile + gridDim.x, cum_s, p.num_experts, p.n_blocks);
-          nb_row0 = tn.expert * p.b_rows_per_expert + tn.n_blk * p.n_stride;
-          nb_row1 = nb_row0 + p.second_slab_offset;
-        }
         for (int k = 0; k < p.k_iters; ++k) {
-          if (bp.l2_ahead > 0) {
-            // Weights stream from DRAM once; the ring holds four stages, less than the bytes a DRAM
-            // round trip needs in flight.  Asking L2 for the slabs some stages early deepens the
-            // pipeline without shared memory.
-            int kp = k + bp.l2_ahead, r0 = b_row0, r1 = b_row1;
-            if (kp >= p.k_iters) { kp -= p.k_iters; r0 = nb_row0; r1 = nb_row1; }
-            if (r0 >= 0 && kp < p.k_iters) {
-              int px, py0, py1;
-              b_coords(p, r0, kp, 128, px, py0);
-              b_coords(p, r1, kp, 128, px, py1);
-              ptx::tma_prefetch_l2_2d(&tm_b, px, py0);
-              ptx::tma_prefetch_l2_2d(&tm_b, px, py1);
-            }
-          }
           if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) {
             ok = false;
             break;

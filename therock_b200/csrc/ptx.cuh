@@ -91,14 +91,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 // is a release that is cumulative over everything the thread has observed.
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
-// Hint: bring one box of a tiled tensor into L2 (no shared memory, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tm, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-               :
-               : "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y)
-               : "memory");
-}
-
 // ----------------------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),
