@@ -634,7 +634,8 @@ def measure_ep(env, a, c, sampler):
         try:
             moe = ep.PeerExpertParallelMoE(c["E"], world, rank, traits, d["w1"], d["w2"], d["s1"], d["s2"],
                                            tokens_per_rank=T_local, topk=c["K"], hidden=H, fused=a.ep_fused == "on",
-                                           fp8_wire=a.ep_fp8_wire == "on")
+                                           fp8_wire=a.ep_fp8_wire == "on",
+                                           dedup=None if a.ep_dedup == "auto" else a.ep_dedup == "on")
             ep_transport = "peer_memory"
         except Exception as exc:  # noqa: BLE001
             if rank == 0:
@@ -667,6 +668,7 @@ def measure_ep(env, a, c, sampler):
     res["config"]["ep_transport"] = ep_transport
     res["config"]["ep_step"] = "fused kernels" if getattr(moe, "fused", False) else "single-purpose kernels"
     res["config"]["ep_wire"] = "e4m3 rows + scales" if getattr(moe, "fp8_wire", False) else "bf16 rows"
+    res["config"]["ep_rows"] = "one per (token, owner rank)" if getattr(moe, "dedup", False) else "one per (token, expert)"
     if a.kernel_only:
         return res, None
 
@@ -830,6 +832,8 @@ def main():
                     help="single GPU, default workload: also measure C2, C3, C4 and attach them as per_config")
     ap.add_argument("--ep-fp8-wire", choices=["on", "off"], default="on",
                     help="N>1, fp8 configurations, fused step: token rows cross NVLink as e4m3 + scales (on) or bf16 (off)")
+    ap.add_argument("--ep-dedup", choices=["auto", "on", "off"], default="auto",
+                    help="N>1, fused step: one row per (token, owner rank) instead of per (token, expert); auto = from K >= 4")
     ap.add_argument("--ep-fused", choices=["on", "off"], default="on",
                     help="N > 1, peer memory: the fused step (send / recv_ready / wait_combine) or the single-purpose kernels")
     ap.add_argument("--gemm-mode", type=int, choices=[0, 1, 2], default=0,

@@ -293,6 +293,8 @@ typedef struct fmoe_ep_layout_c {
   uint64_t flags_return;   /* int32[G]: epoch at which each peer finished returning this rank's rows (fused path) */
   uint64_t row_scales;     /* bytes [recv_cap, scale_row_bytes]: scales of the received rows when they travel as
                               e4m3 (fmoe_ep_send_rows); unused otherwise */
+  uint64_t src_rank;       /* int32[recv_cap]: source rank of each received row (de-duplicated step, where
+                              ids / weights are [recv_cap, K] and src is int32 [recv_cap, K]: pair index or -1) */
 } fmoe_ep_layout_c;
 
 /* Groups this rank's T*K routed pairs by the rank that owns the expert (stable):
@@ -363,6 +365,23 @@ FMOE_API int fmoe_ep_send_rows(const void* rows, int32_t row_bytes, const void* 
 /* Waits until every rank's rows have arrived and fills row_ptrs[i] (i < *n_recv_dev) with the
  * address, in the source rank's `back` array, where the result of received row i belongs: the
  * partial_row_ptrs of the local fmoe_run. */
+/* De-duplicated form of the fused step: one row per (token, owner rank) instead of per (token,
+ * expert).  The owner receives the token's K-wide lists: ids [recv_cap, K] (local expert id, -1
+ * where the expert lives on another rank), weights [recv_cap, K], src int32 [recv_cap, K] (routed
+ * pair index on the source rank, -1 likewise) and src_rank [recv_cap]; n_recv_dev counts rows.
+ * The owner runs the operator with K experts per row and fmoe_ep_recv_ready_dedup's row_ptrs
+ * [recv_cap * K] as partial_row_ptrs; fmoe_ep_wait_combine is unchanged.  At most 256 tokens per
+ * SM and rank.  Results are bit-identical to the form with one row per pair. */
+FMOE_API int fmoe_ep_send_rows_dedup(const void* rows, int32_t row_bytes, const void* row_scales,
+                                     int32_t scale_row_bytes, const int32_t* topk_ids, const float* topk_weight,
+                                     int32_t T, int32_t K, int32_t experts_per_rank, const uint64_t* peer_base,
+                                     const fmoe_ep_layout_c* lay, int32_t me, int32_t G, int32_t* scratch,
+                                     const int32_t* epoch_dev, int32_t* n_recv_dev, int32_t* status,
+                                     int32_t timeout_ms, void* stream);
+FMOE_API int fmoe_ep_recv_ready_dedup(int32_t H, int32_t K, const int32_t* n_recv_dev, const uint64_t* peer_base,
+                                      const fmoe_ep_layout_c* lay, int32_t me, int32_t G, const int32_t* epoch_dev,
+                                      uint64_t* row_ptrs, int32_t* scratch, int32_t* status, int32_t timeout_ms,
+                                      void* stream);
 FMOE_API int fmoe_ep_recv_ready(int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base,
                                 const fmoe_ep_layout_c* lay, int32_t me, int32_t G, const int32_t* epoch_dev,
                                 uint64_t* row_ptrs, int32_t* scratch, int32_t* status, int32_t timeout_ms,

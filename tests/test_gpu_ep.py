@@ -278,7 +278,7 @@ def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
     run_gpu(d)
 
 
-def _stress_worker(rank, world, port, quant, steps, ret):
+def _stress_worker(rank, world, port, quant, steps, ret, dedup=None, K=2):
     """Many steps with fresh routing and activations every step, the fused step and the
     single-purpose kernels side by side: both return bf16 partial rows and add them in k order,
     so their outputs must agree bit for bit; a race between steps (a flag, a count or a row
@@ -291,7 +291,7 @@ def _stress_worker(rank, world, port, quant, steps, ret):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        T, H, I, E, K = 192 * world, 512, 256, 8, 2
+        T, H, I, E = 192 * world, 512, 256, 8
         d = O.make_inputs(T, H, I, E, K, quant, "softmax", seed=29)
         e_local, t_local = E // world, T // world
         lo = rank * e_local
@@ -301,7 +301,8 @@ def _stress_worker(rank, world, port, quant, steps, ret):
             w1, w2 = to_dev(d["w1"][lo:lo + e_local], device=dev), to_dev(d["w2"][lo:lo + e_local], device=dev)
             s1, s2 = to_dev(d["w1_scale"][lo:lo + e_local], device=dev), to_dev(d["w2_scale"][lo:lo + e_local], device=dev)
         mk = lambda fused: ep.PeerExpertParallelMoE(E, world, rank, traits_for(quant), w1, w2, s1, s2,
-                                                    tokens_per_rank=t_local, topk=K, hidden=H, fused=fused)
+                                                    tokens_per_rank=t_local, topk=K, hidden=H, fused=fused,
+                                                    dedup=dedup)
         fused, plain = mk(True), mk(False)
         g = torch.Generator(device=dev)
         g.manual_seed(1000 + rank)
@@ -325,16 +326,19 @@ def _stress_worker(rank, world, port, quant, steps, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("quant", [0, 1, 3])
-def test_fused_and_single_purpose_steps_agree_bit_for_bit_over_many_random_steps(quant):
+@pytest.mark.parametrize("quant,dedup,K", [(0, False, 2), (1, False, 2), (3, False, 2), (0, True, 2), (3, True, 2),
+                                           (1, True, 5)])
+def test_fused_and_single_purpose_steps_agree_bit_for_bit_over_many_random_steps(quant, dedup, K):
     """With an fp8 quant mode the fused step also sends e4m3 rows + scales where the single-purpose
-    kernels send bf16 rows: the agreement covers that the wire format does not change a bit."""
+    kernels send bf16 rows, and with dedup one row per (token, owner rank) with K-wide lists
+    (K = 5 of 8 experts on 2 ranks: more experts per token than a rank owns): the agreement covers
+    that neither the wire format nor the de-duplication changes a bit."""
     world = 2 if torch.cuda.device_count() >= 2 else 1
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_stress_worker, args=(r, world, port, quant, 60, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_stress_worker, args=(r, world, port, quant, 40, ret, dedup, K)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

@@ -62,7 +62,8 @@ class EpLayout(ctypes.Structure):
     """Byte offsets inside the per-rank peer-addressable buffer (fmoe_ep_layout_c)."""
     _fields_ = [(n, ctypes.c_uint64) for n in ("flags", "matrix", "rows", "ids", "weights", "src", "back")] + \
                [("recv_cap", ctypes.c_int64), ("send_cap", ctypes.c_int64),
-                ("flags_dispatch", ctypes.c_uint64), ("flags_return", ctypes.c_uint64), ("row_scales", ctypes.c_uint64)]
+                ("flags_dispatch", ctypes.c_uint64), ("flags_return", ctypes.c_uint64), ("row_scales", ctypes.c_uint64),
+                ("src_rank", ctypes.c_uint64)]
 
 
 _lib: Optional[ctypes.CDLL] = None
@@ -118,6 +119,8 @@ def lib() -> ctypes.CDLL:
                                    vp, vp, i32, vp]
         l.fmoe_ep_send_rows.argtypes = [vp, i32, vp, i32, vp, vp, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32,
                                         vp, vp, vp, vp, i32, vp]
+        l.fmoe_ep_send_rows_dedup.argtypes = l.fmoe_ep_send_rows.argtypes
+        l.fmoe_ep_recv_ready_dedup.argtypes = [i32, i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp, vp, i32, vp]
         l.fmoe_quantise_rows.argtypes = [vp, i32, i32, i32, vp, vp, vp]
         l.fmoe_ep_recv_ready.argtypes = [i32, vp, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp, vp, i32, vp]
         l.fmoe_ep_wait_combine.argtypes = [vp, i32, i32, i32, i32, vp, ctypes.POINTER(EpLayout), i32, i32, vp, vp, vp,

@@ -336,6 +336,153 @@ ep_send_kernel(const EpSendParams p) {
   }
 }
 
+// The same step with one row per (token, owner rank): a token whose K experts live on fewer than K
+// ranks crosses the wire once per rank, with its K-wide list of local expert ids (-1 where the
+// expert lives elsewhere), weights and return slots, and the owner's operator multiplies it for
+// every listed expert.  One token per thread (at most kSendThreads tokens per CTA).
+__global__ void __launch_bounds__(kSendThreads)
+ep_send_dedup_kernel(const EpSendParams p) {
+  __shared__ int32_t tcnt[kSendThreads][kSendMaxRanks];      // per token and destination: 0/1, then running offset
+  __shared__ int32_t slot_of[kSendThreads][kSendMaxRanks];   // receive slot of (token, destination), -1 = not sent there
+  __shared__ int32_t cta_base[kSendMaxRanks], recv_base[kSendMaxRanks], total[kSendMaxRanks];
+  const int tid = threadIdx.x, G = p.G, C = gridDim.x;
+  const int chunk = (p.T + C - 1) / C;             // <= kSendThreads (checked by the host)
+  const int t0 = blockIdx.x * chunk;
+  const int n = max(0, min(p.T, t0 + chunk) - t0);
+  const int epoch = *p.epoch;
+  const int n_exp = p.e_local * G;
+
+  // 1. owner ranks of this thread's token
+  uint32_t mask = 0;
+  if (tid < n) {
+    for (int k = 0; k < p.K; ++k) {
+      const int e = p.topk_ids[(t0 + tid) * p.K + k];
+      if (e >= 0 && e < n_exp) mask |= 1u << (e / p.e_local);
+    }
+  }
+  for (int d = 0; d < G; ++d) tcnt[tid][d] = static_cast<int32_t>((mask >> d) & 1u);
+  __syncthreads();
+  if (tid < G) {
+    int run = 0;
+    for (int t = 0; t < kSendThreads; ++t) {
+      const int v = tcnt[t][tid];
+      tcnt[t][tid] = run;
+      run += v;
+    }
+    p.cta_counts[blockIdx.x * G + tid] = run;
+  }
+  // 2. all CTAs of this kernel meet (they are co-resident: at most one per SM)
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    atomicAdd(&p.sync[0], 1);
+    const long long t_start = clock64();
+    while (atomicAdd(&p.sync[0], 0) < C) {
+      if (clock64() - t_start > p.limit) {
+        atomicExch(p.status, 0x310);
+        break;
+      }
+      __nanosleep(32);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  // 3. offsets of this CTA inside each destination's group; totals; CTA 0 publishes the totals
+  if (tid < G) {
+    int before = 0, all = 0;
+    for (int c = 0; c < C; ++c) {
+      const int v = __ldcg(&p.cta_counts[c * G + tid]);
+      if (c < static_cast<int>(blockIdx.x)) before += v;
+      all += v;
+    }
+    cta_base[tid] = before;
+    total[tid] = all;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < G * G; i += kSendThreads) {
+      const int peer = i / G, d = i % G;
+      peer_ptr<int32_t>(p.peer_base, peer, p.lay.matrix)[p.me * G + d] = total[d];
+    }
+    __syncthreads();
+    if (tid < G) st_release_sys(peer_ptr<int32_t>(p.peer_base, tid, p.lay.flags) + p.me, epoch);
+  }
+  // 4. everybody's counts
+  wait_flags(peer_ptr<int32_t>(p.peer_base, p.me, p.lay.flags), p.sync + 2, G, epoch, p.limit, p.status);
+  const int32_t* matrix = peer_ptr<int32_t>(p.peer_base, p.me, p.lay.matrix);
+  if (tid < G) {
+    int base = 0;
+    for (int s2 = 0; s2 < p.me; ++s2) base += __ldcg(&matrix[s2 * G + tid]);
+    recv_base[tid] = base;
+  }
+  if (blockIdx.x == 0 && tid == 0) {
+    int nr = 0;
+    for (int s2 = 0; s2 < G; ++s2) nr += __ldcg(&matrix[s2 * G + p.me]);
+    *p.n_recv_dev = nr;
+  }
+  __syncthreads();
+  // 5. receive slot of every (token, destination)
+  for (int d = 0; d < G; ++d)
+    slot_of[tid][d] = ((mask >> d) & 1u) ? recv_base[d] + cta_base[d] + tcnt[tid][d] : -1;
+  __syncthreads();
+  // 6. one warp per (token, destination): the row, its scales, the K-wide metadata
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int pd = warp; pd < n * G; pd += kSendThreads / 32) {
+    const int i = pd / G, d = pd - i * G;
+    const int dst = slot_of[i][d];
+    if (dst < 0 || dst >= p.lay.recv_cap) continue;
+    const int t = t0 + i;
+    uint4* rows = peer_ptr<uint4>(p.peer_base, d, p.lay.rows) + static_cast<size_t>(dst) * p.row_vecs;
+    const uint4* src_row = p.x + static_cast<size_t>(t) * p.row_vecs;
+    for (int v = lane; v < p.row_vecs; v += 32) rows[v] = src_row[v];
+    for (int w = lane; w < p.scale_words; w += 32)
+      peer_ptr<uint32_t>(p.peer_base, d, p.lay.row_scales)[static_cast<size_t>(dst) * p.scale_words + w] =
+          p.x_scale[static_cast<size_t>(t) * p.scale_words + w];
+    for (int k = lane; k < p.K; k += 32) {
+      const int r = t * p.K + k;
+      const int e = p.topk_ids[r];
+      const bool here = e >= 0 && e < n_exp && e / p.e_local == d;
+      const size_t o = static_cast<size_t>(dst) * p.K + k;
+      peer_ptr<int32_t>(p.peer_base, d, p.lay.ids)[o] = here ? e % p.e_local : -1;
+      peer_ptr<float>(p.peer_base, d, p.lay.weights)[o] = p.topk_w[r];
+      peer_ptr<int32_t>(p.peer_base, d, p.lay.src)[o] = here ? r : -1;
+    }
+    if (lane == 0) peer_ptr<int32_t>(p.peer_base, d, p.lay.src_rank)[dst] = p.me;
+  }
+  // 7. the last CTA to finish tells every rank that this rank's rows are complete
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int prev = atomicAdd(&p.sync[1], 1);
+    if (prev == C - 1) {
+      p.sync[0] = 0;
+      p.sync[1] = 0;
+      fence_acq_rel_sys();
+      for (int peer = 0; peer < G; ++peer)
+        st_relaxed_sys(peer_ptr<int32_t>(p.peer_base, peer, p.lay.flags_dispatch) + p.me, epoch);
+    }
+  }
+}
+
+// Return addresses of the de-duplicated step: entry (row, k) of the received rows.
+__global__ void __launch_bounds__(256)
+ep_recv_ready_dedup_kernel(int H, int K, const int32_t* __restrict__ n_recv_dev,
+                           const uint64_t* __restrict__ peer_base, fmoe_ep_layout_c lay, int me, int G,
+                           const int32_t* __restrict__ epoch, uint64_t* __restrict__ row_ptrs,
+                           int32_t* __restrict__ scratch, int32_t* __restrict__ status, long long limit) {
+  wait_flags(peer_ptr<int32_t>(peer_base, me, lay.flags_dispatch), scratch + 3, G, *epoch, limit, status);
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = i / K;
+  if (row >= *n_recv_dev || row >= lay.recv_cap) return;
+  const int s = __ldcg(peer_ptr<int32_t>(peer_base, me, lay.src) + i);
+  if (s < 0) return;                       // this expert of the token lives on another rank: never read
+  const int from = __ldcg(peer_ptr<int32_t>(peer_base, me, lay.src_rank) + row);
+  // never follow a bad return address: such a row goes to a scratch row of this rank instead
+  const bool ok = from >= 0 && from < G && s < lay.send_cap;
+  row_ptrs[i] = ok ? peer_base[from] + lay.back + static_cast<uint64_t>(s) * H * 2 : peer_base[me] + lay.rows;
+  if (!ok) atomicExch(status, 0x320);
+}
+
 __global__ void __launch_bounds__(256)
 ep_recv_ready_kernel(int H, const int32_t* __restrict__ n_recv_dev, const uint64_t* __restrict__ peer_base,
                      fmoe_ep_layout_c lay, int me, int G, const int32_t* __restrict__ epoch,
@@ -521,6 +668,53 @@ int fmoe_ep_send_rows(const void* x, int32_t row_bytes, const void* row_scales, 
   p.limit = wait_limit_cycles(timeout_ms);
   fmoe::ep_send_kernel<<<grid, fmoe::kSendThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return fmoe::launch_status("fmoe_ep_send");
+}
+
+int fmoe_ep_send_rows_dedup(const void* x, int32_t row_bytes, const void* row_scales, int32_t scale_row_bytes,
+                            const int32_t* topk_ids, const float* topk_weight, int32_t T, int32_t K,
+                            int32_t experts_per_rank, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,
+                            int32_t me, int32_t G, int32_t* scratch, const int32_t* epoch_dev, int32_t* n_recv_dev,
+                            int32_t* status, int32_t timeout_ms, void* stream) {
+  if (!x || !topk_ids || !topk_weight || !peer_base || !lay || !scratch || !epoch_dev || !n_recv_dev || !status)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send_rows_dedup: a required pointer is null");
+  if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send_rows_dedup: rank %d / world %d out of range (at most %d ranks)",
+                      me, G, fmoe::kSendMaxRanks);
+  if (row_bytes <= 0 || row_bytes % 16 || T <= 0 || K <= 0 || experts_per_rank <= 0 || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send_rows_dedup: row bytes must be a positive multiple of 16; T, K, experts_per_rank positive");
+  if (scale_row_bytes < 0 || scale_row_bytes % 4 || (scale_row_bytes > 0 && !row_scales))
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_send_rows_dedup: scale row bytes must be a multiple of 4 and come with row_scales");
+  const int sms = fmoe::device_sm_count();
+  const int grid = T < sms ? T : sms;
+  if ((T + grid - 1) / grid > fmoe::kSendThreads)
+    return fmoe::fail(FMOE_ERR_UNSUPPORTED, "fmoe_ep_send_rows_dedup: at most %d tokens per rank", grid * fmoe::kSendThreads);
+  fmoe::EpSendParams p;
+  p.x = reinterpret_cast<const uint4*>(x);
+  p.x_scale = reinterpret_cast<const uint32_t*>(row_scales);
+  p.row_vecs = row_bytes / 16; p.scale_words = scale_row_bytes / 4;
+  p.topk_ids = topk_ids; p.topk_w = topk_weight;
+  p.T = T; p.K = K; p.e_local = experts_per_rank;
+  p.peer_base = peer_base; p.lay = *lay; p.me = me; p.G = G;
+  p.sync = scratch; p.cta_counts = scratch + 8;
+  p.epoch = epoch_dev; p.n_recv_dev = n_recv_dev; p.status = status;
+  p.limit = wait_limit_cycles(timeout_ms);
+  fmoe::ep_send_dedup_kernel<<<grid, fmoe::kSendThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return fmoe::launch_status("fmoe_ep_send_rows_dedup");
+}
+
+int fmoe_ep_recv_ready_dedup(int32_t H, int32_t K, const int32_t* n_recv_dev, const uint64_t* peer_base,
+                             const fmoe_ep_layout_c* lay, int32_t me, int32_t G, const int32_t* epoch_dev,
+                             uint64_t* row_ptrs, int32_t* scratch, int32_t* status, int32_t timeout_ms, void* stream) {
+  if (!n_recv_dev || !peer_base || !lay || !epoch_dev || !row_ptrs || !scratch || !status)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_recv_ready_dedup: a required pointer is null");
+  if (G <= 0 || G > fmoe::kSendMaxRanks || me < 0 || me >= G || H <= 0 || K <= 0 || timeout_ms < 0)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "fmoe_ep_recv_ready_dedup: bad arguments (rank %d, world %d, H %d, K %d)", me,
+                      G, H, K);
+  if (lay->recv_cap <= 0) return FMOE_OK;
+  const unsigned grid = static_cast<unsigned>((lay->recv_cap * K + 255) / 256);
+  fmoe::ep_recv_ready_dedup_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      H, K, n_recv_dev, peer_base, *lay, me, G, epoch_dev, row_ptrs, scratch, status, wait_limit_cycles(timeout_ms));
+  return fmoe::launch_status("fmoe_ep_recv_ready_dedup");
 }
 
 int fmoe_ep_recv_ready(int32_t H, const int32_t* n_recv_dev, const uint64_t* peer_base, const fmoe_ep_layout_c* lay,

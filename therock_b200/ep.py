@@ -278,6 +278,11 @@ class PeerExpertParallelMoE:
         e4m3 rows + scales, half the bytes of bf16; the owner hands them to the operator as
         pre-quantised activations.  Bit-identical to sending bf16 rows; one more launch.
 
+    dedup (fused step; default on from four experts per token): one row per (token, owner rank)
+        instead of per (token, expert).  The owner receives the token's K-wide id / weight / return
+        lists (-1 where the expert lives elsewhere) and its operator runs with K experts per row.
+        Bit-identical to one row per pair.
+
     Arithmetic in both: each (token, k) partial row crosses NVLink as bf16 and the k-sum is f32 with
     one more rounding -- the operator's partial_dtype = bf16 contract.
     Every wait is a bounded spin; a rank that never arrives shows up in `status` instead of
@@ -286,7 +291,7 @@ class PeerExpertParallelMoE:
 
     def __init__(self, num_experts: int, world: int, rank: int, traits, w1_local, w2_local,
                  w1_scale=None, w2_scale=None, *, tokens_per_rank: int, topk: int, hidden: int, group=None,
-                 fused: bool = True, fp8_wire: Optional[bool] = None):
+                 fused: bool = True, fp8_wire: Optional[bool] = None, dedup: Optional[bool] = None):
         import copy
         import ctypes
         import os
@@ -302,12 +307,15 @@ class PeerExpertParallelMoE:
             self.traits.partial_dtype = "bf16"
         is_fp8 = self.traits.quant != "none"
         self.fp8_wire = self.fused and is_fp8 and hidden % 16 == 0 and (fp8_wire is None or bool(fp8_wire))
+        self.dedup = self.fused and (topk >= 4 if dedup is None else bool(dedup))
         self.E, self.world, self.rank = num_experts, world, rank
         self.e_local = num_experts // world
         self.T, self.K, self.H = tokens_per_rank, topk, hidden
         dev = w1_local.device
         R = tokens_per_rank * topk
-        recv_cap = R * world
+        # rows this rank can receive: every routed pair of every rank, or every token once
+        recv_cap = tokens_per_rank * world if self.dedup else R * world
+        kw = topk if self.dedup else 1          # width of the per-row id / weight / return lists
 
         def al(n):
             return (n + 255) // 256 * 256
@@ -319,8 +327,9 @@ class PeerExpertParallelMoE:
         for name, nbytes in (("flags", world * 4), ("flags_dispatch", world * 4), ("flags_return", world * 4),
                              ("matrix", world * world * 4),
                              ("rows", recv_cap * row_bytes), ("row_scales", recv_cap * scale_bytes),
-                             ("ids", recv_cap * 4), ("weights", recv_cap * 4),
-                             ("src", recv_cap * 8), ("back", R * hidden * 2)):
+                             ("ids", recv_cap * kw * 4), ("weights", recv_cap * kw * 4),
+                             ("src", recv_cap * max(2, kw) * 4), ("src_rank", recv_cap * 4),
+                             ("back", R * hidden * 2)):
             setattr(lay, name, off)
             off = al(off + nbytes)
         lay.recv_cap, lay.send_cap = recv_cap, R
@@ -344,8 +353,8 @@ class PeerExpertParallelMoE:
         else:
             self.rows = view("rows", recv_cap * hidden, torch.bfloat16).view(recv_cap, hidden)
             self.row_scales = None
-        self.ids = view("ids", recv_cap, torch.int32).view(recv_cap, 1)
-        self.wts = view("weights", recv_cap, torch.float32).view(recv_cap, 1)
+        self.ids = view("ids", recv_cap * kw, torch.int32).view(recv_cap, kw)
+        self.wts = view("weights", recv_cap * kw, torch.float32).view(recv_cap, kw)
         self.back = view("back", R * hidden, torch.bfloat16).view(R, hidden)
         self.order = torch.empty(R, dtype=torch.int32, device=dev)
         self.inv = torch.empty(R, dtype=torch.int32, device=dev)
@@ -356,7 +365,8 @@ class PeerExpertParallelMoE:
         self.out_rows = torch.empty(recv_cap, hidden, dtype=torch.bfloat16, device=dev)
         self.args = api.FusedMoeArgs(a=self.rows, g=w1_local, d=w2_local, topk_ids=self.ids,
                                      topk_weight=self.wts, o=self.out_rows, g_scale=w1_scale,
-                                     d_scale=w2_scale, num_tokens_dev=self.n_recv, expected_tokens=R,
+                                     d_scale=w2_scale, num_tokens_dev=self.n_recv,
+                                     expected_tokens=tokens_per_rank if self.dedup else R,
                                      a_scale=self.row_scales)
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         if self.fused:
@@ -364,7 +374,7 @@ class PeerExpertParallelMoE:
             self.epoch_dev.fill_(1)
             self.send_scratch = torch.zeros(int(api.lib().fmoe_ep_send_scratch_words(tokens_per_rank, topk, world)),
                                             dtype=torch.int32, device=dev)
-            self.row_ptrs = torch.zeros(recv_cap, dtype=torch.int64, device=dev)
+            self.row_ptrs = torch.zeros(recv_cap * kw, dtype=torch.int64, device=dev)
             self.args.partial_row_ptrs = self.row_ptrs
             self.args.done_flag_addrs = (self.peer_base + (lay.flags_return + 4 * rank)).contiguous()
             self.args.done_flag_value = self.epoch_dev
@@ -393,24 +403,33 @@ class PeerExpertParallelMoE:
         if out is None:
             out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         self._mark("start")
-        if self.fp8_wire:
-            api.quantise_rows(x, self.traits.quant, self.xq, self.xq_scale)
-            api._check(lib.fmoe_ep_send_rows(self.xq.data_ptr(), self.row_bytes, self.xq_scale.data_ptr(),
-                                             self.scale_row_bytes, topk_ids.data_ptr(), topk_weight.data_ptr(), T, K,
-                                             self.e_local, pb, by(self.lay), self.rank, G,
-                                             self.send_scratch.data_ptr(), self.epoch_dev.data_ptr(),
-                                             self.n_recv.data_ptr(), self.status.data_ptr(),
-                                             self.barrier_timeout_ms, st))
+        if self.fp8_wire or self.dedup:
+            if self.fp8_wire:
+                api.quantise_rows(x, self.traits.quant, self.xq, self.xq_scale)
+                rows, scales = self.xq.data_ptr(), self.xq_scale.data_ptr()
+            else:
+                rows, scales = x.data_ptr(), None
+            send = lib.fmoe_ep_send_rows_dedup if self.dedup else lib.fmoe_ep_send_rows
+            api._check(send(rows, self.row_bytes, scales, self.scale_row_bytes, topk_ids.data_ptr(),
+                            topk_weight.data_ptr(), T, K, self.e_local, pb, by(self.lay), self.rank, G,
+                            self.send_scratch.data_ptr(), self.epoch_dev.data_ptr(), self.n_recv.data_ptr(),
+                            self.status.data_ptr(), self.barrier_timeout_ms, st))
         else:
             api._check(lib.fmoe_ep_send(x.data_ptr(), topk_ids.data_ptr(), topk_weight.data_ptr(), T, K, H,
                                         self.e_local, pb, by(self.lay), self.rank, G, self.send_scratch.data_ptr(),
                                         self.epoch_dev.data_ptr(), self.n_recv.data_ptr(), self.status.data_ptr(),
                                         self.barrier_timeout_ms, st))
         self._mark("send")
-        api._check(lib.fmoe_ep_recv_ready(H, self.n_recv.data_ptr(), pb, by(self.lay), self.rank, G,
-                                          self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(),
-                                          self.send_scratch.data_ptr(), self.status.data_ptr(),
-                                          self.barrier_timeout_ms, st))
+        if self.dedup:
+            api._check(lib.fmoe_ep_recv_ready_dedup(H, K, self.n_recv.data_ptr(), pb, by(self.lay), self.rank, G,
+                                                    self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(),
+                                                    self.send_scratch.data_ptr(), self.status.data_ptr(),
+                                                    self.barrier_timeout_ms, st))
+        else:
+            api._check(lib.fmoe_ep_recv_ready(H, self.n_recv.data_ptr(), pb, by(self.lay), self.rank, G,
+                                              self.epoch_dev.data_ptr(), self.row_ptrs.data_ptr(),
+                                              self.send_scratch.data_ptr(), self.status.data_ptr(),
+                                              self.barrier_timeout_ms, st))
         self._mark("recv_ready")
         api.fused_moe(self.traits, self.args)
         self._mark("local_moe")
