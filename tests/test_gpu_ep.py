@@ -214,15 +214,17 @@ def test_barrier_wait_is_bounded_when_a_rank_never_arrives():
     assert int(theirs[:8].view(torch.int32)[0].item()) == 3
 
 
-def _fake_two_rank_layout(dev, T, K, H):
-    """Two full peer buffers on one GPU: rank 0 is driven by the test, rank 1 never acts."""
+def _fake_two_rank_layout(dev, T, K, H, kw=1):
+    """Two full peer buffers on one GPU: rank 0 is driven by the test, rank 1 never acts.
+    kw: width of the per-row id / weight / return lists (K in the de-duplicated step)."""
     from therock_b200 import api
     lay = api.EpLayout()
     R, world = T * K, 2
     recv_cap, off = R * world, 0
     for name, nbytes in (("flags", 8), ("flags_dispatch", 8), ("flags_return", 8), ("matrix", 16),
-                         ("rows", recv_cap * H * 2), ("ids", recv_cap * 4), ("weights", recv_cap * 4),
-                         ("src", recv_cap * 8), ("back", R * H * 2)):
+                         ("rows", recv_cap * H * 2), ("row_scales", 256), ("ids", recv_cap * kw * 4),
+                         ("weights", recv_cap * kw * 4), ("src", recv_cap * max(2, kw) * 4),
+                         ("src_rank", recv_cap * 4), ("back", R * H * 2)):
         setattr(lay, name, off)
         off = (off + nbytes + 255) // 256 * 256
     lay.recv_cap, lay.send_cap = recv_cap, R
@@ -232,15 +234,17 @@ def _fake_two_rank_layout(dev, T, K, H):
     return lay, mine, theirs, peer_base
 
 
-def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
+@pytest.mark.parametrize("dedup", [False, True])
+def test_fused_step_waits_are_bounded_when_a_rank_never_arrives(dedup):
     """Failure detection for the fused kernels without a fault: rank 1 of a two-rank step never
-    writes any flag.  Each of the three kernels must give up after its 50 ms limit, report rank 1
-    in the status word and return, leaving the context usable."""
+    writes any flag.  Each of the three kernels (both forms of the send and of recv_ready) must
+    give up after its 50 ms limit, report rank 1 in the status word and return, leaving the
+    context usable."""
     import ctypes
     from therock_b200 import api
     dev = "cuda:0"
     T, K, H, e_local = 64, 2, 256, 4
-    lay, mine, theirs, peer_base = _fake_two_rank_layout(dev, T, K, H)
+    lay, mine, theirs, peer_base = _fake_two_rank_layout(dev, T, K, H, kw=K if dedup else 1)
     lib, by = api.lib(), ctypes.byref
     st = torch.cuda.current_stream().cuda_stream
     d = O.make_inputs(T, H, 128, 2 * e_local, K, 0, "softmax", seed=41)
@@ -249,8 +253,14 @@ def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     n_recv = torch.zeros(1, dtype=torch.int32, device=dev)
     scratch = torch.zeros(int(lib.fmoe_ep_send_scratch_words(T, K, 2)), dtype=torch.int32, device=dev)
-    rc = lib.fmoe_ep_send(x.data_ptr(), ids.data_ptr(), w.data_ptr(), T, K, H, e_local, peer_base.data_ptr(), by(lay),
-                          0, 2, scratch.data_ptr(), epoch.data_ptr(), n_recv.data_ptr(), status.data_ptr(), 50, st)
+    if dedup:
+        rc = lib.fmoe_ep_send_rows_dedup(x.data_ptr(), 2 * H, None, 0, ids.data_ptr(), w.data_ptr(), T, K, e_local,
+                                         peer_base.data_ptr(), by(lay), 0, 2, scratch.data_ptr(), epoch.data_ptr(),
+                                         n_recv.data_ptr(), status.data_ptr(), 50, st)
+    else:
+        rc = lib.fmoe_ep_send(x.data_ptr(), ids.data_ptr(), w.data_ptr(), T, K, H, e_local, peer_base.data_ptr(),
+                              by(lay), 0, 2, scratch.data_ptr(), epoch.data_ptr(), n_recv.data_ptr(),
+                              status.data_ptr(), 50, st)
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) == (0x300 | 1)
@@ -259,9 +269,14 @@ def test_fused_step_waits_are_bounded_when_a_rank_never_arrives():
     assert int(theirs[lay.flags_dispatch:lay.flags_dispatch + 4].view(torch.int32).item()) == 1
     assert int(scratch[:2].abs().sum().item()) == 0                  # the kernel's own counters are back at zero
     status.zero_()
-    row_ptrs = torch.zeros(int(lay.recv_cap), dtype=torch.int64, device=dev)
-    rc = lib.fmoe_ep_recv_ready(H, n_recv.data_ptr(), peer_base.data_ptr(), by(lay), 0, 2, epoch.data_ptr(),
-                                row_ptrs.data_ptr(), scratch.data_ptr(), status.data_ptr(), 50, st)
+    row_ptrs = torch.zeros(int(lay.recv_cap) * K, dtype=torch.int64, device=dev)
+    if dedup:
+        rc = lib.fmoe_ep_recv_ready_dedup(H, K, n_recv.data_ptr(), peer_base.data_ptr(), by(lay), 0, 2,
+                                          epoch.data_ptr(), row_ptrs.data_ptr(), scratch.data_ptr(),
+                                          status.data_ptr(), 50, st)
+    else:
+        rc = lib.fmoe_ep_recv_ready(H, n_recv.data_ptr(), peer_base.data_ptr(), by(lay), 0, 2, epoch.data_ptr(),
+                                    row_ptrs.data_ptr(), scratch.data_ptr(), status.data_ptr(), 50, st)
     torch.cuda.synchronize()
     assert rc == 0 and int(status.item()) == (0x300 | 1)
     status.zero_()
