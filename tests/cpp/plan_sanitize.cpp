@@ -98,6 +98,25 @@ int main() {
       }
     }
   }
+  // pre-quantised activations: fp8 modes only; no quantise-once pass, no decode prologue, no x_quant region
+  {
+    fmoe_traits_c tq = t;
+    int dummy = 0;
+    fmoe_args_c aq = dims(16, 512, 256, 8, 2);
+    aq.x_scale = &dummy;
+    tq.quant = FMOE_QUANT_NONE; tq.weight_dtype = FMOE_BF16;
+    EXPECT(validate_dims(&tq, &aq) == FMOE_ERR_INVALID_ARG);
+    tq.quant = FMOE_QUANT_TOKEN_CHANNEL; tq.weight_dtype = FMOE_FP8_E4M3;
+    EXPECT(validate_dims(&tq, &aq) == FMOE_OK);
+    EXPECT(!fused_prologue(&tq, &aq) && !quantise_once(&tq, &aq));
+    Plan p;
+    EXPECT(make_plan(&tq, &aq, &p) == FMOE_OK && p.l.x_quant_scale == p.l.x_quant);
+    fmoe_run_info_c info;
+    std::memset(&info, 0, sizeof(info));
+    EXPECT(describe_run(&tq, &aq, 148, 0, &info) == FMOE_OK && info.launches == 6);   // sort, gather, gemm1, quant y, gemm2, combine
+    aq.x_scale = nullptr;
+    EXPECT(fused_prologue(&tq, &aq));
+  }
   // UE8M0 scale rows are padded to whole 32-bit words
   EXPECT(packed_scale_pitch(7 * 128) == 8 && packed_scale_pitch(16 * 128) == 16 && packed_scale_pitch(128) == 4);
   EXPECT(packed_scale_bytes(256, 7 * 128) == 256u * 8u);
