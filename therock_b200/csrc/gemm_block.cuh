@@ -431,7 +431,12 @@ fmoe_grouped_gemm_block_kernel(const __grid_constant__ CUtensorMap tm_a,
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                    static_cast<uint32_t>(buf * kTileN);
             uint32_t v[2][32];
-            const bool dbg_no_ld = FMOE_DBG(p, 4u), dbg_no_fma = FMOE_DBG(p, 1u);
+            // The loop is register-tight (232 per thread: 128 sums, 64 loaded values, the scales in
+            // flight).  Its phases -- two loads, FMAs, two loads, FMAs -- stay separate basic
+            // blocks behind conditions that are always true but not provable (k_blocks > 0, n_blocks > 0): without
+            // them the compiler overlaps the phases' live ranges and spills inside the loop (208
+            // bytes of spill stores in the second GEMM's instance, 2.7 ms instead of 2.1 ms).
+            const bool dbg_no_ld = FMOE_DBG(p, 4u) || bp.k_blocks <= 0, dbg_no_fma = FMOE_DBG(p, 1u) || p.n_blocks <= 0;
             if (!dbg_no_ld) {
               ptx::tmem_ld_32x32(t_row + col0, v[0]);
               ptx::tmem_ld_32x32(t_row + col0 + 32, v[1]);
