@@ -320,7 +320,7 @@ def _coverage_tokens(sorted_tok, npp, mblk_cum, T, n_blocks_wanted, rng):
     return np.unique(np.array(sel, dtype=np.int32))
 
 
-def _full_size(name, n_blocks_wanted=64):
+def _full_size(name, n_blocks_wanted=64, gemm_mode=0):
     """Inputs generated on the device at the configuration's full size (the benchmark's own
     generator).  The oracle evaluates the tokens that sit in the first and the last live slot of
     at least 64 row blocks -- every expert's first and last block among them -- so every expert
@@ -332,10 +332,10 @@ def _full_size(name, n_blocks_wanted=64):
     d = bench.device_inputs(c, torch.device("cuda:0"))
     args = M.FusedMoeArgs(a=d["x"], g=d["w1"], d=d["w2"], topk_ids=d["ids"], topk_weight=d["w"],
                           g_scale=d["s1"], d_scale=d["s2"])
-    out = M.fused_moe(traits_for(quant), args)
+    out = M.fused_moe(traits_for(quant, gemm_mode=gemm_mode), args)
     torch.cuda.synchronize()
     assert api.check_status(args.workspace) == 0
-    lay = M.workspace_layout(traits_for(quant), args)
+    lay = M.workspace_layout(traits_for(quant, gemm_mode=gemm_mode), args)
     ws, cap = args.workspace, lay["capacity"]
     tok = ws[lay["sorted_token_ids"]:lay["sorted_token_ids"] + 4 * cap].view(torch.int32).cpu().numpy()
     cum = ws[lay["mblk_cum"]:lay["mblk_cum"] + 4 * (E + 1)].view(torch.int32).cpu().numpy()
@@ -372,6 +372,12 @@ def test_full_size_deepseek_block_scaled_fp8():
 
 def test_full_size_deepseek_block_scaled_fp8_power_of_two_scales():
     assert _full_size("C4m", n_blocks_wanted=256) >= 512
+
+
+def test_full_size_deepseek_power_of_two_scales_tokens_on_n_kernel():
+    """The selectable kernel form (weights on M, tokens on N) at the full DeepSeek-V3-shape size:
+    256 experts with 200-320 live rows each, i.e. two chunks of unequal size per expert."""
+    assert _full_size("C4m", n_blocks_wanted=128, gemm_mode=2) >= 256
 
 
 def test_deepseek_shape_block_scaled_reduced():
