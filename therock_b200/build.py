@@ -63,6 +63,9 @@ def _build_variant(suffix: str, defines: list, force: bool, verbose: bool) -> st
 
     with ThreadPoolExecutor(max_workers=4) as ex:
         for cmd, rc, out in ex.map(run, jobs):
+            # ptxas -v output (registers, spills, shared memory per kernel) is kept beside the object
+            with open(cmd[-1] + ".log", "w") as f:
+                f.write(out)
             if verbose or rc != 0:
                 print(" ".join(cmd))
                 print(out)
